@@ -1,0 +1,294 @@
+/*
+ * mxk.h - C ABI of libmxk, the sm_100a implementation of Miroxen's fused DiT layer ops.
+ *
+ * Every entry point below replaces one launcher of the reference's src/kernels/ops.h (the
+ * citation beside each declaration is the reference declaration it stands in for) or one of the
+ * host-side table builders in its model graphs.  The conventions are the reference's own:
+ *
+ *  - all data pointers are caller-owned DEVICE memory on the CURRENT device, unless the
+ *    parameter name ends in _host;
+ *  - the call is asynchronous on `stream`; nothing here synchronises, allocates, frees or
+ *    changes the current device;
+ *  - rows <= 0 / S <= 0 / n <= 0 is a silent no-op that returns MXK_OK (src/kernels/ops.cu:155,
+ *    179, 200, 139);
+ *  - bf16 tensors are passed as uint16_t* holding the raw bfloat16 bit patterns;
+ *  - the residual stream is fp32, GEMM/attention operands are bf16, modulation vectors, norm
+ *    weights and cos/sin tables are fp32, arithmetic is fp32 (src/kernels/ops.h:2).
+ *
+ * Return value: MXK_OK (0) or a negative MXK_ERR_* code; mxk_last_error() then returns a
+ * thread-local, human-readable message.  The C++ shim in mx_ops.h turns a non-zero status into
+ * std::runtime_error, which is what the reference's MX_CHECK / MX_KCHECK macros throw
+ * (src/core/common.h:34-48).
+ */
+#ifndef MXK_H_
+#define MXK_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MXK_OK 0
+#define MXK_ERR_INVALID_ARG (-1) /* a shape, pointer or mode the op cannot accept */
+#define MXK_ERR_CUDA (-2)        /* the CUDA runtime reported an error at launch */
+#define MXK_ERR_TOO_LARGE (-3)   /* a size beyond a documented fixed limit */
+
+typedef uint16_t mxk_bf16;  /* raw bfloat16 bits */
+typedef void* mxk_stream_t; /* a cudaStream_t */
+
+/* Per-row choice between two modulation vectors: rows with index < prefix_len use `prefix`,
+ * the others `target`; target == NULL means "this modulation is absent".  Same layout as the
+ * reference's RowMod (src/kernels/ops.h:11-15). */
+typedef struct MxkRowMod {
+  const float* target;
+  const float* prefix;
+  int64_t prefix_len;
+} MxkRowMod;
+
+/* src/kernels/ops.h:39 enum RopeMode */
+#define MXK_ROPE_NONE 0
+#define MXK_ROPE_INTERLEAVED 1 /* channel pairs (2i, 2i+1) */
+#define MXK_ROPE_HALF 2        /* channel pairs (i, i + rot/2) */
+
+const char* mxk_last_error(void);
+/* ABI version of the library (major * 100 + minor). */
+int mxk_version(void);
+/* Number of kernel launches this thread has issued through the library since the last call of
+ * mxk_reset_launch_count(); used by the benchmark to state its own launch count. */
+int64_t mxk_launch_count(void);
+void mxk_reset_launch_count(void);
+
+/* ---- normalisation + modulation + cast -------------------------------------------------- */
+
+/* src/kernels/ops.h:18 layernorm_mod: out = bf16(LayerNorm(x) * (1 + scale) + shift), no affine,
+ * two-pass variance, rstd = rsqrt(var + eps). x fp32 [rows, dim], out bf16 [rows, dim]. */
+int mxk_layernorm_mod(const float* x, int64_t rows, int64_t dim, float eps, MxkRowMod scale,
+                      MxkRowMod shift, mxk_bf16* out, mxk_stream_t stream);
+/* src/kernels/ops.h:21 rmsnorm_mod: out = bf16(x * rsqrt(mean(x^2) + eps) * w * (1 + scale) + shift);
+ * w, scale and shift may each be absent. */
+int mxk_rmsnorm_mod(const float* x, int64_t rows, int64_t dim, float eps, const float* w,
+                    MxkRowMod scale, MxkRowMod shift, mxk_bf16* out, mxk_stream_t stream);
+/* src/kernels/ops.h:24 rmsnorm_bf16: rmsnorm_mod with a bf16 input and no modulation. */
+int mxk_rmsnorm_bf16(const mxk_bf16* x, int64_t rows, int64_t dim, float eps, const float* w,
+                     mxk_bf16* out, mxk_stream_t stream);
+
+/* ---- residual --------------------------------------------------------------------------- */
+
+/* src/kernels/ops.h:27 gated_residual: x += act(gate) * y with act = tanh when gate_tanh != 0,
+ * identity otherwise; gate.target == NULL gives x += y. x fp32 [rows, dim], y bf16 [rows, dim]. */
+int mxk_gated_residual(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, MxkRowMod gate,
+                       int gate_tanh, mxk_stream_t stream);
+/* src/kernels/ops.h:30 add_inplace_bf16: x(bf16) = bf16(x + y). */
+int mxk_add_inplace_bf16(mxk_bf16* x, const mxk_bf16* y, int64_t n, mxk_stream_t stream);
+
+/* ---- per-head RMSNorm + rotary ---------------------------------------------------------- */
+
+/* src/kernels/ops.h:35 head_norm_rope: head h of token s is in[s*in_stride + col0 + h*D .. +D);
+ * optional per-head RMSNorm (norm_w fp32 [D], NULL skips it) then rotary on the first `rot`
+ * channels with cos/sin fp32 [S, rot/2]; writes out bf16 [S, H, D].  D even and <= 256, rot even
+ * and <= D (src/kernels/ops.cu:201).  mode MXK_ROPE_NONE with norm_w == NULL is a strided copy. */
+int mxk_head_norm_rope(const mxk_bf16* in, int64_t S, int64_t in_stride, int64_t col0, int H,
+                       int D, const float* norm_w, float eps, const float* cos, const float* sin,
+                       int rot, int mode, mxk_bf16* out, mxk_stream_t stream);
+
+/* ---- activations ------------------------------------------------------------------------ */
+
+/* src/kernels/ops.h:44 silu_mul: gu bf16 [rows, 2F] (gate | up) -> out bf16 [rows, F] = silu(gate) * up. */
+int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk_stream_t stream);
+/* src/kernels/ops.h:46 gelu_tanh_inplace: x = bf16(0.5 v (1 + tanh(0.7978845608 (v + 0.044715 v^3)))). */
+int mxk_gelu_tanh_inplace(mxk_bf16* x, int64_t n, mxk_stream_t stream);
+/* src/kernels/ops.h:48 gelu_erf_inplace: x = bf16(0.5 v (1 + erf(v / sqrt 2))). */
+int mxk_gelu_erf_inplace(mxk_bf16* x, int64_t n, mxk_stream_t stream);
+/* src/kernels/ops.h:51 silu_inplace_f32: x = x / (1 + exp(-x)) on fp32. */
+int mxk_silu_inplace_f32(float* x, int64_t n, mxk_stream_t stream);
+
+/* ---- helpers around the GEMMs ----------------------------------------------------------- */
+
+/* src/kernels/ops.h:50 scatter_rows: x[rows[i], :] = src[i, :] (+= when add != 0); rows int32 [n]
+ * on the device, x fp32 [*, dim], src bf16 [n, dim]. */
+int mxk_scatter_rows(float* x, int64_t dim, const int32_t* rows, const mxk_bf16* src, int64_t n,
+                     int add, mxk_stream_t stream);
+/* src/kernels/ops.h:53 add_bias_bf16: y[r, :] = bf16(y[r, :] + bias). */
+int mxk_add_bias_bf16(mxk_bf16* y, const float* bias, int64_t rows, int64_t dim, mxk_stream_t stream);
+/* src/kernels/ops.h:54 add_bias_f32 */
+int mxk_add_bias_f32(float* y, const float* bias, int64_t rows, int64_t dim, mxk_stream_t stream);
+/* src/kernels/ops.h:56 f32_to_bf16 */
+int mxk_f32_to_bf16(const float* x, mxk_bf16* y, int64_t n, mxk_stream_t stream);
+/* src/kernels/ops.h:57 bf16_to_f32 */
+int mxk_bf16_to_f32(const mxk_bf16* x, float* y, int64_t n, mxk_stream_t stream);
+/* src/kernels/ops.h:59 axpy_f32: x += a * y */
+int mxk_axpy_f32(float* x, const float* y, float a, int64_t n, mxk_stream_t stream);
+/* src/kernels/ops.h:61 axpby_f32: x = a * x + b * y */
+int mxk_axpby_f32(float* x, const float* y, float a, float b, int64_t n, mxk_stream_t stream);
+
+/* ---- fused extensions (no single counterpart in ops.h; each equals the two or three
+ *      reference calls named, issued back to back on the same rows) ------------------------ */
+
+/* gated_residual (src/kernels/ops.h:27) followed by layernorm_mod / rmsnorm_mod
+ * (src/kernels/ops.h:18,21) on the same rows, as src/models/qwen_image/dit.cpp:305-307 and
+ * src/models/minimax_h3/dit.cpp:238-239 call them: x is read once, updated in place and
+ * normalised from registers.  norm_mode 0 = LayerNorm, 1 = RMSNorm. */
+int mxk_gated_residual_norm(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, MxkRowMod gate,
+                            int gate_tanh, int norm_mode, float eps, const float* w,
+                            MxkRowMod scale, MxkRowMod shift, mxk_bf16* out, mxk_stream_t stream);
+
+/* One tensor of a multi-tensor head_norm_rope launch. */
+typedef struct MxkHeadTensor {
+  const mxk_bf16* in; /* [S, in_stride] */
+  int64_t in_stride;
+  int64_t col0;
+  const float* norm_w; /* fp32 [D] or NULL */
+  mxk_bf16* out;       /* [S, H, D] */
+  int rot;             /* 0 with mode NONE = copy */
+  int mode;
+} MxkHeadTensor;
+/* Up to three head_norm_rope calls (q, k and the v copy of src/models/minimax_h3/dit.cpp:210-213;
+ * q and k of src/models/qwen_image/dit.cpp:270-272) that share S, H, D, eps and the cos/sin table,
+ * in one launch: the token's cos/sin row is fetched once for all of them. */
+int mxk_qkv_norm_rope(const MxkHeadTensor* tensors_host, int n_tensors, int64_t S, int H, int D,
+                      float eps, const float* cos, const float* sin, mxk_stream_t stream);
+
+/* ---- RoPE tables and timestep embeddings ------------------------------------------------
+ * The reference builds these on the host with libm and uploads them once per generation
+ * (src/models/qwen_image/dit.cpp:151-185, src/models/minimax_h3/dit.cpp:254-262).  libm's
+ * cosf/sinf are not reproducible by a different algorithm, so bit-exact tables need libm.  The
+ * split used here: the host evaluates libm only on the DISTINCT (position, frequency) pairs of
+ * each axis (a few thousand values), and a kernel expands those per-axis look-up tables into
+ * the [S, rot/2] table by each row's position index. */
+
+/* Describes a run of consecutive rows whose per-axis look-up indices follow a grid:
+ * row r = row0 + (i0 * n1 + i1) * n2 + i2 with i0 < n0, i1 < n1, i2 < n2 has, on axis a,
+ * the look-up index base[a] + i0*step0[a] + i1*step1[a] + i2*step2[a]. */
+typedef struct MxkRopeRun {
+  int64_t row0;
+  int32_t n0, n1, n2;
+  int32_t base[3];
+  int32_t step0[3];
+  int32_t step1[3];
+  int32_t step2[3];
+} MxkRopeRun;
+
+/* Expand per-axis look-up tables into cos/sin fp32 [S, half].  lut_cos/lut_sin: device fp32,
+ * axis a occupies rows [lut_row0[a], ...) of width pairs[a] starting at element lut_off[a];
+ * output pair columns of axis a are [col0[a], col0[a] + pairs[a]).  runs_host: n_runs
+ * descriptors (<= 64) covering [0, S). */
+int mxk_rope_table_expand(const float* lut_cos, const float* lut_sin, const int64_t* lut_off_host,
+                          const int32_t* pairs_host, const int32_t* col0_host, int n_axes,
+                          const MxkRopeRun* runs_host, int n_runs, int64_t S, int half, float* cos,
+                          float* sin, mxk_stream_t stream);
+
+/* Host builders (pure host code, libm; they touch no GPU).  Each returns MXK_OK or an error. */
+
+/* MSRoPE inverse frequencies of src/models/qwen_image/dit.cpp:153-157:
+ * invf = 1.0f / powf(theta, float(2j) / float(axis)) for each axis in turn; out_host has
+ * sum(axes[a] / 2) entries. */
+int mxk_msrope_inv_freq_host(const int32_t* axes_host, int n_axes, float theta, float* out_host);
+/* Look-up table of one axis: lut[(p - pos_min) * pairs + j] = cosf/sinf(float(p) * invf[j]) for
+ * p in [pos_min, pos_max] (src/models/qwen_image/dit.cpp:160-166). */
+int mxk_rope_lut_int_host(int64_t pos_min, int64_t pos_max, const float* invf_host, int pairs,
+                          float* lut_cos_host, float* lut_sin_host);
+/* Same for explicit fp32 positions (src/models/minimax_h3/dit.cpp:258-262):
+ * lut[i * pairs + j] = cosf/sinf(pos[i] * invf[j]). */
+int mxk_rope_lut_f32_host(const float* pos_host, int64_t n, const float* invf_host, int pairs,
+                          float* lut_cos_host, float* lut_sin_host);
+/* Spatial rotary coordinates of one latent axis (src/models/minimax_h3/layout.cpp:15-21):
+ * g[k] = float(((1 - r)/2 + r*k/n) * 32) with r = dim / sqrt(H*W), n = dim/2, in double. */
+int mxk_h3_spatial_grid_host(int64_t dim, int64_t H, int64_t W, float* out_host);
+/* Time coordinate of each latent frame (src/models/minimax_h3/layout.cpp:90-97):
+ * ft[f] = T + sum_{g<f} (5/3) * {1,4,4,4,4}[g % 5], in double, returned as fp32. */
+int mxk_h3_frame_times_host(int64_t T, int64_t F_lat, float* out_host);
+/* Qwen-Image timestep embedding (src/models/qwen_image/dit.cpp:220-230): two rows (t and 0) of
+ * 256 values, cos half first, t and every value rounded through bf16. out_host fp32 [2, 256]. */
+int mxk_qwen_timestep_embedding_host(float t, float* out_host);
+/* The same embedding evaluated on the device: frequencies come from libm on the host, the
+ * angle is the same fp32 product, cos/sin are evaluated in fp64 and rounded to fp32 then bf16.
+ * out fp32 [2, 256] on the device. */
+int mxk_qwen_timestep_embedding(float t, float* out, mxk_stream_t stream);
+/* MiniMax-H3 time basis (src/models/minimax_h3/dit.cpp:166-179): linear interpolation in
+ * table fp32 [grid, basis] at pos = clamp(t, 0, 1) * (grid - 1); ts fp32 [nt] and table on the
+ * device, out fp32 [nt, basis].  Uses unfused multiply and add so the result is bit-identical
+ * to the host formula. */
+int mxk_h3_time_basis(const float* ts, int64_t nt, const float* table, int64_t grid, int64_t basis,
+                      float* out, mxk_stream_t stream);
+
+/* ---- call-pattern drivers ---------------------------------------------------------------
+ * The op sequence the reference's model graphs issue around each GEMM / attention call, with
+ * the GEMM and attention outputs supplied by the caller as ready-made device buffers. */
+
+typedef struct MxkBlockArgs {
+  /* Shapes: rows tokens; residual width dim; attention width inner = H * D; MLP width F. */
+  int64_t rows, dim, F;
+  int H, D;
+  int norm_mode; /* 0 LayerNorm (no affine), 1 RMSNorm */
+  float eps;
+  int act_mode;  /* 0: gelu_tanh_inplace on act [rows, F]; 1: silu_mul of act2 [rows, 2F] into act */
+  int fused;     /* 0: one launch per reference call; 1: the fused extensions where calls are adjacent */
+  int64_t chunk_rows; /* > 0: issue the sequence per chunk of this many rows (src/models/minimax_h3/dit.cpp:199) */
+  /* Modulation (each may have target == NULL) and RMSNorm weights (NULL = none). */
+  const float* norm1_w;
+  const float* norm2_w;
+  MxkRowMod shift1, scale1, gate1, shift2, scale2, gate2;
+  int gate_tanh;
+  /* q / k / v projections: head h of row s is X_in[s * qkv_stride + X_col0 + h * D ...]. v_in NULL = no v. */
+  const mxk_bf16* q_in;
+  const mxk_bf16* k_in;
+  const mxk_bf16* v_in;
+  int64_t qkv_stride, q_col0, k_col0, v_col0;
+  const float* norm_q; /* fp32 [D] */
+  const float* norm_k;
+  const float* cos; /* fp32 [rows, rot/2] */
+  const float* sin;
+  int rot, rope_mode;
+  mxk_bf16* q_out; /* bf16 [rows, H, D] */
+  mxk_bf16* k_out;
+  mxk_bf16* v_out;
+  /* Residual stream and the GEMM-side buffers. */
+  float* x;               /* fp32 [rows, dim], updated in place */
+  mxk_bf16* h1;           /* bf16 [rows, dim], first norm output (input of the QKV GEMM) */
+  mxk_bf16* h2;           /* bf16 [rows, dim], second norm output (input of the MLP GEMM); may equal h1 */
+  const mxk_bf16* attn_o; /* bf16 [rows, dim], stand-in for the attention out-projection */
+  mxk_bf16* act;          /* bf16 [rows, F] */
+  const mxk_bf16* act2;   /* bf16 [rows, 2F] when act_mode == 1 */
+  const mxk_bf16* mlp_o;  /* bf16 [rows, dim], stand-in for the MLP down-projection */
+} MxkBlockArgs;
+/* The fused-op sequence of one DiT block in the order of src/models/qwen_image/dit.cpp:265-314 and
+ * src/models/minimax_h3/dit.cpp:199-247: norm+mod, q/k(/v) head norm + rope, gated residual,
+ * norm+mod, activation, gated residual. */
+int mxk_dit_block_ops(const MxkBlockArgs* a, mxk_stream_t stream);
+
+/* Per-op device timing of one mxk_dit_block_ops pass: a CUDA event is recorded on the stream before
+ * the first op and after every op.  The handle owns 16 events (created here, not on the hot path). */
+typedef struct MxkOpTimes MxkOpTimes;
+int mxk_op_times_create(MxkOpTimes** out);
+void mxk_op_times_destroy(MxkOpTimes* t);
+/* Same launches as mxk_dit_block_ops (chunk_rows must be 0) with the events in between. */
+int mxk_dit_block_ops_timed(const MxkBlockArgs* a, mxk_stream_t stream, MxkOpTimes* t);
+/* Waits for the last event of the most recent timed pass and writes the milliseconds of each op, in
+ * launch order, to ms_host; returns the number of ops (>= 0) or a negative status. */
+int mxk_op_times_read(MxkOpTimes* t, float* ms_host, int cap);
+
+/* The same sequence with HOST buffers: rows are streamed through the GPU in chunks, the copies
+ * of one chunk overlapping the kernels of another on three internal streams owned by the handle.
+ * Host buffers should be pinned for the copies to overlap. */
+typedef struct MxkHostPipeline MxkHostPipeline;
+/* Allocates two sets of device staging buffers for chunks of chunk_rows rows (this is the one
+ * place the library allocates device memory; the handle owns it). with_v / act_mode mirror the args. */
+int mxk_host_pipeline_create(int64_t chunk_rows, int64_t dim, int64_t F, int H, int D, int rot,
+                             int with_v, int act_mode, MxkHostPipeline** out);
+void mxk_host_pipeline_destroy(MxkHostPipeline* p);
+/* `a` holds HOST pointers for x, h1, h2, q/k/v_in, q/k/v_out, attn_o, act, act2, mlp_o, cos, sin
+ * and DEVICE pointers for the modulation vectors and norm weights; q/k/v_in are read as separate
+ * [rows, H*D] arrays (qkv_stride and col0 as given apply to the host arrays).  Blocks until the
+ * results are back in host memory.  h2d_bytes / d2h_bytes (may be NULL) receive the bytes copied. */
+int mxk_dit_block_ops_host(MxkHostPipeline* p, const MxkBlockArgs* a, int64_t* h2d_bytes,
+                           int64_t* d2h_bytes);
+
+/* Development knob: overrides a launch-shape default (see tuning.h for the names); value 0
+ * restores the default.  Results do not depend on it. */
+int mxk_set_tuning(const char* name, int value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MXK_H_ */

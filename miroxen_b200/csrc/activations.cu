@@ -1,0 +1,154 @@
+// silu_mul, gelu_tanh_inplace, gelu_erf_inplace, silu_inplace_f32
+// (reference: src/kernels/ops.cu:121-128, 212-233, 244-246).
+#include "flat_map.cuh"
+
+namespace mxk {
+namespace {
+
+// 0.5 v (1 + tanh(u)), u = 0.7978845608 (v + 0.044715 v^3)  (src/kernels/ops.cu:222-224).
+// With e = exp(-2|u|) in (0, 1]:  1 + tanh(u) = 2 / (1 + e) for u >= 0 and 2 e / (1 + e) for
+// u < 0, so the value is v * (u >= 0 ? 1 : e) / (1 + e): one ex2 and one reciprocal, no
+// cancellation in the negative tail and no overflow.
+__device__ __forceinline__ float gelu_tanh_f(float v) {
+  const float u = 0.7978845608f * (v + 0.044715f * v * v * v);
+  const float e = __expf(-2.f * fabsf(u));
+  const float num = u >= 0.f ? v : v * e;
+  return __fdividef(num, 1.f + e);
+}
+
+__device__ __forceinline__ float gelu_erf_f(float v) {
+  return 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
+}
+
+// g / (1 + exp(-g))  (src/kernels/ops.cu:127)
+__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+
+template <int KIND>  // 0 gelu tanh, 1 gelu erf
+struct GeluOp {
+  static constexpr int VEC = 8;
+  using Frag = uint4;
+  bf16* x;
+  bool vector_ok() const { return aligned(x, 16); }
+  __device__ static float f(float v) { return KIND == 0 ? gelu_tanh_f(v) : gelu_erf_f(v); }
+  __device__ Frag load(int64_t vi) const { return ld_stream(reinterpret_cast<const uint4*>(x) + vi); }
+  __device__ void finish(int64_t vi, const Frag& r) const {
+    float v[8];
+    unpack8(r, v);
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = f(v[i]);
+    st_stream(reinterpret_cast<uint4*>(x) + vi, pack8(v));
+  }
+  __device__ void scalar(int64_t i) const { x[i] = __float2bfloat16(f(bf16_to_f(x[i]))); }
+};
+
+struct SiluF32Op {
+  static constexpr int VEC = 4;
+  using Frag = float4;
+  float* x;
+  bool vector_ok() const { return aligned(x, 16); }
+  __device__ static float f(float v) { return v / (1.f + __expf(-v)); }
+  __device__ Frag load(int64_t vi) const { return reinterpret_cast<const float4*>(x)[vi]; }
+  __device__ void finish(int64_t vi, const Frag& r) const {
+    reinterpret_cast<float4*>(x)[vi] = make_float4(f(r.x), f(r.y), f(r.z), f(r.w));
+  }
+  __device__ void scalar(int64_t i) const { x[i] = f(x[i]); }
+};
+
+constexpr int kActRowsInFlight = 4;
+
+// out[r, c] = silu(gu[r, c]) * gu[r, F + c]; each thread owns 8 columns and walks a strip of rows.
+__global__ void __launch_bounds__(256)
+    silu_mul_kernel(const bf16* __restrict__ gu, int64_t rows, int F, bf16* __restrict__ out,
+                    int rows_per_chunk) {
+  constexpr int U = kActRowsInFlight;
+  const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+  if (col >= F) return;
+  const int64_t nchunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
+  for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
+    const int64_t r0 = c * rows_per_chunk;
+    const int64_t r1 = r0 + rows_per_chunk < rows ? r0 + rows_per_chunk : rows;
+    for (int64_t r = r0; r < r1; r += U) {
+      uint4 g[U], u[U];
+#pragma unroll
+      for (int k = 0; k < U; k++) {
+        if (r + k < r1) {
+          const bf16* p = gu + (r + k) * 2 * F + col;
+          g[k] = ld_stream(reinterpret_cast<const uint4*>(p));
+          u[k] = ld_stream(reinterpret_cast<const uint4*>(p + F));
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < U; k++) {
+        if (r + k < r1) {
+          float a[8], b[8];
+          unpack8(g[k], a);
+          unpack8(u[k], b);
+#pragma unroll
+          for (int i = 0; i < 8; i++) a[i] = silu_f(a[i]) * b[i];
+          st_stream(reinterpret_cast<uint4*>(out + (r + k) * F + col), pack8(a));
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+    silu_mul_scalar_kernel(const bf16* __restrict__ gu, int64_t rows, int F, bf16* __restrict__ out) {
+  const int i = blockIdx.y * blockDim.x + threadIdx.x;
+  if (i >= F) return;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float g = bf16_to_f(gu[row * 2 * F + i]);
+    const float u = bf16_to_f(gu[row * 2 * F + F + i]);
+    out[row * F + i] = __float2bfloat16(silu_f(g) * u);
+  }
+}
+
+}  // namespace
+}  // namespace mxk
+
+using namespace mxk;
+
+extern "C" {
+
+int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk_stream_t stream) {
+  if (rows <= 0 || F <= 0) return MXK_OK;
+  if (!gu || !out) return fail(MXK_ERR_INVALID_ARG, "silu_mul: null gu or out");
+  if (F > (int64_t(1) << 29)) return fail(MXK_ERR_INVALID_ARG, "silu_mul: F=%lld out of range", (long long)F);
+  cudaStream_t s = as_stream(stream);
+  const bf16* in = reinterpret_cast<const bf16*>(gu);
+  bf16* o = reinterpret_cast<bf16*>(out);
+  if (F % 8 == 0 && aligned(gu, 16) && aligned(out, 16)) {
+    const int threads = 256;
+    const int rpc = tune(TUNE_ACT_ROWS_PER_CTA, 4);
+    const unsigned gy = unsigned(ceil_div(F / 8, threads));
+    const int64_t nchunks = ceil_div(rows, rpc);
+    int64_t gx = ceil_div(int64_t(sm_count()) * 16, gy);
+    if (gx > nchunks) gx = nchunks;
+    silu_mul_kernel<<<dim3(unsigned(gx), gy), threads, 0, s>>>(in, rows, int(F), o, rpc);
+  } else {
+    const unsigned gy = unsigned(ceil_div(F, 256));
+    int64_t gx = rows < int64_t(sm_count()) * 16 ? rows : int64_t(sm_count()) * 16;
+    silu_mul_scalar_kernel<<<dim3(unsigned(gx), gy), 256, 0, s>>>(in, rows, int(F), o);
+  }
+  return after_launch("silu_mul");
+}
+
+int mxk_gelu_tanh_inplace(mxk_bf16* x, int64_t n, mxk_stream_t stream) {
+  if (n <= 0) return MXK_OK;
+  if (!x) return fail(MXK_ERR_INVALID_ARG, "gelu_tanh_inplace: null x");
+  return run_flat("gelu_tanh_inplace", n, GeluOp<0>{reinterpret_cast<bf16*>(x)}, as_stream(stream));
+}
+
+int mxk_gelu_erf_inplace(mxk_bf16* x, int64_t n, mxk_stream_t stream) {
+  if (n <= 0) return MXK_OK;
+  if (!x) return fail(MXK_ERR_INVALID_ARG, "gelu_erf_inplace: null x");
+  return run_flat("gelu_erf_inplace", n, GeluOp<1>{reinterpret_cast<bf16*>(x)}, as_stream(stream));
+}
+
+int mxk_silu_inplace_f32(float* x, int64_t n, mxk_stream_t stream) {
+  if (n <= 0) return MXK_OK;
+  if (!x) return fail(MXK_ERR_INVALID_ARG, "silu_inplace_f32: null x");
+  return run_flat("silu_inplace_f32", n, SiluF32Op{x}, as_stream(stream));
+}
+
+}  // extern "C"

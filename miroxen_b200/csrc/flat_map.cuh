@@ -1,0 +1,72 @@
+// Flat elementwise framework: n contiguous elements processed in 16-byte (or wider) vectors,
+// UNROLL independent vectors per thread so that several loads are in flight before the first
+// store.  An op is a struct with
+//   static constexpr int VEC;                 elements per vector
+//   using Frag = ...;                          what load() brings into registers
+//   bool vector_ok() const;                    pointers aligned for the vector accesses
+//   __device__ Frag load(int64_t vi) const;    vector vi covers elements [vi*VEC, vi*VEC + VEC)
+//   __device__ void finish(int64_t vi, const Frag&) const;   compute + store
+//   __device__ void scalar(int64_t i) const;   one element, used for the tail and as fallback
+#pragma once
+
+#include "common.cuh"
+#include "tuning.h"
+
+namespace mxk {
+
+template <int UNROLL, class Op>
+__global__ void __launch_bounds__(512) flat_vec_kernel(int64_t n, Op op) {
+  const int64_t nvec = n / Op::VEC;
+  const int T = blockDim.x;
+  const int64_t tile = int64_t(T) * UNROLL;
+  for (int64_t base = blockIdx.x * tile; base < nvec; base += gridDim.x * tile) {
+    typename Op::Frag f[UNROLL];
+#pragma unroll
+    for (int u = 0; u < UNROLL; u++) {
+      const int64_t vi = base + u * T + threadIdx.x;
+      if (vi < nvec) f[u] = op.load(vi);
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; u++) {
+      const int64_t vi = base + u * T + threadIdx.x;
+      if (vi < nvec) op.finish(vi, f[u]);
+    }
+  }
+  if (blockIdx.x == 0) {
+    const int64_t i = nvec * Op::VEC + threadIdx.x;
+    if (i < n) op.scalar(i);  // fewer than VEC (<= 8) leftover elements
+  }
+}
+
+template <class Op>
+__global__ void __launch_bounds__(256) flat_scalar_kernel(int64_t n, Op op) {
+  for (int64_t i = int64_t(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += int64_t(gridDim.x) * blockDim.x)
+    op.scalar(i);
+}
+
+template <class Op>
+inline int run_flat(const char* name, int64_t n, const Op& op, cudaStream_t s) {
+  if (n <= 0) return MXK_OK;
+  const int64_t cap = int64_t(sm_count()) * 16;
+  if (op.vector_ok() && n >= Op::VEC) {
+    const int threads = tune(TUNE_EW_THREADS, 256);
+    const int unroll = tune(TUNE_EW_UNROLL, 4);
+    const int64_t nvec = n / Op::VEC;
+    int64_t grid = ceil_div(nvec, int64_t(threads) * unroll);
+    if (grid > cap) grid = cap;
+    switch (unroll) {
+      case 1: flat_vec_kernel<1, Op><<<unsigned(grid), threads, 0, s>>>(n, op); break;
+      case 2: flat_vec_kernel<2, Op><<<unsigned(grid), threads, 0, s>>>(n, op); break;
+      case 8: flat_vec_kernel<8, Op><<<unsigned(grid), threads, 0, s>>>(n, op); break;
+      default: flat_vec_kernel<4, Op><<<unsigned(grid), threads, 0, s>>>(n, op); break;
+    }
+  } else {
+    int64_t grid = ceil_div(n, 256);
+    if (grid > cap) grid = cap;
+    flat_scalar_kernel<Op><<<unsigned(grid), 256, 0, s>>>(n, op);
+  }
+  return after_launch(name);
+}
+
+}  // namespace mxk

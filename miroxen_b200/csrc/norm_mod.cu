@@ -1,0 +1,49 @@
+// layernorm_mod / rmsnorm_mod / rmsnorm_bf16 launchers (reference: src/kernels/ops.cu:153-175).
+#include "norm_dispatch.cuh"
+
+using namespace mxk;
+
+namespace {
+NormArgs make_args(const void* x, int64_t rows, int64_t dim, float eps, const float* w,
+                   MxkRowMod scale, MxkRowMod shift, mxk_bf16* out) {
+  NormArgs a{};
+  a.x = x;
+  a.rows = rows;
+  a.dim = int(dim);
+  a.nvec = int(dim / 4);
+  a.eps = eps;
+  a.w = w;
+  a.scale = scale;
+  a.shift = shift;
+  a.out = reinterpret_cast<bf16*>(out);
+  return a;
+}
+}  // namespace
+
+extern "C" {
+
+int mxk_layernorm_mod(const float* x, int64_t rows, int64_t dim, float eps, MxkRowMod scale,
+                      MxkRowMod shift, mxk_bf16* out, mxk_stream_t stream) {
+  if (rows <= 0) return MXK_OK;
+  if (int rc = check_norm_common("layernorm_mod", x, rows, dim, out, scale, shift)) return rc;
+  return run_norm<0, float, false>("layernorm_mod", make_args(x, rows, dim, eps, nullptr, scale, shift, out),
+                                   as_stream(stream));
+}
+
+int mxk_rmsnorm_mod(const float* x, int64_t rows, int64_t dim, float eps, const float* w,
+                    MxkRowMod scale, MxkRowMod shift, mxk_bf16* out, mxk_stream_t stream) {
+  if (rows <= 0) return MXK_OK;
+  if (int rc = check_norm_common("rmsnorm_mod", x, rows, dim, out, scale, shift)) return rc;
+  return run_norm<1, float, false>("rmsnorm_mod", make_args(x, rows, dim, eps, w, scale, shift, out),
+                                   as_stream(stream));
+}
+
+int mxk_rmsnorm_bf16(const mxk_bf16* x, int64_t rows, int64_t dim, float eps, const float* w,
+                     mxk_bf16* out, mxk_stream_t stream) {
+  if (rows <= 0) return MXK_OK;
+  if (int rc = check_norm_common("rmsnorm_bf16", x, rows, dim, out, MxkRowMod{}, MxkRowMod{})) return rc;
+  return run_norm<1, bf16, false>("rmsnorm_bf16", make_args(x, rows, dim, eps, w, MxkRowMod{}, MxkRowMod{}, out),
+                                  as_stream(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,249 @@
+// Row-normalisation kernels: LayerNorm / RMSNorm + modulation + bf16 cast, optionally preceded
+// by the gated residual update of the same row.
+//
+// Behaviour follows the reference's norm_mod_kernel (src/kernels/ops.cu:43-71) and
+// gated_residual_kernel (src/kernels/ops.cu:73-84): mean, then sum of squared deviations (two
+// passes over the row's values), rstd = rsqrtf(sum / dim + eps), then in this order
+// normalise -> * w -> * (1 + scale) -> + shift -> round to bf16.
+//
+// Layout of the work: one CTA walks a contiguous range of rows.  Thread t of a T-thread CTA owns
+// the 4-element column groups t, t + T, ... (VPT of them), the same for every row, so the
+// modulation values of those columns live in registers for the whole range and the row itself
+// is read from HBM exactly once into registers; mean and variance come from those registers.
+#pragma once
+
+#include "common.cuh"
+
+namespace mxk {
+
+constexpr int kNormMaxVpt = 8;
+
+struct NormArgs {
+  const void* x;   // fp32 or bf16 [rows, dim]
+  float* xw;       // fused residual: updated x is written here (== x)
+  const bf16* y;   // fused residual: bf16 [rows, dim]
+  MxkRowMod gate;  // fused residual
+  int gate_tanh;
+  int64_t rows;
+  int dim;
+  int nvec;  // dim / 4
+  float eps;
+  const float* w;
+  MxkRowMod scale, shift;
+  bf16* out;
+  int rows_per_cta;
+};
+
+// Sum over the CTA; `red` is a 16-float scratch that must not be reused before the next
+// __syncthreads() of the caller's control flow (callers alternate two scratch arrays).
+__device__ __forceinline__ float cta_sum(float v, float* red, int nwarps) {
+  v = warp_sum(v);
+  if (nwarps == 1) return v;
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = red[0];
+  for (int i = 1; i < nwarps; i++) t += red[i];
+  return t;
+}
+
+// Raw 4-element vector as it sits in memory.
+template <class TIN> struct Raw4;
+template <> struct Raw4<float> { using type = float4; };
+template <> struct Raw4<bf16> { using type = uint2; };
+__device__ __forceinline__ float4 widen(const float4& v) { return v; }
+__device__ __forceinline__ float4 widen(const uint2& v) {
+  return make_float4(bf16_lo(v.x), bf16_hi(v.x), bf16_lo(v.y), bf16_hi(v.y));
+}
+
+// CTA sizes the vector kernel may be launched with, by vectors per thread: the wide variants
+// need more than 128 registers per thread, which a 512-thread CTA cannot have.
+__host__ __device__ constexpr int norm_max_threads(int vpt) { return vpt <= 4 ? 512 : 256; }
+
+// MODE 0 = LayerNorm, 1 = RMSNorm.  EXACT: blockDim.x * VPT == nvec (no column predicate).
+// The loads of row r + 1 are issued before the reductions of row r, so that each CTA keeps two
+// rows in flight.
+template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool EXACT>
+__global__ void __launch_bounds__(norm_max_threads(VPT))
+    norm_rows_kernel(const NormArgs a) {
+  using raw_t = typename Raw4<TIN>::type;
+  __shared__ float red[2][16];
+  const int tid = threadIdx.x, T = blockDim.x, nwarps = T >> 5;
+  const int64_t r0 = int64_t(blockIdx.x) * a.rows_per_cta;
+  const int64_t r1 = r0 + a.rows_per_cta < a.rows ? r0 + a.rows_per_cta : a.rows;
+  const TIN* x = static_cast<const TIN*>(a.x);
+  const float fdim = float(a.dim);
+
+  bool on[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; k++) on[k] = EXACT || (k * T + tid < a.nvec);
+
+  // Modulation of this thread's columns: A = 1 + scale, B = shift, W = w, G = act(gate).
+  float4 A[VPT], B[VPT], W[HAS_W ? VPT : 1], G[FUSE_RES ? VPT : 1];
+  int cur_set = -1;
+#pragma unroll
+  for (int k = 0; k < VPT; k++) {
+    if (HAS_W) W[k] = on[k] ? *reinterpret_cast<const float4*>(a.w + 4 * (k * T + tid))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  raw_t xn[VPT];
+  uint2 yn[FUSE_RES ? VPT : 1];
+  auto fetch = [&](int64_t row) {
+    const TIN* xr = x + row * a.dim;
+#pragma unroll
+    for (int k = 0; k < VPT; k++)
+      if (on[k]) xn[k] = ld_stream(reinterpret_cast<const raw_t*>(xr + 4 * (k * T + tid)));
+    if (FUSE_RES) {
+      const bf16* yr = a.y + row * a.dim;
+#pragma unroll
+      for (int k = 0; k < VPT; k++)
+        if (on[k]) yn[k] = ld_stream(reinterpret_cast<const uint2*>(yr + 4 * (k * T + tid)));
+    }
+  };
+#pragma unroll
+  for (int k = 0; k < VPT; k++) {
+    if constexpr (sizeof(TIN) == 4) xn[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    else xn[k] = make_uint2(0u, 0u);
+    if (FUSE_RES) yn[k] = make_uint2(0u, 0u);
+  }
+  if (r0 < r1) fetch(r0);
+
+  int parity = 0;
+  for (int64_t row = r0; row < r1; row++) {
+    const int set = (row < a.scale.prefix_len ? 1 : 0) | (row < a.shift.prefix_len ? 2 : 0) |
+                    (FUSE_RES && row < a.gate.prefix_len ? 4 : 0);
+    if (set != cur_set) {
+      cur_set = set;
+      const float* sc = a.scale.target ? pick(a.scale, row) : nullptr;
+      const float* sh = a.shift.target ? pick(a.shift, row) : nullptr;
+      const float* gt = FUSE_RES && a.gate.target ? pick(a.gate, row) : nullptr;
+#pragma unroll
+      for (int k = 0; k < VPT; k++) {
+        const int c = 4 * (k * T + tid);
+        // An absent scale multiplies by 1; an absent shift adds -0, which leaves every value,
+        // signed zeros included, as it was.
+        A[k] = make_float4(1.f, 1.f, 1.f, 1.f);
+        B[k] = make_float4(-0.f, -0.f, -0.f, -0.f);
+        if (on[k]) {
+          if (sc) {
+            float4 v = *reinterpret_cast<const float4*>(sc + c);
+            A[k] = make_float4(1.f + v.x, 1.f + v.y, 1.f + v.z, 1.f + v.w);
+          }
+          if (sh) B[k] = *reinterpret_cast<const float4*>(sh + c);
+        }
+        if (FUSE_RES) {
+          G[k] = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (gt && on[k]) {
+            float4 g = *reinterpret_cast<const float4*>(gt + c);
+            G[k] = a.gate_tanh ? make_float4(tanhf(g.x), tanhf(g.y), tanhf(g.z), tanhf(g.w)) : g;
+          }
+        }
+      }
+    }
+
+    float4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) v[k] = widen(xn[k]);
+    if (FUSE_RES) {
+      float* xo = a.xw + row * a.dim;
+#pragma unroll
+      for (int k = 0; k < VPT; k++) {
+        float4 yv = widen(yn[k]);
+        v[k].x += yv.x * G[k].x;
+        v[k].y += yv.y * G[k].y;
+        v[k].z += yv.z * G[k].z;
+        v[k].w += yv.w * G[k].w;
+        if (on[k]) st_stream(reinterpret_cast<float4*>(xo + 4 * (k * T + tid)), v[k]);
+      }
+    }
+    if (row + 1 < r1) fetch(row + 1);
+
+    float mean = 0.f;
+    if (MODE == 0) {
+      float s = 0.f;
+#pragma unroll
+      for (int k = 0; k < VPT; k++) s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+      mean = cta_sum(s, red[0], nwarps) / fdim;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+      // Padding lanes hold zeros; in LayerNorm mode their deviation would be -mean, so they
+      // are masked out of the sum of squares.
+      float dx = v[k].x - mean, dy = v[k].y - mean, dz = v[k].z - mean, dw = v[k].w - mean;
+      float q = (dx * dx + dy * dy) + (dz * dz + dw * dw);
+      ss += (EXACT || MODE == 1 || on[k]) ? q : 0.f;
+    }
+    const float rstd = rsqrtf(cta_sum(ss, red[MODE == 0 ? 1 : parity], nwarps) / fdim + a.eps);
+    parity ^= 1;
+
+    bf16* orow = a.out + row * a.dim;
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+      float o[4] = {(v[k].x - mean) * rstd, (v[k].y - mean) * rstd, (v[k].z - mean) * rstd,
+                    (v[k].w - mean) * rstd};
+      if (HAS_W) o[0] *= W[k].x, o[1] *= W[k].y, o[2] *= W[k].z, o[3] *= W[k].w;
+      o[0] = o[0] * A[k].x + B[k].x;
+      o[1] = o[1] * A[k].y + B[k].y;
+      o[2] = o[2] * A[k].z + B[k].z;
+      o[3] = o[3] * A[k].w + B[k].w;
+      if (on[k]) st_stream(reinterpret_cast<uint2*>(orow + 4 * (k * T + tid)), pack4(o));
+    }
+  }
+}
+
+// Any dim, any alignment: one CTA per row, three sweeps over the row (the later sweeps hit L1/L2).
+template <int MODE, class TIN, bool FUSE_RES>
+__global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a) {
+  __shared__ float red[2][16];
+  const int tid = threadIdx.x, T = blockDim.x, nwarps = T >> 5;
+  const int64_t row = blockIdx.x;
+  const TIN* xr = static_cast<const TIN*>(a.x) + row * a.dim;
+  const float fdim = float(a.dim);
+  auto ldx = [&](int i) -> float {
+    if constexpr (sizeof(TIN) == 4) return xr[i];
+    else return bf16_to_f(xr[i]);
+  };
+  if (FUSE_RES) {
+    const float* gt = a.gate.target ? pick(a.gate, row) : nullptr;
+    const bf16* yr = a.y + row * a.dim;
+    float* xo = a.xw + row * a.dim;
+    for (int i = tid; i < a.dim; i += T) {
+      float v = bf16_to_f(yr[i]);
+      if (gt) v *= a.gate_tanh ? tanhf(gt[i]) : gt[i];
+      xo[i] = ldx(i) + v;  // the same thread re-reads this element in the sweeps below
+    }
+  }
+  float mean = 0.f;
+  if (MODE == 0) {
+    float s = 0.f;
+    for (int i = tid; i < a.dim; i += T) s += ldx(i);
+    mean = cta_sum(s, red[0], nwarps) / fdim;
+  }
+  float ss = 0.f;
+  for (int i = tid; i < a.dim; i += T) {
+    float d = ldx(i) - mean;
+    ss += d * d;
+  }
+  const float rstd = rsqrtf(cta_sum(ss, red[1], nwarps) / fdim + a.eps);
+  const float* sc = a.scale.target ? pick(a.scale, row) : nullptr;
+  const float* sh = a.shift.target ? pick(a.shift, row) : nullptr;
+  bf16* orow = a.out + row * a.dim;
+  for (int i = tid; i < a.dim; i += T) {
+    float v = (ldx(i) - mean) * rstd;
+    if (a.w) v *= a.w[i];
+    if (sc) v *= 1.f + sc[i];
+    if (sh) v += sh[i];
+    orow[i] = __float2bfloat16(v);
+  }
+}
+
+// Launch plan shared by every instantiation: threads per CTA, vectors per thread, grid.
+struct NormPlan {
+  int threads, vpt;
+  bool exact;
+  int rows_per_cta;
+  unsigned grid;
+};
+
+}  // namespace mxk

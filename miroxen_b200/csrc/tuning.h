@@ -1,0 +1,23 @@
+// Launch-shape knobs.  Each has a built-in default chosen from measurements on B200; a value set
+// through mxk_set_tuning() overrides it process-wide (0 restores the default).  They change how
+// the work is tiled, never the results.
+#pragma once
+
+namespace mxk {
+
+enum TuneKey {
+  TUNE_NORM_THREADS = 0,   // preferred CTA size of the row-norm kernels
+  TUNE_NORM_CTAS_PER_SM,   // CTAs per SM the row-norm grid is sized for
+  TUNE_ROPE_THREADS,       // CTA size of head_norm_rope
+  TUNE_ROPE_CTAS_PER_SM,
+  TUNE_RES_ROWS_PER_CTA,   // rows each gated_residual CTA walks
+  TUNE_RES_THREADS,
+  TUNE_EW_THREADS,         // CTA size of the flat elementwise kernels
+  TUNE_EW_UNROLL,          // independent 16-byte vectors per thread (1, 2, 4 or 8)
+  TUNE_ACT_ROWS_PER_CTA,   // rows each silu_mul CTA walks
+  TUNE_COUNT
+};
+
+int tune(int key, int dflt);
+
+}  // namespace mxk

@@ -1,0 +1,212 @@
+"""Python host mirror of the reference's launcher API (src/kernels/ops.h:18-61) over libmxk.
+
+Same names, argument order and meaning as the reference's `namespace mx` functions; tensors are
+torch CUDA tensors (bf16 tensors are torch.bfloat16), the stream defaults to torch's current
+stream.  Every function launches asynchronously and raises MxkError on a non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib
+from ._lib import BlockArgs, HeadTensor, RopeRun, RowMod, check, lib
+
+ROPE_NONE, ROPE_INTERLEAVED, ROPE_HALF = 0, 1, 2
+
+__all__ = [
+    "ROPE_NONE", "ROPE_INTERLEAVED", "ROPE_HALF", "row_mod", "layernorm_mod", "rmsnorm_mod", "rmsnorm_bf16",
+    "gated_residual", "add_inplace_bf16", "head_norm_rope", "silu_mul", "gelu_tanh_inplace", "gelu_erf_inplace",
+    "scatter_rows", "silu_inplace_f32", "add_bias_bf16", "add_bias_f32", "f32_to_bf16", "bf16_to_f32", "axpy_f32",
+    "axpby_f32", "gated_residual_norm", "qkv_norm_rope", "HeadSpec", "dit_block_ops", "BlockArgs", "RowMod",
+    "HostPipeline", "OpTimes", "launch_count", "reset_launch_count", "set_tuning",
+]
+
+
+def _p(t) -> Optional[int]:
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+def _stream(stream) -> Optional[int]:
+    if stream is None:
+        return torch.cuda.current_stream().cuda_stream or None
+    if isinstance(stream, int):
+        return stream or None
+    return stream.cuda_stream or None
+
+
+def row_mod(target=None, prefix=None, prefix_len: int = 0) -> RowMod:
+    """RowMod{target, prefix, prefix_len}; with one vector set pass it as `target` only."""
+    if target is not None and prefix is None:
+        prefix = target
+    return RowMod(_p(target), _p(prefix), int(prefix_len))
+
+
+_NONE = RowMod(None, None, 0)
+
+
+def layernorm_mod(x, rows, dim, eps, scale: RowMod, shift: RowMod, out, stream=None):
+    check(lib().mxk_layernorm_mod(_p(x), rows, dim, eps, scale or _NONE, shift or _NONE, _p(out), _stream(stream)))
+
+
+def rmsnorm_mod(x, rows, dim, eps, w, scale: RowMod, shift: RowMod, out, stream=None):
+    check(lib().mxk_rmsnorm_mod(_p(x), rows, dim, eps, _p(w), scale or _NONE, shift or _NONE, _p(out), _stream(stream)))
+
+
+def rmsnorm_bf16(x, rows, dim, eps, w, out, stream=None):
+    check(lib().mxk_rmsnorm_bf16(_p(x), rows, dim, eps, _p(w), _p(out), _stream(stream)))
+
+
+def gated_residual(x, y, rows, dim, gate: RowMod, gate_tanh, stream=None):
+    check(lib().mxk_gated_residual(_p(x), _p(y), rows, dim, gate or _NONE, int(gate_tanh), _stream(stream)))
+
+
+def add_inplace_bf16(x, y, n, stream=None):
+    check(lib().mxk_add_inplace_bf16(_p(x), _p(y), n, _stream(stream)))
+
+
+def head_norm_rope(in_, S, in_stride, col0, H, D, norm_w, eps, cos, sin, rot, mode, out, stream=None):
+    check(lib().mxk_head_norm_rope(_p(in_), S, in_stride, col0, H, D, _p(norm_w), eps, _p(cos), _p(sin), rot, mode,
+                                   _p(out), _stream(stream)))
+
+
+def silu_mul(gu, rows, F, out, stream=None):
+    check(lib().mxk_silu_mul(_p(gu), rows, F, _p(out), _stream(stream)))
+
+
+def gelu_tanh_inplace(x, n, stream=None):
+    check(lib().mxk_gelu_tanh_inplace(_p(x), n, _stream(stream)))
+
+
+def gelu_erf_inplace(x, n, stream=None):
+    check(lib().mxk_gelu_erf_inplace(_p(x), n, _stream(stream)))
+
+
+def scatter_rows(x, dim, rows, src, n, add, stream=None):
+    check(lib().mxk_scatter_rows(_p(x), dim, _p(rows), _p(src), n, int(add), _stream(stream)))
+
+
+def silu_inplace_f32(x, n, stream=None):
+    check(lib().mxk_silu_inplace_f32(_p(x), n, _stream(stream)))
+
+
+def add_bias_bf16(y, bias, rows, dim, stream=None):
+    check(lib().mxk_add_bias_bf16(_p(y), _p(bias), rows, dim, _stream(stream)))
+
+
+def add_bias_f32(y, bias, rows, dim, stream=None):
+    check(lib().mxk_add_bias_f32(_p(y), _p(bias), rows, dim, _stream(stream)))
+
+
+def f32_to_bf16(x, y, n, stream=None):
+    check(lib().mxk_f32_to_bf16(_p(x), _p(y), n, _stream(stream)))
+
+
+def bf16_to_f32(x, y, n, stream=None):
+    check(lib().mxk_bf16_to_f32(_p(x), _p(y), n, _stream(stream)))
+
+
+def axpy_f32(x, y, a, n, stream=None):
+    check(lib().mxk_axpy_f32(_p(x), _p(y), a, n, _stream(stream)))
+
+
+def axpby_f32(x, y, a, b, n, stream=None):
+    check(lib().mxk_axpby_f32(_p(x), _p(y), a, b, n, _stream(stream)))
+
+
+# ---- fused extensions -------------------------------------------------------------------------
+
+def gated_residual_norm(x, y, rows, dim, gate: RowMod, gate_tanh, norm_mode, eps, w, scale: RowMod, shift: RowMod, out,
+                        stream=None):
+    """gated_residual followed by layernorm_mod (norm_mode 0) / rmsnorm_mod (1) on the same rows."""
+    check(lib().mxk_gated_residual_norm(_p(x), _p(y), rows, dim, gate or _NONE, int(gate_tanh), norm_mode, eps, _p(w),
+                                        scale or _NONE, shift or _NONE, _p(out), _stream(stream)))
+
+
+@dataclass
+class HeadSpec:
+    """One tensor of a qkv_norm_rope launch (the per-tensor arguments of head_norm_rope)."""
+    in_: object
+    in_stride: int
+    col0: int
+    norm_w: object
+    out: object
+    rot: int
+    mode: int
+
+
+def qkv_norm_rope(tensors: Sequence[HeadSpec], S, H, D, eps, cos, sin, stream=None):
+    arr = (HeadTensor * len(tensors))(*[
+        HeadTensor(_p(t.in_), t.in_stride, t.col0, _p(t.norm_w), _p(t.out), t.rot, t.mode) for t in tensors])
+    check(lib().mxk_qkv_norm_rope(arr, len(tensors), S, H, D, eps, _p(cos), _p(sin), _stream(stream)))
+
+
+def dit_block_ops(args: BlockArgs, stream=None):
+    """The op sequence of one DiT block (see MxkBlockArgs in include/mxk.h)."""
+    check(lib().mxk_dit_block_ops(C.byref(args), _stream(stream)))
+
+
+class OpTimes:
+    """mxk_op_times_*: per-op CUDA-event timing of a block pass."""
+
+    def __init__(self):
+        self._h = C.c_void_p()
+        check(lib().mxk_op_times_create(C.byref(self._h)))
+
+    def run(self, args: BlockArgs, stream=None):
+        check(lib().mxk_dit_block_ops_timed(C.byref(args), _stream(stream), self._h))
+
+    def read(self):
+        buf = (C.c_float * 16)()
+        n = lib().mxk_op_times_read(self._h, buf, 16)
+        if n < 0:
+            check(n)
+        return [buf[i] for i in range(n)]
+
+    def close(self):
+        if self._h:
+            lib().mxk_op_times_destroy(self._h)
+            self._h = C.c_void_p()
+
+
+class HostPipeline:
+    """mxk_host_pipeline_*: the block sequence on HOST buffers, streamed through the GPU in row chunks."""
+
+    def __init__(self, chunk_rows, dim, F, H, D, rot, with_v=False, act_mode=0):
+        self._h = C.c_void_p()
+        check(lib().mxk_host_pipeline_create(chunk_rows, dim, F, H, D, rot, int(with_v), act_mode, C.byref(self._h)))
+
+    def run(self, args: BlockArgs):
+        up, down = C.c_int64(0), C.c_int64(0)
+        check(lib().mxk_dit_block_ops_host(self._h, C.byref(args), C.byref(up), C.byref(down)))
+        return up.value, down.value
+
+    def close(self):
+        if self._h:
+            lib().mxk_host_pipeline_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+def launch_count() -> int:
+    return lib().mxk_launch_count()
+
+
+def reset_launch_count() -> None:
+    lib().mxk_reset_launch_count()
+
+
+def set_tuning(name: str, value: int) -> None:
+    check(lib().mxk_set_tuning(name.encode(), value))

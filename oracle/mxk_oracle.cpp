@@ -1,0 +1,415 @@
+// CPU ORACLE - TEST INFRASTRUCTURE ONLY.  Nothing in the product (miroxen_b200/, include/) may
+// call, link or import this file; it exists so that the tests, the smoke check and the CPU-baseline
+// leg of the benchmark have an independent statement of what the reference computes.
+//
+// It restates, in plain fp32 C++ (no FMA contraction, libm for every transcendental), the
+// algorithm of the reference's fused layer ops (src/kernels/ops.cu) and of its host-side table
+// builders (src/models/qwen_image/dit.cpp, src/models/minimax_h3/dit.cpp, layout.cpp); each
+// function cites the lines it follows.  Where the reference reduces over a CUDA block, the same
+// association order is used: per-thread strided partial sums, an xor-butterfly inside each warp,
+// then a butterfly over the per-warp totals (src/kernels/ops.cu:8-30).
+//
+// Pinning: the reference holds no unit test, golden vector or CPU implementation for these ops
+// (its only checks are whole-model comparisons that need checkpoints).  The oracle is pinned
+// against outputs of the reference's own kernels - src/kernels/ops.cu compiled unmodified for
+// sm_100a (oracle/Makefile, target _ref) and run on a B200 - stored under tests/golden/.  The
+// table builders have no runnable counterpart outside the reference's model classes: for them
+// parity is unpinned beyond the closed-form spot checks in the tests.
+#include <algorithm>
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <thread>
+#include <vector>
+
+namespace {
+
+int g_threads = 1;
+
+inline float bf2f(uint16_t b) {
+  uint32_t u = uint32_t(b) << 16;
+  float f;
+  memcpy(&f, &u, 4);
+  return f;
+}
+// round-to-nearest-even, as __float2bfloat16
+inline uint16_t f2bf(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return 0x7fff;
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return uint16_t(u >> 16);
+}
+inline float round_bf16(float v) { return bf2f(f2bf(v)); }
+
+template <class F>
+void parallel_rows(int64_t rows, F f) {
+  int nt = int(std::min<int64_t>(g_threads, rows));
+  if (nt <= 1) {
+    f(0, rows);
+    return;
+  }
+  std::vector<std::thread> th;
+  int64_t per = (rows + nt - 1) / nt;
+  for (int t = 0; t < nt; t++) {
+    int64_t a = t * per, b = std::min(rows, a + per);
+    if (a < b) th.emplace_back([=] { f(a, b); });
+  }
+  for (auto& t : th) t.join();
+}
+
+// block_sum of src/kernels/ops.cu:14-30 for a block of `threads` threads (multiple of 32).
+float block_sum(const float* partial, int threads) {
+  const int nw = threads / 32;
+  float tot[32];
+  for (int w = 0; w < 32; w++) tot[w] = 0.f;
+  for (int w = 0; w < nw; w++) {
+    float v[32], n[32];
+    for (int l = 0; l < 32; l++) v[l] = partial[w * 32 + l];
+    for (int o = 16; o > 0; o >>= 1) {
+      for (int l = 0; l < 32; l++) n[l] = v[l] + v[l ^ o];
+      memcpy(v, n, sizeof(v));
+    }
+    tot[w] = v[0];
+  }
+  float v[32], n[32];
+  memcpy(v, tot, sizeof(v));
+  for (int o = 16; o > 0; o >>= 1) {
+    for (int l = 0; l < 32; l++) n[l] = v[l] + v[l ^ o];
+    memcpy(v, n, sizeof(v));
+  }
+  return v[0];
+}
+
+struct RowMod {
+  const float* target;
+  const float* prefix;
+  int64_t prefix_len;
+};
+inline const float* pick(const RowMod& m, int64_t row) { return row < m.prefix_len ? m.prefix : m.target; }
+
+// norm_mod_kernel, src/kernels/ops.cu:43-71.  MODE 0 LayerNorm, 1 RMSNorm; 256 threads.
+template <int MODE, bool BF16_IN>
+void norm_mod(const void* xin, int64_t rows, int64_t dim, float eps, const float* w, RowMod scale, RowMod shift,
+              uint16_t* out) {
+  parallel_rows(rows, [=](int64_t a, int64_t b) {
+    std::vector<float> xr(dim);
+    for (int64_t row = a; row < b; row++) {
+      if (BF16_IN) {
+        const uint16_t* p = static_cast<const uint16_t*>(xin) + row * dim;
+        for (int64_t i = 0; i < dim; i++) xr[i] = bf2f(p[i]);
+      } else {
+        memcpy(xr.data(), static_cast<const float*>(xin) + row * dim, dim * 4);
+      }
+      float part[256];
+      float mean = 0.f;
+      if (MODE == 0) {
+        for (int t = 0; t < 256; t++) part[t] = 0.f;
+        for (int64_t i = 0; i < dim; i++) part[i & 255] += xr[i];
+        mean = block_sum(part, 256) / float(dim);
+      }
+      for (int t = 0; t < 256; t++) part[t] = 0.f;
+      for (int64_t i = 0; i < dim; i++) {
+        float d = xr[i] - mean;
+        part[i & 255] += d * d;
+      }
+      const float rstd = 1.0f / std::sqrt(block_sum(part, 256) / float(dim) + eps);
+      const float* sc = scale.target ? pick(scale, row) : nullptr;
+      const float* sh = shift.target ? pick(shift, row) : nullptr;
+      uint16_t* orow = out + row * dim;
+      for (int64_t i = 0; i < dim; i++) {
+        float v = (xr[i] - mean) * rstd;
+        if (w) v *= w[i];
+        if (sc) v *= 1.f + sc[i];
+        if (sh) v += sh[i];
+        orow[i] = f2bf(v);
+      }
+    }
+  });
+}
+
+}  // namespace
+
+extern "C" {
+
+void or_set_threads(int n) { g_threads = n < 1 ? 1 : n; }
+int or_get_threads() { return g_threads; }
+
+// src/kernels/ops.cu:153-159
+void or_layernorm_mod(const float* x, int64_t rows, int64_t dim, float eps, RowMod scale, RowMod shift, uint16_t* out) {
+  if (rows <= 0) return;
+  norm_mod<0, false>(x, rows, dim, eps, nullptr, scale, shift, out);
+}
+// src/kernels/ops.cu:161-167
+void or_rmsnorm_mod(const float* x, int64_t rows, int64_t dim, float eps, const float* w, RowMod scale, RowMod shift,
+                    uint16_t* out) {
+  if (rows <= 0) return;
+  norm_mod<1, false>(x, rows, dim, eps, w, scale, shift, out);
+}
+// src/kernels/ops.cu:169-175
+void or_rmsnorm_bf16(const uint16_t* x, int64_t rows, int64_t dim, float eps, const float* w, uint16_t* out) {
+  if (rows <= 0) return;
+  norm_mod<1, true>(x, rows, dim, eps, w, RowMod{nullptr, nullptr, 0}, RowMod{nullptr, nullptr, 0}, out);
+}
+
+// gated_residual_kernel, src/kernels/ops.cu:73-84
+void or_gated_residual(float* x, const uint16_t* y, int64_t rows, int64_t dim, RowMod gate, int gate_tanh) {
+  parallel_rows(rows, [=](int64_t a, int64_t b) {
+    for (int64_t row = a; row < b; row++)
+      for (int64_t i = 0; i < dim; i++) {
+        float v = bf2f(y[row * dim + i]);
+        if (gate.target) {
+          float g = pick(gate, row)[i];
+          v *= gate_tanh ? std::tanh(g) : g;
+        }
+        x[row * dim + i] += v;
+      }
+  });
+}
+
+// src/kernels/ops.cu:191-195
+void or_add_inplace_bf16(uint16_t* x, const uint16_t* y, int64_t n) {
+  for (int64_t i = 0; i < n; i++) x[i] = f2bf(bf2f(x[i]) + bf2f(y[i]));
+}
+
+// head_norm_rope_kernel, src/kernels/ops.cu:87-119; mode 0 none, 1 interleaved, 2 half.
+// Returns -1 for the shapes the launcher rejects (src/kernels/ops.cu:201).
+int or_head_norm_rope(const uint16_t* in, int64_t S, int64_t in_stride, int64_t col0, int H, int D, const float* norm_w,
+                      float eps, const float* cs, const float* sn, int rot, int mode, uint16_t* out) {
+  if (S <= 0) return 0;
+  if (!(D % 2 == 0 && D <= 256 && rot <= D && rot % 2 == 0)) return -1;
+  const int threads = (D + 31) / 32 * 32;
+  parallel_rows(S, [=](int64_t a, int64_t b) {
+    float buf[256], part[256];
+    for (int64_t s = a; s < b; s++)
+      for (int h = 0; h < H; h++) {
+        for (int d = 0; d < D; d++) buf[d] = bf2f(in[s * in_stride + col0 + int64_t(h) * D + d]);
+        if (norm_w) {
+          for (int d = 0; d < threads; d++) part[d] = d < D ? buf[d] * buf[d] : 0.f;
+          const float ss = block_sum(part, threads);
+          const float r = 1.0f / std::sqrt(ss / float(D) + eps);
+          for (int d = 0; d < D; d++) buf[d] = buf[d] * r * norm_w[d];
+        }
+        uint16_t* o = out + (s * H + h) * D;
+        for (int d = 0; d < D; d++) {
+          float v = buf[d];
+          if (d < rot && mode != 0) {
+            const int half = rot / 2;
+            int pair, idx;
+            float other;
+            if (mode == 1) {
+              pair = d >> 1, idx = d & 1, other = buf[d ^ 1];
+            } else {
+              pair = d < half ? d : d - half;
+              idx = d < half ? 0 : 1;
+              other = buf[d < half ? d + half : d - half];
+            }
+            const float c = cs[s * half + pair], si = sn[s * half + pair];
+            v = idx == 0 ? v * c - other * si : other * si + v * c;
+          }
+          o[d] = f2bf(v);
+        }
+      }
+  });
+  return 0;
+}
+
+// silu_mul_kernel, src/kernels/ops.cu:121-128
+void or_silu_mul(const uint16_t* gu, int64_t rows, int64_t F, uint16_t* out) {
+  parallel_rows(rows, [=](int64_t a, int64_t b) {
+    for (int64_t row = a; row < b; row++)
+      for (int64_t i = 0; i < F; i++) {
+        const float g = bf2f(gu[row * 2 * F + i]);
+        const float u = bf2f(gu[row * 2 * F + F + i]);
+        out[row * F + i] = f2bf(g / (1.f + std::exp(-g)) * u);
+      }
+  });
+}
+
+// src/kernels/ops.cu:220-226
+void or_gelu_tanh_inplace(uint16_t* x, int64_t n) {
+  parallel_rows(n, [=](int64_t a, int64_t b) {
+    for (int64_t i = a; i < b; i++) {
+      const float v = bf2f(x[i]);
+      const float t = std::tanh(0.7978845608f * (v + 0.044715f * v * v * v));
+      x[i] = f2bf(0.5f * v * (1.f + t));
+    }
+  });
+}
+
+// src/kernels/ops.cu:228-233
+void or_gelu_erf_inplace(uint16_t* x, int64_t n) {
+  parallel_rows(n, [=](int64_t a, int64_t b) {
+    for (int64_t i = a; i < b; i++) {
+      const float v = bf2f(x[i]);
+      x[i] = f2bf(0.5f * v * (1.f + std::erf(v * 0.7071067811865476f)));
+    }
+  });
+}
+
+// src/kernels/ops.cu:244-246
+void or_silu_inplace_f32(float* x, int64_t n) {
+  for (int64_t i = 0; i < n; i++) x[i] = x[i] / (1.f + std::exp(-x[i]));
+}
+
+// src/kernels/ops.cu:235-242
+void or_scatter_rows(float* x, int64_t dim, const int32_t* rows, const uint16_t* src, int64_t n, int add) {
+  for (int64_t i = 0; i < n * dim; i++) {
+    const int64_t r = i / dim, d = i % dim;
+    const float v = bf2f(src[i]);
+    float* p = x + int64_t(rows[r]) * dim + d;
+    *p = add ? *p + v : v;
+  }
+}
+
+// src/kernels/ops.cu:249-270
+void or_add_bias_bf16(uint16_t* y, const float* bias, int64_t rows, int64_t dim) {
+  for (int64_t r = 0; r < rows; r++)
+    for (int64_t j = 0; j < dim; j++) y[r * dim + j] = f2bf(bf2f(y[r * dim + j]) + bias[j]);
+}
+// src/kernels/ops.cu:272-274
+void or_add_bias_f32(float* y, const float* bias, int64_t rows, int64_t dim) {
+  for (int64_t i = 0; i < rows * dim; i++) y[i] += bias[i % dim];
+}
+// src/kernels/ops.cu:276-282
+void or_f32_to_bf16(const float* x, uint16_t* y, int64_t n) {
+  for (int64_t i = 0; i < n; i++) y[i] = f2bf(x[i]);
+}
+void or_bf16_to_f32(const uint16_t* x, float* y, int64_t n) {
+  for (int64_t i = 0; i < n; i++) y[i] = bf2f(x[i]);
+}
+// src/kernels/ops.cu:284-290
+void or_axpy_f32(float* x, const float* y, float a, int64_t n) {
+  for (int64_t i = 0; i < n; i++) x[i] += a * y[i];
+}
+void or_axpby_f32(float* x, const float* y, float a, float b, int64_t n) {
+  for (int64_t i = 0; i < n; i++) x[i] = a * x[i] + b * y[i];
+}
+
+// ---- table builders ------------------------------------------------------------------------
+
+// A sequence segment of the Qwen-Image layout: a text run of `len` rows, or an image of ih x iw rows.
+struct QwenSeg {
+  int32_t is_text;
+  int32_t pad;
+  int64_t len, ih, iw;
+};
+
+// src/models/qwen_image/dit.cpp:151-185.  segs lists the prefix runs in order; the target image
+// (H x W) comes last, as `image(H, W)` does at :181.  cos/sin: fp32 [S, sum(axes)/2].
+// Returns the number of rows written.
+int64_t or_qwen_rope_table(const QwenSeg* segs, int n_segs, const int32_t* axes, float theta, float* hc, float* hs) {
+  std::vector<float> invf;
+  for (int a = 0; a < 3; a++)
+    for (int j = 0; j < axes[a] / 2; j++) invf.push_back(1.0f / std::pow(theta, float(2 * j) / float(axes[a])));
+  const int pairs = int(invf.size());
+  const int p0 = axes[0] / 2, p1 = p0 + axes[1] / 2;
+  auto put = [&](int64_t s, int64_t f, int64_t h, int64_t w) {
+    for (int p = 0; p < pairs; p++) {
+      int64_t pos = p < p0 ? f : p < p1 ? h : w;
+      float ang = float(pos) * invf[p];
+      hc[s * pairs + p] = std::cos(ang);
+      hs[s * pairs + p] = std::sin(ang);
+    }
+  };
+  int64_t position = 0, row = 0;
+  for (int i = 0; i < n_segs; i++) {
+    if (segs[i].is_text) {
+      for (int64_t k = 0; k < segs[i].len; k++, position++) put(row++, position, position, position);
+    } else {
+      const int64_t ih = segs[i].ih, iw = segs[i].iw;
+      for (int64_t r = 0; r < ih; r++)
+        for (int64_t col = 0; col < iw; col++) put(row++, position, r - (ih - ih / 2), col - (iw - iw / 2));
+      position += std::max(ih, iw);
+    }
+  }
+  return row;
+}
+
+// src/models/minimax_h3/layout.cpp:15-21
+static std::vector<double> spatial_grid(int64_t dim, double sqrt_area) {
+  double ratio = double(dim) / sqrt_area, left = (1.0 - ratio) / 2.0;
+  int64_t n = dim / 2;
+  std::vector<double> g(n);
+  for (int64_t k = 0; k < n; k++) g[k] = (left + ratio * double(k) / double(n)) * 32.0;
+  return g;
+}
+
+// Rotary positions of the first/last-frame layout, src/models/minimax_h3/layout.cpp:68-118:
+// rows = T text | n_anchors condition frames | 2A audio | F_lat video frames, each frame
+// (H/2) x (W/2) rows.  anchors[i]: 0 = "first", 1 = "last".  positions: fp32 [S, 3].
+// Returns S.
+int64_t or_h3_positions(int64_t T, int64_t F_lat, int64_t H, int64_t W, int64_t A, const int32_t* anchors, int n_anchors,
+                        float* positions) {
+  const int64_t rpf = (H / 2) * (W / 2);
+  const int64_t cond = int64_t(n_anchors) * rpf, audio = 2 * A, video = F_lat * rpf;
+  const int64_t S = T + cond + audio + video;
+  auto set = [&](int64_t r, double t, double h, double w) {
+    positions[r * 3] = float(t), positions[r * 3 + 1] = float(h), positions[r * 3 + 2] = float(w);
+  };
+  for (int64_t i = 0; i < T; i++) set(i, double(i), 0, 0);
+  const double sa = std::sqrt(double(H * W));
+  auto hg = spatial_grid(H, sa), wg = spatial_grid(W, sa);
+  static const int per_latent[5] = {1, 4, 4, 4, 4};
+  std::vector<double> ft(F_lat);
+  double acc = double(T), total = 0;
+  for (int64_t f = 0; f < F_lat; f++) {
+    ft[f] = acc;
+    double span = (5.0 / 3.0) * per_latent[f % 5];
+    acc += span;
+    total += span;
+  }
+  auto frame_rows = [&](int64_t r0, double t) {
+    for (int64_t y = 0; y < H / 2; y++)
+      for (int64_t x = 0; x < W / 2; x++) set(r0 + y * (W / 2) + x, t, hg[y], wg[x]);
+  };
+  for (int i = 0; i < n_anchors; i++) {
+    double t = anchors[i] == 0 ? double(T) : double(T) + total - 5.0 / 3.0;
+    frame_rows(T + int64_t(i) * rpf, t);
+  }
+  const int64_t audio_start = T + cond, video_start = T + cond + audio;
+  for (int64_t c = 0; c < 2; c++)
+    for (int64_t a = 0; a < A; a++) set(audio_start + c * A + a, double(T) + double(a), 0, c == 0 ? wg.front() : wg.back());
+  for (int64_t f = 0; f < F_lat; f++) frame_rows(video_start + f * rpf, ft[f]);
+  return S;
+}
+
+// src/models/minimax_h3/dit.cpp:254-262: entry [s, a*nf + j] = cosf/sinf(positions[s, a] * inv_freq[j]).
+void or_h3_rope_table(const float* positions, int64_t S, const float* inv_freq, int nf, float* hc, float* hs) {
+  const int64_t half = 3 * int64_t(nf);
+  for (int64_t s = 0; s < S; s++)
+    for (int a = 0; a < 3; a++)
+      for (int j = 0; j < nf; j++) {
+        float ang = positions[s * 3 + a] * inv_freq[j];
+        hc[s * half + a * nf + j] = std::cos(ang);
+        hs[s * half + a * nf + j] = std::sin(ang);
+      }
+}
+
+// src/models/qwen_image/dit.cpp:219-230; out fp32 [2, 256]
+void or_qwen_timestep_embedding(float t, float* emb) {
+  const int half = 128;
+  float ts[2] = {round_bf16(t) * 1000.f, 0.f};
+  for (int r = 0; r < 2; r++)
+    for (int i = 0; i < half; i++) {
+      float f = std::exp(-std::log(10000.f) * float(i) / float(half));
+      float arg = ts[r] * f;
+      emb[r * 256 + i] = round_bf16(std::cos(arg));
+      emb[r * 256 + half + i] = round_bf16(std::sin(arg));
+    }
+}
+
+// src/models/minimax_h3/dit.cpp:166-179
+void or_h3_time_basis(const float* ts, int64_t nt, const float* table, int64_t grid, int64_t basis, float* out) {
+  for (int64_t i = 0; i < nt; i++) {
+    float pos = std::clamp(ts[i], 0.f, 1.f) * float(grid - 1);
+    int64_t lo = std::min<int64_t>(int64_t(std::floor(pos)), grid - 2);
+    float fr = pos - float(lo);
+    for (int64_t j = 0; j < basis; j++) {
+      float a = table[lo * basis + j], b = table[(lo + 1) * basis + j];
+      out[i * basis + j] = a + (b - a) * fr;
+    }
+  }
+}
+
+}  // extern "C"
