@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the second chain and the per-op pass")
+    ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
+                    help="override a launch-shape knob of libmxk (see miroxen_b200/csrc/tuning.h); repeatable")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (default: chosen for ~10-30 s)")
     return ap.parse_args()
 
@@ -275,6 +277,9 @@ def main():
     if world > 1 and args.impl == "mxk":
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     mx.lib()
+    for kv in args.tune:
+        k, v = kv.split("=")
+        mx.set_tuning(k, int(v))
     w = W[args.workload]
     n_gpus = world if args.impl == "mxk" else 1
 

@@ -284,6 +284,11 @@ void mxk_host_pipeline_destroy(MxkHostPipeline* p);
 int mxk_dit_block_ops_host(MxkHostPipeline* p, const MxkBlockArgs* a, int64_t* h2d_bytes,
                            int64_t* d2h_bytes);
 
+/* Reads (and with clear != 0 resets) the current device's error word: 0, or 1 when a kernel's bounded
+ * wait on a bulk copy ran out and the kernel returned early (its outputs are then incomplete).
+ * Synchronises with the device. */
+int mxk_device_error(int* out_host, int clear);
+
 /* Development knob: overrides a launch-shape default (see tuning.h for the names); value 0
  * restores the default.  Results do not depend on it. */
 int mxk_set_tuning(const char* name, int value);

@@ -7,21 +7,27 @@ namespace {
 
 // 0.5 v (1 + tanh(u)), u = 0.7978845608 (v + 0.044715 v^3)  (src/kernels/ops.cu:222-224).
 // With e = exp(-2|u|) in (0, 1]:  1 + tanh(u) = 2 / (1 + e) for u >= 0 and 2 e / (1 + e) for
-// u < 0, so the value is v * (u >= 0 ? 1 : e) / (1 + e): one ex2 and one reciprocal, no
-// cancellation in the negative tail and no overflow.
+// u < 0, so the value is v / (1 + e), times e when v < 0 (u has the sign of v): one ex2 and one
+// reciprocal, no cancellation in the negative tail and no overflow.  The constants fold
+// 2 log2(e) into the polynomial: 2 log2(e) u = v (A0 + A1 v^2).  Ten issue slots per element;
+// the kernel has to sustain more than one element per clock per SM quarter to keep up with HBM.
 __device__ __forceinline__ float gelu_tanh_f(float v) {
-  const float u = 0.7978845608f * (v + 0.044715f * v * v * v);
-  const float e = __expf(-2.f * fabsf(u));
-  const float num = u >= 0.f ? v : v * e;
-  return __fdividef(num, 1.f + e);
+  constexpr float A0 = 2.f * 1.4426950408889634f * 0.7978845608f;
+  constexpr float A1 = A0 * 0.044715f;
+  const float w = v * fmaf(v * v, A1, A0);
+  const float e = ex2_approx(-fabsf(w));
+  const float m = v * rcp_approx(1.f + e);
+  return v >= 0.f ? m : m * e;
 }
 
 __device__ __forceinline__ float gelu_erf_f(float v) {
   return 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
 }
 
-// g / (1 + exp(-g))  (src/kernels/ops.cu:127)
-__device__ __forceinline__ float silu_f(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+// g / (1 + exp(-g))  (src/kernels/ops.cu:127): exp through ex2, the division as a reciprocal.
+__device__ __forceinline__ float silu_f(float g) {
+  return g * rcp_approx(1.f + ex2_approx(g * -1.4426950408889634f));
+}
 
 template <int KIND>  // 0 gelu tanh, 1 gelu erf
 struct GeluOp {
@@ -122,8 +128,9 @@ int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk
     const int rpc = tune(TUNE_ACT_ROWS_PER_CTA, 4);
     const unsigned gy = unsigned(ceil_div(F / 8, threads));
     const int64_t nchunks = ceil_div(rows, rpc);
-    int64_t gx = ceil_div(int64_t(sm_count()) * 16, gy);
+    int64_t gx = ceil_div(int64_t(sm_count()) * resident_ctas(silu_mul_kernel, threads), gy);
     if (gx > nchunks) gx = nchunks;
+    if (gx < 1) gx = 1;
     silu_mul_kernel<<<dim3(unsigned(gx), gy), threads, 0, s>>>(in, rows, int(F), o, rpc);
   } else {
     const unsigned gy = unsigned(ceil_div(F, 256));

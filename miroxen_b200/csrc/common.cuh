@@ -21,6 +21,17 @@ int after_launch(const char* what);
 // Number of SMs of the current device (cached per device ordinal).
 int sm_count();
 
+// Address, on the current device, of the int the kernels' bounded waits report to (0 = no error).
+int* device_error_word();
+
+// CTAs of `kernel` that one SM holds at this CTA size (occupancy API, cached per kernel/size).
+// Grids of the persistent kernels are sized to exactly one resident wave with it.
+int resident_ctas_lookup(const void* kernel, int threads, size_t smem);
+template <class K>
+inline int resident_ctas(K kernel, int threads, size_t smem = 0) {
+  return resident_ctas_lookup(reinterpret_cast<const void*>(kernel), threads, smem);
+}
+
 inline cudaStream_t as_stream(mxk_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
 
 template <class T>
@@ -68,6 +79,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ float bf16_to_f(bf16 v) { return __bfloat162float(v); }
+
+// Single-instruction special functions (MUFU), flush-to-zero: 2^x and 1/x to about 2 ulp.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 __device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
   f[0] = bf16_lo(v.x), f[1] = bf16_hi(v.x);

@@ -148,8 +148,9 @@ int run_add_bias(const char* name, T* y, const float* bias, int64_t rows, int64_
     const int rpc = 8;
     const unsigned gy = unsigned(ceil_div(dim / VEC, 256));
     const int64_t nchunks = ceil_div(rows, rpc);
-    int64_t gx = ceil_div(int64_t(sm_count()) * 16, gy);
+    int64_t gx = ceil_div(int64_t(sm_count()) * resident_ctas(add_bias_vec_kernel<T>, 256), gy);
     if (gx > nchunks) gx = nchunks;
+    if (gx < 1) gx = 1;
     add_bias_vec_kernel<T><<<dim3(unsigned(gx), gy), 256, 0, s>>>(y, bias, rows, int(dim), rpc);
   } else {
     const unsigned gy = unsigned(ceil_div(dim, 256));

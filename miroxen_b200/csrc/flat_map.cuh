@@ -53,13 +53,18 @@ inline int run_flat(const char* name, int64_t n, const Op& op, cudaStream_t s) {
     const int threads = tune(TUNE_EW_THREADS, 256);
     const int unroll = tune(TUNE_EW_UNROLL, 4);
     const int64_t nvec = n / Op::VEC;
-    int64_t grid = ceil_div(nvec, int64_t(threads) * unroll);
-    if (grid > cap) grid = cap;
+    // a grid-stride loop over exactly one resident wave of CTAs (fewer when the array is small)
+    auto go = [&](auto kern) {
+      int64_t grid = ceil_div(nvec, int64_t(threads) * unroll);
+      const int64_t wave = int64_t(sm_count()) * tune(TUNE_EW_CTAS_PER_SM, resident_ctas(kern, threads));
+      if (grid > wave) grid = wave;
+      kern<<<unsigned(grid), threads, 0, s>>>(n, op);
+    };
     switch (unroll) {
-      case 1: flat_vec_kernel<1, Op><<<unsigned(grid), threads, 0, s>>>(n, op); break;
-      case 2: flat_vec_kernel<2, Op><<<unsigned(grid), threads, 0, s>>>(n, op); break;
-      case 8: flat_vec_kernel<8, Op><<<unsigned(grid), threads, 0, s>>>(n, op); break;
-      default: flat_vec_kernel<4, Op><<<unsigned(grid), threads, 0, s>>>(n, op); break;
+      case 1: go(flat_vec_kernel<1, Op>); break;
+      case 2: go(flat_vec_kernel<2, Op>); break;
+      case 8: go(flat_vec_kernel<8, Op>); break;
+      default: go(flat_vec_kernel<4, Op>); break;
     }
   } else {
     int64_t grid = ceil_div(n, 256);

@@ -11,6 +11,7 @@
 // (one 128-bit load) per lane.  A token is shared by `gpt` such lane groups; each group walks
 // the heads gh, gh + gpt, ... of every tensor of the launch (q, k, v) with the token's cos/sin
 // values in registers, so the table row is fetched once per token per group, not once per head.
+#include "bulk_copy.cuh"
 #include "common.cuh"
 #include "tuning.h"
 
@@ -19,6 +20,15 @@ namespace {
 
 constexpr int kMaxTensors = 3;
 constexpr int kHeadsInFlight = 4;  // independent 128-bit loads each lane issues per batch
+
+// What one bulk copy brings in: the bytes of one or more tensors for the tokens of a group.
+struct CopySeg {
+  const unsigned char* base;  // global address of token 0's first byte
+  int64_t token_stride;       // bytes from one token to the next in global memory
+  int token_bytes;            // bytes per token (multiple of 16)
+  int smem_off;               // offset of the group's first token inside a stage
+  int dense;                  // token_stride == token_bytes: a whole group is one contiguous copy
+};
 
 struct RopeArgs {
   MxkHeadTensor t[kMaxTensors];
@@ -30,6 +40,17 @@ struct RopeArgs {
   const float* sin;
   int gpt;              // lane groups per token
   int tokens_per_pass;  // tokens a CTA holds at once
+  // bulk-copy pipeline kernel
+  int passes, heads_per_pass, stages, stage_bytes;
+  int rot, mode;    // shared by every rotating tensor of the launch
+  int tpc;          // tokens per stage (one group)
+  int64_t groups_per_cta;
+  CopySeg seg[kMaxTensors];
+  int n_seg;
+  int t_seg[kMaxTensors];  // segment that holds tensor ti
+  int t_off[kMaxTensors];  // byte offset of tensor ti's first head inside the token's segment bytes
+  int cos_off, sin_off;    // table slots inside a stage
+  int* err;
 };
 
 template <int LPH>
@@ -149,6 +170,253 @@ __global__ void __launch_bounds__(512) head_rope_kernel(const RopeArgs a) {
   }
 }
 
+// Bulk-copy (TMA) pipeline.  The last warp of the CTA is a producer: for each group of `tpc`
+// consecutive tokens it issues cp.async.bulk copies of the tensors' bytes (one copy per group
+// where the tokens are contiguous in memory, which is the case for a dense [S, H*D] projection
+// and for a packed [S, 3*H*D] q|k|v buffer) and of the group's cos / sin rows into a
+// shared-memory stage, completing on the stage's `full` mbarrier.  The other warps are consumers:
+// thread t holds channels 8l..8l+7 (l = t % LPH) of head t / LPH (+ heads_per_pass per pass),
+// reads them from the stage, normalises, rotates and stores 128 bits to global memory.  No warp
+// depends on another one's heads, so there is no CTA-wide barrier in the loop: a warp that is
+// done with a stage arrives on its `empty` mbarrier and the producer refills it once all have.
+// Bytes in flight are stages x stage size per CTA, whatever the register count.
+//
+// All mbarrier waits are bounded (bulk_copy.cuh); a warp whose wait runs out records
+// kErrBulkTimeout and leaves the loop, the others then run out too, and before the CTA exits the
+// producer gives the copies it issued a bounded chance to land.
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ float rsqrt_approx(float x) {
+  float y;
+  asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Per-thread constants of a consumer: where its 8 channels sit and how they rotate.
+struct LaneRole {
+  int thread_off;   // byte offset of channels 8l..8l+7 of head hp inside a token's H*D bf16
+  int pass_off;     // bytes from one pass's head to the next (heads_per_pass * D * 2)
+  int tab_idx;      // first cos/sin entry of the lane (4 entries interleaved, 8 half mode)
+  int partner;      // lane that holds the pair partners (half mode)
+  int last_pass_heads;  // heads handled in the final pass (others handle heads_per_pass)
+  int hp;
+  bool rotates;     // 8l < rot
+  bool first;       // half mode: the lane holds the first element of each pair
+};
+
+// All `ntok` tokens of one tensor inside a stage.  NORM: per-head RMSNorm; MODE as MXK_ROPE_*.
+// src points at the thread's 8 channels of token 0 (pass 0) in shared memory, dst at the same
+// place of the output; cr / sr at the lane's first table entry of token 0.
+template <int LPH, bool NORM, int MODE>
+__device__ __forceinline__ void rope_tokens(const unsigned char* src, int tok_bytes, const float* cr, const float* sr,
+                                            int half, int ntok, unsigned char* dst, int out_tok_bytes,
+                                            const float* wsm_row, float inv_d, float eps, int passes, int heads_per_pass,
+                                            int H, const LaneRole& r) {
+  float w[8];
+  if (NORM) {
+    const float4 w0 = *reinterpret_cast<const float4*>(wsm_row), w1 = *reinterpret_cast<const float4*>(wsm_row + 4);
+    w[0] = w0.x, w[1] = w0.y, w[2] = w0.z, w[3] = w0.w, w[4] = w1.x, w[5] = w1.y, w[6] = w1.z, w[7] = w1.w;
+  }
+  for (int tk = 0; tk < ntok; tk++) {
+    float c[8], sg[8];
+    if (MODE == MXK_ROPE_INTERLEAVED) {
+      // channels 8l..8l+7 are pairs 4l..4l+3: (a, b) -> (a c - b s, a s + b c)
+      const float4 cc = *reinterpret_cast<const float4*>(cr), ss = *reinterpret_cast<const float4*>(sr);
+      c[0] = cc.x, c[1] = cc.y, c[2] = cc.z, c[3] = cc.w;
+      sg[0] = ss.x, sg[1] = ss.y, sg[2] = ss.z, sg[3] = ss.w;
+    } else if (MODE == MXK_ROPE_HALF) {
+      const float4 c0 = *reinterpret_cast<const float4*>(cr), c1 = *reinterpret_cast<const float4*>(cr + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sr), s1 = *reinterpret_cast<const float4*>(sr + 4);
+      c[0] = c0.x, c[1] = c0.y, c[2] = c0.z, c[3] = c0.w, c[4] = c1.x, c[5] = c1.y, c[6] = c1.z, c[7] = c1.w;
+      // the first element of a pair takes -sin, the second +sin
+      const float f = r.first ? -1.f : 1.f;
+      sg[0] = f * s0.x, sg[1] = f * s0.y, sg[2] = f * s0.z, sg[3] = f * s0.w;
+      sg[4] = f * s1.x, sg[5] = f * s1.y, sg[6] = f * s1.z, sg[7] = f * s1.w;
+    }
+    const unsigned char* sp = src;
+    unsigned char* dp = dst;
+    for (int pass = 0; pass < passes; pass++) {
+      const bool on = r.hp < (pass + 1 < passes ? heads_per_pass : H - pass * heads_per_pass);
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (on) raw = *reinterpret_cast<const uint4*>(sp);
+      float v[8];
+      unpack8(raw, v);
+      if (NORM) {
+        float q = v[0] * v[0];
+#pragma unroll
+        for (int i = 1; i < 8; i++) q = fmaf(v[i], v[i], q);
+        q = group_sum<LPH>(q);
+        const float rstd = rsqrt_approx(fmaf(q, inv_d, eps));
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = v[i] * rstd * w[i];
+      }
+      if (MODE == MXK_ROPE_INTERLEAVED) {
+        if (r.rotates) {
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const float a0 = v[2 * i], b0 = v[2 * i + 1];
+            v[2 * i] = a0 * c[i] - b0 * sg[i];
+            v[2 * i + 1] = b0 * c[i] + a0 * sg[i];
+          }
+        }
+      } else if (MODE == MXK_ROPE_HALF) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float other = __shfl_sync(0xffffffffu, v[i], r.partner);
+          if (r.rotates) v[i] = fmaf(other, sg[i], v[i] * c[i]);
+        }
+      }
+      if (on) st_stream(reinterpret_cast<uint4*>(dp), pack8(v));
+      sp += r.pass_off;
+      dp += r.pass_off;
+    }
+    src += tok_bytes;
+    dst += out_tok_bytes;
+    cr += half;
+    sr += half;
+  }
+}
+
+template <int LPH>
+__global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
+  extern __shared__ __align__(128) unsigned char dyn[];
+  __shared__ __align__(8) unsigned long long full[8], empty[8];
+  __shared__ __align__(16) float wsm[kMaxTensors][256];  // the tensors' norm weights
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int n_cons_warps = (blockDim.x >> 5) - 1;
+  for (int i = tid; i < a.n_tensors * a.D; i += blockDim.x) {
+    const int ti = i / a.D, d = i - ti * a.D;
+    wsm[ti][d] = a.t[ti].norm_w ? a.t[ti].norm_w[d] : 1.f;
+  }
+  const int half = a.rot >> 1;
+  const bool rope = a.mode != MXK_ROPE_NONE && a.rot > 0;
+  const int64_t n_groups = (a.S + a.tpc - 1) / a.tpc;
+  const int64_t g_begin = int64_t(blockIdx.x) * a.groups_per_cta;
+  const int64_t g_end = g_begin + a.groups_per_cta < n_groups ? g_begin + a.groups_per_cta : n_groups;
+  const int my_groups = g_end > g_begin ? int(g_end - g_begin) : 0;
+
+  if (tid == 0) {
+    for (int i = 0; i < a.stages; i++) {
+      mbar_init(smem_u32(&full[i]), 1);
+      mbar_init(smem_u32(&empty[i]), unsigned(n_cons_warps));
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  bool ok = true;
+  int issued = 0;  // producer: groups whose copies were issued
+  if (warp == n_cons_warps) {
+    if (lane == 0) {
+      int st = 0;
+      unsigned ph = 1;  // parity of the `empty` phase to wait for; flips each trip round the ring
+      int64_t s0 = g_begin * a.tpc;
+      for (int it = 0; it < my_groups; it++, s0 += a.tpc) {
+        if (it >= a.stages && !mbar_wait(smem_u32(&empty[st]), ph)) {
+          ok = false;
+          break;
+        }
+        const unsigned ntok = unsigned(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
+        const unsigned bar = smem_u32(&full[st]);
+        const unsigned dst = smem_u32(dyn + size_t(st) * a.stage_bytes);
+        unsigned bytes = rope ? 2u * ntok * unsigned(half) * 4u : 0u;
+        for (int i = 0; i < a.n_seg; i++) bytes += ntok * unsigned(a.seg[i].token_bytes);
+        mbar_expect_tx(bar, bytes);
+        for (int i = 0; i < a.n_seg; i++) {
+          const CopySeg& sg = a.seg[i];
+          const unsigned char* src = sg.base + s0 * sg.token_stride;
+          if (sg.dense) {
+            bulk_g2s(dst + sg.smem_off, src, ntok * unsigned(sg.token_bytes), bar);
+          } else {
+            for (unsigned t = 0; t < ntok; t++)
+              bulk_g2s(dst + sg.smem_off + t * unsigned(sg.token_bytes), src + t * sg.token_stride,
+                       unsigned(sg.token_bytes), bar);
+          }
+        }
+        if (rope) {
+          bulk_g2s(dst + a.cos_off, a.cos + s0 * half, ntok * unsigned(half) * 4u, bar);
+          bulk_g2s(dst + a.sin_off, a.sin + s0 * half, ntok * unsigned(half) * 4u, bar);
+        }
+        issued++;
+        if (++st == a.stages) st = 0, ph ^= (it >= a.stages ? 1u : 0u);
+      }
+    }
+  } else {
+    const int l = tid % LPH;
+    LaneRole r;
+    r.hp = tid / LPH;
+    r.thread_off = (r.hp * a.D + 8 * l) * 2;
+    r.pass_off = a.heads_per_pass * a.D * 2;
+    r.rotates = rope && 8 * l < a.rot;
+    r.tab_idx = 0, r.partner = lane, r.first = true;
+    if (r.rotates) {
+      if (a.mode == MXK_ROPE_INTERLEAVED) {
+        r.tab_idx = 4 * l;
+      } else {
+        const int hl = half >> 3;
+        r.first = l < hl;
+        r.tab_idx = 8 * (r.first ? l : l - hl);
+        r.partner = (lane & ~(LPH - 1)) + (r.first ? l + hl : l - hl);
+      }
+    }
+    const float inv_d = 1.f / float(a.D);  // D is a power of two on this path: exact
+    const int tok_out_bytes = a.H * a.D * 2;
+
+    int st = 0;
+    unsigned ph = 0;
+    int64_t s0 = g_begin * a.tpc;
+    for (int it = 0; it < my_groups; it++, s0 += a.tpc) {
+      if (!mbar_wait(smem_u32(&full[st]), ph)) {
+        ok = false;
+        break;
+      }
+      const unsigned char* stage = dyn + size_t(st) * a.stage_bytes;
+      const int ntok = int(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
+      const float* cr = reinterpret_cast<const float*>(stage + a.cos_off) + r.tab_idx;
+      const float* sr = reinterpret_cast<const float*>(stage + a.sin_off) + r.tab_idx;
+#pragma unroll 1
+      for (int ti = 0; ti < a.n_tensors; ti++) {
+        {
+          const MxkHeadTensor& t = a.t[ti];
+          const CopySeg& sg = a.seg[a.t_seg[ti]];
+          const unsigned char* src = stage + sg.smem_off + a.t_off[ti] + r.thread_off;
+          unsigned char* dst = reinterpret_cast<unsigned char*>(t.out) + s0 * tok_out_bytes + r.thread_off;
+          const bool t_rope = t.mode != MXK_ROPE_NONE && t.rot > 0;
+          const float* wr = &wsm[ti][8 * l];
+#define MXK_ROPE_CALL(NORM, MODE)                                                                          \
+  rope_tokens<LPH, NORM, MODE>(src, sg.token_bytes, cr, sr, half, ntok, dst, tok_out_bytes, wr, inv_d, a.eps, \
+                               a.passes, a.heads_per_pass, a.H, r)
+          if (t.norm_w) {
+            if (!t_rope) MXK_ROPE_CALL(true, MXK_ROPE_NONE);
+            else if (a.mode == MXK_ROPE_INTERLEAVED) MXK_ROPE_CALL(true, MXK_ROPE_INTERLEAVED);
+            else MXK_ROPE_CALL(true, MXK_ROPE_HALF);
+          } else {
+            if (!t_rope) MXK_ROPE_CALL(false, MXK_ROPE_NONE);
+            else if (a.mode == MXK_ROPE_INTERLEAVED) MXK_ROPE_CALL(false, MXK_ROPE_INTERLEAVED);
+            else MXK_ROPE_CALL(false, MXK_ROPE_HALF);
+          }
+#undef MXK_ROPE_CALL
+        }
+      }
+      // The stage's bytes are in this warp's registers (they fed the stores above): hand it back.
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty[st]));
+      if (++st == a.stages) st = 0, ph ^= 1u;
+    }
+  }
+
+  if (!ok && a.err) atomicExch(a.err, kErrBulkTimeout);
+  // Every warp reaches this barrier (all waits above are bounded).  On the normal path every
+  // issued copy has been consumed, hence completed; after a failure the producer waits, bounded,
+  // for the copies of its last `stages` groups so that none lands in a dead CTA's shared memory.
+  const bool any_failed = __syncthreads_or(!ok) != 0;
+  if (any_failed && warp == n_cons_warps && lane == 0) {
+    for (int it = issued > a.stages ? issued - a.stages : 0; it < issued; it++)
+      mbar_wait(smem_u32(&full[it % a.stages]), unsigned((it / a.stages) & 1));
+  }
+}
+
 // Any even D <= 256, any rot, any alignment: one warp per (token, head), the head's values pass
 // through shared memory for the partner exchange.
 __global__ void __launch_bounds__(256) head_rope_generic_kernel(const RopeArgs a) {
@@ -213,7 +481,97 @@ bool fast_ok(const RopeArgs& a) {
   return true;
 }
 
+// Plans the bulk-copy pipeline: beyond fast_ok it needs one (rot, mode) for all rotating tensors
+// and table rows that are multiples of 16 bytes.  Tensors that are consecutive column blocks of
+// the same buffer (packed q|k|v) become one copy segment.
+bool pipe_plan(RopeArgs& a) {
+  a.rot = 0, a.mode = MXK_ROPE_NONE;
+  for (int i = 0; i < a.n_tensors; i++) {
+    const MxkHeadTensor& t = a.t[i];
+    if (t.mode == MXK_ROPE_NONE || t.rot == 0) continue;
+    if (a.mode == MXK_ROPE_NONE) a.rot = t.rot, a.mode = t.mode;
+    else if (a.rot != t.rot || a.mode != t.mode) return false;
+  }
+  const int half = a.rot / 2;
+  if (a.mode != MXK_ROPE_NONE && half % 4) return false;
+  const int lph = a.D / 8;
+  int max_threads = tune(TUNE_ROPE_THREADS, 512);
+  if (max_threads > 512) max_threads = 512;
+  if (max_threads < lph) max_threads = lph;
+  int passes = 1;
+  while (lph * int(ceil_div(a.H, passes)) > max_threads) passes++;
+  a.passes = passes;
+  a.heads_per_pass = int(ceil_div(a.H, passes));
+  const int64_t hd = int64_t(a.H) * a.D;
+  if (hd * 2 > (1 << 20)) return false;
+
+  // one segment when the tensors are adjacent column blocks of one buffer, in order
+  bool packed = a.n_tensors > 1;
+  for (int i = 1; i < a.n_tensors && packed; i++)
+    packed = a.t[i].in == a.t[0].in && a.t[i].in_stride == a.t[0].in_stride && a.t[i].col0 == a.t[0].col0 + i * hd;
+  a.n_seg = packed ? 1 : a.n_tensors;
+  for (int i = 0; i < a.n_seg; i++) {
+    CopySeg& sg = a.seg[i];
+    const MxkHeadTensor& t = a.t[i];
+    sg.base = reinterpret_cast<const unsigned char*>(t.in + t.col0);
+    sg.token_stride = t.in_stride * 2;
+    sg.token_bytes = int((packed ? a.n_tensors * hd : hd) * 2);
+    sg.dense = sg.token_stride == sg.token_bytes;
+  }
+  for (int i = 0; i < a.n_tensors; i++) {
+    a.t_seg[i] = packed ? 0 : i;
+    a.t_off[i] = packed ? int(i * hd * 2) : 0;
+  }
+  int per_token = 2 * half * 4;
+  for (int i = 0; i < a.n_seg; i++) per_token += a.seg[i].token_bytes;
+  int tpc = tune(TUNE_ROPE_TOKENS, 0);
+  if (tpc <= 0) tpc = 24576 / per_token;
+  if (tpc < 1) tpc = 1;
+  if (tpc > 16) tpc = 16;
+  a.tpc = tpc;
+  int off = 0;
+  for (int i = 0; i < a.n_seg; i++) {
+    a.seg[i].smem_off = off;
+    off += (tpc * a.seg[i].token_bytes + 127) & ~127;
+  }
+  a.cos_off = off;
+  off += (tpc * half * 4 + 127) & ~127;
+  a.sin_off = off;
+  off += (tpc * half * 4 + 127) & ~127;
+  a.stage_bytes = off;
+  int stages = tune(TUNE_ROPE_STAGES, 0);
+  if (stages <= 0) stages = 73728 / a.stage_bytes;
+  if (stages < 2) stages = 2;
+  if (stages > 8) stages = 8;
+  a.stages = stages;
+  return size_t(stages) * a.stage_bytes <= 200 * 1024;
+}
+
+template <int LPH>
+int launch_pipe(const char* name, RopeArgs a, cudaStream_t stream) {
+  auto k = head_rope_pipe_kernel<LPH>;
+  const int threads = int(ceil_div(int64_t(LPH) * a.heads_per_pass, 32) * 32) + 32;  // consumers + producer warp
+  const size_t smem = size_t(a.stages) * a.stage_bytes;
+  if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  const int per_sm = tune(TUNE_ROPE_CTAS_PER_SM, resident_ctas(k, threads, smem));
+  const int64_t n_groups = ceil_div(a.S, a.tpc);
+  int64_t ctas = int64_t(sm_count()) * (per_sm > 0 ? per_sm : 1);
+  if (ctas > n_groups) ctas = n_groups;
+  a.groups_per_cta = ceil_div(n_groups, ctas);
+  a.err = device_error_word();
+  k<<<unsigned(ceil_div(n_groups, a.groups_per_cta)), threads, smem, stream>>>(a);
+  return after_launch(name);
+}
+
 int run(const char* name, RopeArgs a, cudaStream_t stream) {
+  if (fast_ok(a) && tune(TUNE_ROPE_PATH, 1) == 1 && a.S >= 2 && pipe_plan(a)) {
+    switch (a.D / 8) {
+      case 4: return launch_pipe<4>(name, a, stream);
+      case 8: return launch_pipe<8>(name, a, stream);
+      case 16: return launch_pipe<16>(name, a, stream);
+      default: return launch_pipe<32>(name, a, stream);
+    }
+  }
   if (fast_ok(a)) {
     const int lph = a.D / 8;
     a.gpt = int(ceil_div(a.H, kHeadsInFlight));
@@ -224,15 +582,18 @@ int run(const char* name, RopeArgs a, cudaStream_t stream) {
       if (tpp < 1) tpp = 1;
       int threads = int(ceil_div(int64_t(per_token) * tpp, 32) * 32);
       a.tokens_per_pass = tpp;
-      const int per_sm = tune(TUNE_ROPE_CTAS_PER_SM, 2048 / threads > 6 ? 6 : 2048 / threads);
-      int64_t grid = ceil_div(a.S, tpp);
-      int64_t cap = int64_t(sm_count()) * (per_sm > 0 ? per_sm : 1);
-      if (grid > cap) grid = cap;
+      auto go = [&](auto kern) {
+        const int per_sm = tune(TUNE_ROPE_CTAS_PER_SM, resident_ctas(kern, threads));
+        int64_t grid = ceil_div(a.S, tpp);
+        const int64_t cap = int64_t(sm_count()) * (per_sm > 0 ? per_sm : 1);
+        if (grid > cap) grid = cap;
+        kern<<<unsigned(grid), threads, 0, stream>>>(a);
+      };
       switch (lph) {
-        case 4: head_rope_kernel<4><<<unsigned(grid), threads, 0, stream>>>(a); break;
-        case 8: head_rope_kernel<8><<<unsigned(grid), threads, 0, stream>>>(a); break;
-        case 16: head_rope_kernel<16><<<unsigned(grid), threads, 0, stream>>>(a); break;
-        default: head_rope_kernel<32><<<unsigned(grid), threads, 0, stream>>>(a); break;
+        case 4: go(head_rope_kernel<4>); break;
+        case 8: go(head_rope_kernel<8>); break;
+        case 16: go(head_rope_kernel<16>); break;
+        default: go(head_rope_kernel<32>); break;
       }
       return after_launch(name);
     }

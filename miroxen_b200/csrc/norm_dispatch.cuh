@@ -24,33 +24,59 @@ inline bool plan_norm(int nvec, int64_t rows, NormPlan& p) {
   }
   if (!p.threads) return false;
   p.exact = p.threads * p.vpt == nvec;
-  const int per_sm = tune(TUNE_NORM_CTAS_PER_SM, p.threads <= 128 ? 8 : p.threads <= 256 ? 4 : 2);
-  int64_t ctas = int64_t(sm_count()) * per_sm;
-  if (ctas > rows) ctas = rows;
-  p.rows_per_cta = int(ceil_div(rows, ctas));
-  p.grid = unsigned(ceil_div(rows, p.rows_per_cta));
   return true;
 }
 
+// Rows are split evenly over exactly one resident wave of CTAs (or fewer when rows are few).
+inline unsigned norm_grid(NormArgs& a, int per_sm) {
+  int64_t ctas = int64_t(sm_count()) * (per_sm > 0 ? per_sm : 1);
+  if (ctas > a.rows) ctas = a.rows;
+  a.rows_per_cta = int(ceil_div(a.rows, ctas));
+  return unsigned(ceil_div(a.rows, a.rows_per_cta));
+}
+
+constexpr int kNormMaxStages = 8;
+
+template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool EXACT>
+inline void launch_norm_inst(const NormPlan& p, NormArgs a, bool tma, cudaStream_t s) {
+  if (tma) {
+    a.err = device_error_word();
+    auto k = norm_rows_tma_kernel<MODE, TIN, VPT, HAS_W, FUSE_RES, EXACT>;
+    const int xb = (a.dim * int(sizeof(TIN)) + 127) & ~127;
+    const int stage_bytes = xb + (FUSE_RES ? ((a.dim * 2 + 127) & ~127) : 0);
+    int stages = tune(TUNE_NORM_STAGES, 0);
+    if (stages <= 0) stages = 49152 / stage_bytes;  // about 48 KB of rows in flight per CTA
+    if (stages < 2) stages = 2;
+    if (stages > kNormMaxStages) stages = kNormMaxStages;
+    const size_t smem = size_t(stages) * stage_bytes;
+    // static shared memory (reduction scratch, barriers) counts against the 48 KB default too
+    if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    const unsigned grid = norm_grid(a, tune(TUNE_NORM_CTAS_PER_SM, resident_ctas(k, p.threads, smem)));
+    k<<<grid, p.threads, smem, s>>>(a, stages, stage_bytes);
+  } else {
+    auto k = norm_rows_kernel<MODE, TIN, VPT, HAS_W, FUSE_RES, EXACT>;
+    const unsigned grid = norm_grid(a, tune(TUNE_NORM_CTAS_PER_SM, resident_ctas(k, p.threads)));
+    k<<<grid, p.threads, 0, s>>>(a);
+  }
+}
+
 template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES>
-inline void launch_norm_vpt(const NormPlan& p, const NormArgs& a, cudaStream_t s) {
-  if (p.exact)
-    norm_rows_kernel<MODE, TIN, VPT, HAS_W, FUSE_RES, true><<<p.grid, p.threads, 0, s>>>(a);
-  else
-    norm_rows_kernel<MODE, TIN, VPT, HAS_W, FUSE_RES, false><<<p.grid, p.threads, 0, s>>>(a);
+inline void launch_norm_vpt(const NormPlan& p, const NormArgs& a, bool tma, cudaStream_t s) {
+  if (p.exact) launch_norm_inst<MODE, TIN, VPT, HAS_W, FUSE_RES, true>(p, a, tma, s);
+  else launch_norm_inst<MODE, TIN, VPT, HAS_W, FUSE_RES, false>(p, a, tma, s);
 }
 
 template <int MODE, class TIN, bool HAS_W, bool FUSE_RES>
-inline void launch_norm(const NormPlan& p, const NormArgs& a, cudaStream_t s) {
+inline void launch_norm(const NormPlan& p, const NormArgs& a, bool tma, cudaStream_t s) {
   switch (p.vpt) {
-    case 1: launch_norm_vpt<MODE, TIN, 1, HAS_W, FUSE_RES>(p, a, s); break;
-    case 2: launch_norm_vpt<MODE, TIN, 2, HAS_W, FUSE_RES>(p, a, s); break;
-    case 3: launch_norm_vpt<MODE, TIN, 3, HAS_W, FUSE_RES>(p, a, s); break;
-    case 4: launch_norm_vpt<MODE, TIN, 4, HAS_W, FUSE_RES>(p, a, s); break;
-    case 5: launch_norm_vpt<MODE, TIN, 5, HAS_W, FUSE_RES>(p, a, s); break;
-    case 6: launch_norm_vpt<MODE, TIN, 6, HAS_W, FUSE_RES>(p, a, s); break;
-    case 7: launch_norm_vpt<MODE, TIN, 7, HAS_W, FUSE_RES>(p, a, s); break;
-    default: launch_norm_vpt<MODE, TIN, 8, HAS_W, FUSE_RES>(p, a, s); break;
+    case 1: launch_norm_vpt<MODE, TIN, 1, HAS_W, FUSE_RES>(p, a, tma, s); break;
+    case 2: launch_norm_vpt<MODE, TIN, 2, HAS_W, FUSE_RES>(p, a, tma, s); break;
+    case 3: launch_norm_vpt<MODE, TIN, 3, HAS_W, FUSE_RES>(p, a, tma, s); break;
+    case 4: launch_norm_vpt<MODE, TIN, 4, HAS_W, FUSE_RES>(p, a, tma, s); break;
+    case 5: launch_norm_vpt<MODE, TIN, 5, HAS_W, FUSE_RES>(p, a, tma, s); break;
+    case 6: launch_norm_vpt<MODE, TIN, 6, HAS_W, FUSE_RES>(p, a, tma, s); break;
+    case 7: launch_norm_vpt<MODE, TIN, 7, HAS_W, FUSE_RES>(p, a, tma, s); break;
+    default: launch_norm_vpt<MODE, TIN, 8, HAS_W, FUSE_RES>(p, a, tma, s); break;
   }
 }
 
@@ -70,12 +96,14 @@ inline int run_norm(const char* name, NormArgs a, cudaStream_t s) {
   NormPlan p;
   // LayerNorm with an affine weight has no caller in the reference; it takes the generic kernel.
   if (!(MODE == 0 && a.w) && norm_vector_ok<TIN>(a) && plan_norm(a.nvec, a.rows, p)) {
-    a.rows_per_cta = p.rows_per_cta;
+    // The bulk-copy pipeline needs 16-byte rows: dim % 4 for fp32 rows (given), dim % 8 for bf16 rows.
+    const bool rows16 = (sizeof(TIN) == 4 || a.dim % 8 == 0) && (!FUSE_RES || a.dim % 8 == 0);
+    const bool tma = rows16 && tune(TUNE_NORM_PATH, 1) == 1 && a.rows >= 2;
     if constexpr (MODE == 1) {
-      if (a.w) launch_norm<MODE, TIN, true, FUSE_RES>(p, a, s);
-      else launch_norm<MODE, TIN, false, FUSE_RES>(p, a, s);
+      if (a.w) launch_norm<MODE, TIN, true, FUSE_RES>(p, a, tma, s);
+      else launch_norm<MODE, TIN, false, FUSE_RES>(p, a, tma, s);
     } else {
-      launch_norm<MODE, TIN, false, FUSE_RES>(p, a, s);
+      launch_norm<MODE, TIN, false, FUSE_RES>(p, a, tma, s);
     }
     return after_launch(name);
   }

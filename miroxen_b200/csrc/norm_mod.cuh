@@ -12,6 +12,7 @@
 // is read from HBM exactly once into registers; mean and variance come from those registers.
 #pragma once
 
+#include "bulk_copy.cuh"
 #include "common.cuh"
 
 namespace mxk {
@@ -32,6 +33,7 @@ struct NormArgs {
   MxkRowMod scale, shift;
   bf16* out;
   int rows_per_cta;
+  int* err;  // device error word (bounded waits report here)
 };
 
 // Sum over the CTA; `red` is a 16-float scratch that must not be reused before the next
@@ -149,10 +151,10 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
 #pragma unroll
       for (int k = 0; k < VPT; k++) {
         float4 yv = widen(yn[k]);
-        v[k].x += yv.x * G[k].x;
-        v[k].y += yv.y * G[k].y;
-        v[k].z += yv.z * G[k].z;
-        v[k].w += yv.w * G[k].w;
+        v[k].x = fmaf(yv.x, G[k].x, v[k].x);
+        v[k].y = fmaf(yv.y, G[k].y, v[k].y);
+        v[k].z = fmaf(yv.z, G[k].z, v[k].z);
+        v[k].w = fmaf(yv.w, G[k].w, v[k].w);
         if (on[k]) st_stream(reinterpret_cast<float4*>(xo + 4 * (k * T + tid)), v[k]);
       }
     }
@@ -192,6 +194,189 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
   }
 }
 
+// ---- bulk-copy (TMA) pipelined variant ----------------------------------------------------------
+//
+// Same arithmetic and the same thread-to-column mapping as norm_rows_kernel (MODE 2 = the gated
+// residual update alone, no norm and no bf16 output), but the rows arrive
+// through a ring of shared-memory stages filled by cp.async.bulk (one elected thread issues a
+// whole-row copy that completes on an mbarrier), so `stages` rows per CTA are in flight no matter
+// how many registers the math needs.  A stage is refilled right after the CTA-wide barrier of the
+// row's first reduction, by which point every thread has moved its part of the row to registers.
+//
+// Every wait on an mbarrier is bounded: when the limit is hit the CTA agrees on it through the
+// barrier vote, records kErrBulkTimeout in the device's error word, drains the copies it still has in
+// flight (bounded again) and returns.
+
+template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool EXACT>
+__global__ void __launch_bounds__(norm_max_threads(VPT))
+    norm_rows_tma_kernel(const NormArgs a, const int stages, const int stage_bytes) {
+  using raw_t = typename Raw4<TIN>::type;
+  extern __shared__ __align__(128) unsigned char dyn[];
+  __shared__ float red[2][16];
+  __shared__ __align__(8) unsigned long long bars[8];
+  const int tid = threadIdx.x, T = blockDim.x, nwarps = T >> 5;
+  const int64_t r0 = int64_t(blockIdx.x) * a.rows_per_cta;
+  const int64_t r1 = r0 + a.rows_per_cta < a.rows ? r0 + a.rows_per_cta : a.rows;
+  const TIN* x = static_cast<const TIN*>(a.x);
+  const float fdim = float(a.dim);
+  const unsigned xbytes = unsigned(a.dim) * sizeof(TIN);
+  const unsigned ybytes = FUSE_RES ? unsigned(a.dim) * 2u : 0u;
+  const unsigned yoff = (xbytes + 127u) & ~127u;  // y row sits after the x row inside a stage
+
+  if (tid == 0) {
+    for (int i = 0; i < stages; i++) mbar_init(smem_u32(&bars[i]), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  auto issue = [&](int64_t row, int st) {  // thread 0 only
+    const unsigned bar = smem_u32(&bars[st]);
+    const unsigned dst = smem_u32(dyn + size_t(st) * stage_bytes);
+    mbar_expect_tx(bar, xbytes + ybytes);
+    bulk_g2s(dst, x + row * a.dim, xbytes, bar);
+    if (FUSE_RES) bulk_g2s(dst + yoff, a.y + row * a.dim, ybytes, bar);
+  };
+  if (tid == 0)
+    for (int i = 0; i < stages && r0 + i < r1; i++) issue(r0 + i, i);
+
+  bool on[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; k++) on[k] = EXACT || (k * T + tid < a.nvec);
+
+  float4 A[VPT], B[VPT], W[HAS_W ? VPT : 1], G[FUSE_RES ? VPT : 1];
+  int cur_set = -1;
+#pragma unroll
+  for (int k = 0; k < VPT; k++) {
+    if (HAS_W) W[k] = on[k] ? *reinterpret_cast<const float4*>(a.w + 4 * (k * T + tid))
+                            : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  int st = 0;
+  unsigned phase = 0;
+  int parity = 0;
+  bool failed = false;
+  int64_t row = r0;
+  for (; row < r1; row++) {
+    const int set = (row < a.scale.prefix_len ? 1 : 0) | (row < a.shift.prefix_len ? 2 : 0) |
+                    (FUSE_RES && row < a.gate.prefix_len ? 4 : 0);
+    if (set != cur_set) {
+      cur_set = set;
+      const float* sc = a.scale.target ? pick(a.scale, row) : nullptr;
+      const float* sh = a.shift.target ? pick(a.shift, row) : nullptr;
+      const float* gt = FUSE_RES && a.gate.target ? pick(a.gate, row) : nullptr;
+#pragma unroll
+      for (int k = 0; k < VPT; k++) {
+        const int c = 4 * (k * T + tid);
+        A[k] = make_float4(1.f, 1.f, 1.f, 1.f);
+        B[k] = make_float4(-0.f, -0.f, -0.f, -0.f);
+        if (on[k]) {
+          if (sc) {
+            float4 v = *reinterpret_cast<const float4*>(sc + c);
+            A[k] = make_float4(1.f + v.x, 1.f + v.y, 1.f + v.z, 1.f + v.w);
+          }
+          if (sh) B[k] = *reinterpret_cast<const float4*>(sh + c);
+        }
+        if (FUSE_RES) {
+          G[k] = make_float4(1.f, 1.f, 1.f, 1.f);
+          if (gt && on[k]) {
+            float4 g = *reinterpret_cast<const float4*>(gt + c);
+            G[k] = a.gate_tanh ? make_float4(tanhf(g.x), tanhf(g.y), tanhf(g.z), tanhf(g.w)) : g;
+          }
+        }
+      }
+    }
+
+    const bool arrived = mbar_wait(smem_u32(&bars[st]), phase);
+    const unsigned char* sx = dyn + size_t(st) * stage_bytes;
+    float4 v[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; k++) {
+      v[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (on[k] && arrived) v[k] = widen(reinterpret_cast<const raw_t*>(sx)[k * T + tid]);
+    }
+    if (FUSE_RES) {
+      float* xo = a.xw + row * a.dim;
+#pragma unroll
+      for (int k = 0; k < VPT; k++) {
+        float4 yv = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (on[k] && arrived) yv = widen(reinterpret_cast<const uint2*>(sx + yoff)[k * T + tid]);
+        v[k].x = fmaf(yv.x, G[k].x, v[k].x);
+        v[k].y = fmaf(yv.y, G[k].y, v[k].y);
+        v[k].z = fmaf(yv.z, G[k].z, v[k].z);
+        v[k].w = fmaf(yv.w, G[k].w, v[k].w);
+        if (on[k] && arrived) st_stream(reinterpret_cast<float4*>(xo + 4 * (k * T + tid)), v[k]);
+      }
+    }
+
+    if constexpr (MODE == 2) {
+      // residual update only: nothing to reduce, the barrier is just the stage hand-over + vote
+      const bool all_ok = nwarps == 1 ? bool(__all_sync(0xffffffffu, arrived)) : __syncthreads_and(arrived) != 0;
+      if (!all_ok) {
+        failed = true;
+        break;
+      }
+      if (tid == 0 && row + stages < r1) issue(row + stages, st);
+      if (++st == stages) st = 0, phase ^= 1u;
+    } else {
+      // first reduction: its barrier also tells every thread whether all of them saw the row arrive
+      bool all_ok;
+      float mean = 0.f, ss = 0.f;
+      if (MODE == 0) {
+        float s = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; k++) s += (v[k].x + v[k].y) + (v[k].z + v[k].w);
+        mean = cta_sum_vote(s, red[0], nwarps, arrived, all_ok) / fdim;
+      }
+#pragma unroll
+      for (int k = 0; k < VPT; k++) {
+        float dx = v[k].x - mean, dy = v[k].y - mean, dz = v[k].z - mean, dw = v[k].w - mean;
+        float q = (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        ss += (EXACT || MODE == 1 || on[k]) ? q : 0.f;
+      }
+      float total;
+      if (MODE == 0) {
+        total = cta_sum(ss, red[1], nwarps);
+      } else {
+        total = cta_sum_vote(ss, red[parity], nwarps, arrived, all_ok);
+        parity ^= 1;
+      }
+      if (!all_ok) {
+        failed = true;
+        break;
+      }
+      // every thread has its part of the row in registers: the stage can take row + stages
+      if (tid == 0 && row + stages < r1) issue(row + stages, st);
+      if (++st == stages) st = 0, phase ^= 1u;
+
+      const float rstd = rsqrtf(total / fdim + a.eps);
+      bf16* orow = a.out + row * a.dim;
+#pragma unroll
+      for (int k = 0; k < VPT; k++) {
+        float o[4] = {(v[k].x - mean) * rstd, (v[k].y - mean) * rstd, (v[k].z - mean) * rstd,
+                      (v[k].w - mean) * rstd};
+        if (HAS_W) o[0] *= W[k].x, o[1] *= W[k].y, o[2] *= W[k].z, o[3] *= W[k].w;
+        o[0] = o[0] * A[k].x + B[k].x;
+        o[1] = o[1] * A[k].y + B[k].y;
+        o[2] = o[2] * A[k].z + B[k].z;
+        o[3] = o[3] * A[k].w + B[k].w;
+        if (on[k]) st_stream(reinterpret_cast<uint2*>(orow + 4 * (k * T + tid)), pack4(o));
+      }
+    }
+  }
+
+  if (failed && tid == 0) {
+    if (a.err) atomicExch(a.err, kErrBulkTimeout);
+    // Copies issued for rows [row, min(r1, row + stages)) may still be in flight into this CTA's
+    // shared memory: give each a bounded chance to land before the CTA goes away.
+    int s2 = st;
+    unsigned ph = phase;
+    for (int64_t r = row; r < r1 && r < row + stages; r++) {
+      mbar_wait(smem_u32(&bars[s2]), ph);
+      if (++s2 == stages) s2 = 0, ph ^= 1u;
+    }
+  }
+}
+
 // Any dim, any alignment: one CTA per row, three sweeps over the row (the later sweeps hit L1/L2).
 template <int MODE, class TIN, bool FUSE_RES>
 __global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a) {
@@ -209,9 +394,8 @@ __global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a
     const bf16* yr = a.y + row * a.dim;
     float* xo = a.xw + row * a.dim;
     for (int i = tid; i < a.dim; i += T) {
-      float v = bf16_to_f(yr[i]);
-      if (gt) v *= a.gate_tanh ? tanhf(gt[i]) : gt[i];
-      xo[i] = ldx(i) + v;  // the same thread re-reads this element in the sweeps below
+      const float g = gt ? (a.gate_tanh ? tanhf(gt[i]) : gt[i]) : 1.f;
+      xo[i] = fmaf(bf16_to_f(yr[i]), g, ldx(i));  // the same thread re-reads this element in the sweeps below
     }
   }
   float mean = 0.f;
@@ -238,12 +422,10 @@ __global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a
   }
 }
 
-// Launch plan shared by every instantiation: threads per CTA, vectors per thread, grid.
+// Launch plan shared by every instantiation: threads per CTA and vectors per thread.
 struct NormPlan {
   int threads, vpt;
   bool exact;
-  int rows_per_cta;
-  unsigned grid;
 };
 
 }  // namespace mxk

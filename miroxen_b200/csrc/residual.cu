@@ -52,10 +52,10 @@ __device__ __forceinline__ void res_rows(float* __restrict__ x, const bf16* __re
 #pragma unroll
         for (int q = 0; q < CPT / 4; q++) {
           float4 v = xv[u][q];
-          v.x += f[4 * q + 0] * g[4 * q + 0];
-          v.y += f[4 * q + 1] * g[4 * q + 1];
-          v.z += f[4 * q + 2] * g[4 * q + 2];
-          v.w += f[4 * q + 3] * g[4 * q + 3];
+          v.x = fmaf(f[4 * q + 0], g[4 * q + 0], v.x);
+          v.y = fmaf(f[4 * q + 1], g[4 * q + 1], v.y);
+          v.z = fmaf(f[4 * q + 2], g[4 * q + 2], v.z);
+          v.w = fmaf(f[4 * q + 3], g[4 * q + 3], v.w);
           st_stream(reinterpret_cast<float4*>(x + off) + q, v);
         }
       }
@@ -105,12 +105,12 @@ __global__ void __launch_bounds__(256)
   const int i = blockIdx.y * blockDim.x + threadIdx.x;
   if (i >= dim) return;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-    float v = bf16_to_f(y[row * dim + i]);
+    float g = 1.f;
     if (gate.target) {
       const float gv = pick(gate, row)[i];
-      v *= gate_tanh ? tanhf(gv) : gv;
+      g = gate_tanh ? tanhf(gv) : gv;
     }
-    x[row * dim + i] += v;
+    x[row * dim + i] = fmaf(bf16_to_f(y[row * dim + i]), g, x[row * dim + i]);
   }
 }
 
@@ -134,16 +134,28 @@ int mxk_gated_residual(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, M
   const int threads = tune(TUNE_RES_THREADS, 128);
   const int rpc = tune(TUNE_RES_ROWS_PER_CTA, 8);
   const int64_t nchunks = ceil_div(rows, rpc);
+  // Preferred: the bulk-copy pipelined row kernel in its residual-only mode.
+  if (tune(TUNE_RES_PATH, 1) == 1 && dim % 8 == 0 && dim <= 8192 && rows >= 2 && aligned(x, 16) && aligned(y, 16) && gate_ok) {
+    NormArgs a{};
+    a.x = x, a.xw = x, a.y = yb, a.gate = gate, a.gate_tanh = gate_tanh;
+    a.rows = rows, a.dim = int(dim), a.nvec = int(dim / 4);
+    NormPlan p;
+    if (plan_norm(a.nvec, rows, p)) {
+      launch_norm<2, float, false, true>(p, a, true, s);
+      return after_launch("gated_residual");
+    }
+  }
+  // grid.y covers the columns, grid.x walks row chunks; together exactly one resident wave
+  auto wave_x = [&](auto kern, unsigned gy) {
+    int64_t gx = ceil_div(int64_t(sm_count()) * resident_ctas(kern, threads), gy);
+    return unsigned(gx > nchunks ? nchunks : gx < 1 ? 1 : gx);
+  };
   if (dim % 8 == 0 && aligned(x, 16) && aligned(y, 16) && gate_ok) {
     const unsigned gy = unsigned(ceil_div(dim / 8, threads));
-    int64_t gx = ceil_div(int64_t(sm_count()) * 2048 / threads, gy);
-    if (gx > nchunks) gx = nchunks;
-    gated_residual_kernel<8><<<dim3(unsigned(gx), gy), threads, 0, s>>>(x, yb, rows, int(dim), gate, gate_tanh, rpc);
+    gated_residual_kernel<8><<<dim3(wave_x(gated_residual_kernel<8>, gy), gy), threads, 0, s>>>(x, yb, rows, int(dim), gate, gate_tanh, rpc);
   } else if (dim % 4 == 0 && aligned(x, 16) && aligned(y, 8) && gate_ok) {
     const unsigned gy = unsigned(ceil_div(dim / 4, threads));
-    int64_t gx = ceil_div(int64_t(sm_count()) * 2048 / threads, gy);
-    if (gx > nchunks) gx = nchunks;
-    gated_residual_kernel<4><<<dim3(unsigned(gx), gy), threads, 0, s>>>(x, yb, rows, int(dim), gate, gate_tanh, rpc);
+    gated_residual_kernel<4><<<dim3(wave_x(gated_residual_kernel<4>, gy), gy), threads, 0, s>>>(x, yb, rows, int(dim), gate, gate_tanh, rpc);
   } else {
     const unsigned gy = unsigned(ceil_div(dim, 256));
     int64_t gx = rows < int64_t(sm_count()) * 16 ? rows : int64_t(sm_count()) * 16;

@@ -15,6 +15,13 @@ enum TuneKey {
   TUNE_EW_THREADS,         // CTA size of the flat elementwise kernels
   TUNE_EW_UNROLL,          // independent 16-byte vectors per thread (1, 2, 4 or 8)
   TUNE_ACT_ROWS_PER_CTA,   // rows each silu_mul CTA walks
+  TUNE_NORM_PATH,          // 1 bulk-copy (TMA) pipelined row kernel, 2 register-prefetch row kernel
+  TUNE_NORM_STAGES,        // rows in flight per CTA of the bulk-copy kernel (2..8)
+  TUNE_ROPE_PATH,          // 1 bulk-copy (TMA) pipelined head kernel, 2 register head kernel
+  TUNE_ROPE_STAGES,        // tokens in flight per CTA of the bulk-copy head kernel (2..8)
+  TUNE_EW_CTAS_PER_SM,     // CTAs per SM the flat elementwise grid is sized for
+  TUNE_RES_PATH,           // 1 bulk-copy pipelined gated_residual, 2 column-strip register kernel
+  TUNE_ROPE_TOKENS,        // tokens per stage of the bulk-copy head kernel (1..16)
   TUNE_COUNT
 };
 

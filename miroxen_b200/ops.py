@@ -22,7 +22,7 @@ __all__ = [
     "gated_residual", "add_inplace_bf16", "head_norm_rope", "silu_mul", "gelu_tanh_inplace", "gelu_erf_inplace",
     "scatter_rows", "silu_inplace_f32", "add_bias_bf16", "add_bias_f32", "f32_to_bf16", "bf16_to_f32", "axpy_f32",
     "axpby_f32", "gated_residual_norm", "qkv_norm_rope", "HeadSpec", "dit_block_ops", "BlockArgs", "RowMod",
-    "HostPipeline", "OpTimes", "launch_count", "reset_launch_count", "set_tuning",
+    "HostPipeline", "OpTimes", "device_error", "launch_count", "reset_launch_count", "set_tuning",
 ]
 
 
@@ -198,6 +198,13 @@ class HostPipeline:
             self.close()
         except Exception:
             pass
+
+
+def device_error(clear: bool = True) -> int:
+    """0, or the code a kernel left when one of its bounded waits ran out (synchronises)."""
+    v = C.c_int(0)
+    check(lib().mxk_device_error(C.byref(v), int(clear)))
+    return v.value
 
 
 def launch_count() -> int:

@@ -12,13 +12,22 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def mx():
+@pytest.fixture(scope="module", params=["bulk_copy", "registers"])
+def mx(request):
+    """Every test runs twice: with the bulk-copy (TMA) pipelined row / head kernels, which are the
+    default, and with the register-prefetch kernels that serve the shapes the bulk copies cannot."""
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     import miroxen_b200 as m
     m.lib()  # raises if libmxk.so is missing - there is no fallback
-    return m
+    path = 1 if request.param == "bulk_copy" else 2
+    m.set_tuning("norm_path", path)
+    m.set_tuning("rope_path", path)
+    yield m
+    torch.cuda.synchronize()
+    assert m.device_error() == 0, "a kernel's bounded wait ran out"
+    m.set_tuning("norm_path", 0)
+    m.set_tuning("rope_path", 0)
 
 
 def dev_mod(mx, keep, target=None, prefix=None, prefix_len=0):
