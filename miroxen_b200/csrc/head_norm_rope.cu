@@ -310,7 +310,9 @@ __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
   if (warp == n_cons_warps) {
     if (lane == 0) {
       int st = 0;
-      unsigned ph = 1;  // parity of the `empty` phase to wait for; flips each trip round the ring
+      // Parity of the `empty` phase to wait for: the k-th refill of a stage (k >= 1) follows the
+      // completion of its phase k - 1, so the first wait uses parity 0 and it flips per trip after that.
+      unsigned ph = 0;
       int64_t s0 = g_begin * a.tpc;
       for (int it = 0; it < my_groups; it++, s0 += a.tpc) {
         if (it >= a.stages && !mbar_wait(smem_u32(&empty[st]), ph)) {
@@ -495,7 +497,7 @@ bool pipe_plan(RopeArgs& a) {
   const int half = a.rot / 2;
   if (a.mode != MXK_ROPE_NONE && half % 4) return false;
   const int lph = a.D / 8;
-  int max_threads = tune(TUNE_ROPE_THREADS, 512);
+  int max_threads = tune(TUNE_ROPE_THREADS, 128);  // small CTAs, many per SM: measured best on B200
   if (max_threads > 512) max_threads = 512;
   if (max_threads < lph) max_threads = lph;
   int passes = 1;
@@ -525,7 +527,7 @@ bool pipe_plan(RopeArgs& a) {
   int per_token = 2 * half * 4;
   for (int i = 0; i < a.n_seg; i++) per_token += a.seg[i].token_bytes;
   int tpc = tune(TUNE_ROPE_TOKENS, 0);
-  if (tpc <= 0) tpc = 24576 / per_token;
+  if (tpc <= 0) tpc = 16384 / per_token;
   if (tpc < 1) tpc = 1;
   if (tpc > 16) tpc = 16;
   a.tpc = tpc;
@@ -540,7 +542,7 @@ bool pipe_plan(RopeArgs& a) {
   off += (tpc * half * 4 + 127) & ~127;
   a.stage_bytes = off;
   int stages = tune(TUNE_ROPE_STAGES, 0);
-  if (stages <= 0) stages = 73728 / a.stage_bytes;
+  if (stages <= 0) stages = 2;
   if (stages < 2) stages = 2;
   if (stages > 8) stages = 8;
   a.stages = stages;

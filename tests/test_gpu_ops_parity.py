@@ -375,3 +375,96 @@ def test_two_shards_equal_one(mx):
     mx.layernorm_mod(x[r0:], rows - r0, dim, 1e-6, mx.row_mod(sc_t, sc_p, plen - r0), None, two[r0:])
     torch.cuda.synchronize()
     assert torch.equal(one.view(torch.int16), two.view(torch.int16))
+
+
+@pytest.mark.parametrize("op", ["layernorm", "rmsnorm", "fused", "residual"])
+@pytest.mark.parametrize("stages", [2, 3])
+def test_row_pipeline_many_trips(mx, op, stages):
+    """Enough rows per CTA that every shared-memory stage of the bulk-copy pipeline is refilled many
+    times (one CTA per SM, 2-3 stages, thousands of rows), with the prefix switch in the middle."""
+    rows, dim, plen = 4001, 3072, 1777
+    g = H.rng(stages * 10 + len(op))
+    x = H.normal_f32(g, (rows, dim), 1.0, 0.2)
+    y = H.normal_bf16(g, (rows, dim))
+    sc_t, sc_p, sh = H.normal_f32(g, dim, 0.3), H.normal_f32(g, dim, 0.3), H.normal_f32(g, dim, 0.3)
+    gt, gp = H.normal_f32(g, dim, 0.7), H.normal_f32(g, dim, 0.7)
+    w = H.normal_f32(g, dim, 0.1, 1.0)
+    keep = []
+    dsc, dsh, dg = dev_mod(mx, keep, sc_t, sc_p, plen), dev_mod(mx, keep, sh), dev_mod(mx, keep, gt, gp, plen)
+    osc, osh, og = orc.mod(sc_t, sc_p, plen), orc.mod(sh), orc.mod(gt, gp, plen)
+    orc.set_threads(8)
+    mx.set_tuning("norm_stages", stages)
+    mx.set_tuning("norm_ctas_per_sm", 1)
+    try:
+        xd = H.Guarded(torch, (rows, dim), torch.float32, fill=torch.from_numpy(x))
+        out = H.Guarded(torch, (rows, dim), torch.bfloat16)
+        if op == "layernorm":
+            ref = orc.layernorm_mod(x, 1e-6, osc, osh)
+            mx.layernorm_mod(xd.t, rows, dim, 1e-6, dsc, dsh, out.t)
+        elif op == "rmsnorm":
+            ref = orc.rmsnorm_mod(x, 1e-6, w, osc, osh)
+            mx.rmsnorm_mod(xd.t, rows, dim, 1e-6, H.to_dev(torch, w), dsc, dsh, out.t)
+        elif op == "fused":
+            xr = orc.gated_residual(x.copy(), y, og, 1)
+            ref = orc.layernorm_mod(xr, 1e-6, osc, osh)
+            mx.gated_residual_norm(xd.t, H.to_dev(torch, y), rows, dim, dg, 1, 0, 1e-6, None, dsc, dsh, out.t)
+        else:
+            xr = orc.gated_residual(x.copy(), y, og, 1)
+            mx.gated_residual(xd.t, H.to_dev(torch, y), rows, dim, dg, 1)
+        torch.cuda.synchronize()
+        xd.check(op), out.check(op)
+        if op != "residual":
+            H.assert_bf16_close(H.bits(out.t), ref, op)
+        if op in ("fused", "residual"):
+            H.assert_f32_close(xd.t.cpu().numpy(), xr, op + " x")
+    finally:
+        orc.set_threads(1)
+        mx.set_tuning("norm_stages", 0)
+        mx.set_tuning("norm_ctas_per_sm", 0)
+
+
+@pytest.mark.parametrize("tokens,stages,threads", [(1, 2, 128), (3, 2, 512), (2, 4, 192)])
+@pytest.mark.parametrize("layout", ["dense_qk", "packed_qkv"])
+def test_head_pipeline_many_trips(mx, tokens, stages, threads, layout):
+    """The head pipeline with every stage refilled many times, one and several tokens per stage,
+    one and several passes over the heads, separate and packed projections."""
+    S, Hh, D = 2999, 24, 128
+    I = Hh * D
+    g = H.rng(tokens * 100 + stages * 10 + threads)
+    ang = g.uniform(-3, 3, (S, D // 2)).astype(np.float32)
+    cos, sin = np.cos(ang).astype(np.float32), np.sin(ang).astype(np.float32)
+    wq, wk = H.normal_f32(g, D, 0.05, 1.0), H.normal_f32(g, D, 0.05, 1.0)
+    orc.set_threads(8)
+    mx.set_tuning("rope_stages", stages)
+    mx.set_tuning("rope_tokens", tokens)
+    mx.set_tuning("rope_threads", threads)
+    mx.set_tuning("rope_ctas_per_sm", 1)
+    try:
+        cd, sd = H.to_dev(torch, cos), H.to_dev(torch, sin)
+        wqd, wkd = H.to_dev(torch, wq), H.to_dev(torch, wk)
+        outs = [H.Guarded(torch, (S, Hh, D), torch.bfloat16) for _ in range(3)]
+        if layout == "dense_qk":
+            q, k = H.normal_bf16(g, (S, I)), H.normal_bf16(g, (S, I))
+            refs = [orc.head_norm_rope(q, S, I, 0, Hh, D, wq, 1e-6, cos, sin, D, 1),
+                    orc.head_norm_rope(k, S, I, 0, Hh, D, wk, 1e-6, cos, sin, D, 1)]
+            qd, kd = H.to_dev(torch, q), H.to_dev(torch, k)
+            mx.head_norm_rope(qd, S, I, 0, Hh, D, wqd, 1e-6, cd, sd, D, 1, outs[0].t)
+            mx.qkv_norm_rope([mx.HeadSpec(qd, I, 0, wqd, outs[2].t, D, 1), mx.HeadSpec(kd, I, 0, wkd, outs[1].t, D, 1)],
+                             S, Hh, D, 1e-6, cd, sd)
+            refs.append(refs[0])
+        else:
+            qkv = H.normal_bf16(g, (S, 3 * I))
+            refs = [orc.head_norm_rope(qkv, S, 3 * I, 0, Hh, D, wq, 1e-6, cos, sin, D, 2),
+                    orc.head_norm_rope(qkv, S, 3 * I, I, Hh, D, wk, 1e-6, cos, sin, D, 2),
+                    orc.head_norm_rope(qkv, S, 3 * I, 2 * I, Hh, D, None, 0.0, None, None, 0, 0)]
+            d = H.to_dev(torch, qkv)
+            mx.qkv_norm_rope([mx.HeadSpec(d, 3 * I, 0, wqd, outs[0].t, D, 2), mx.HeadSpec(d, 3 * I, I, wkd, outs[1].t, D, 2),
+                              mx.HeadSpec(d, 3 * I, 2 * I, None, outs[2].t, 0, 0)], S, Hh, D, 1e-6, cd, sd)
+        torch.cuda.synchronize()
+        for o, r in zip(outs, refs):
+            o.check("head pipeline")
+            H.assert_bf16_close(H.bits(o.t), r, f"head pipeline {layout}")
+    finally:
+        orc.set_threads(1)
+        for k in ("rope_stages", "rope_tokens", "rope_threads", "rope_ctas_per_sm"):
+            mx.set_tuning(k, 0)
