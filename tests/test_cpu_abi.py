@@ -99,3 +99,37 @@ def test_host_builders_match_oracle(L):
     hg = np.empty(30, np.float32)
     assert lib.mxk_h3_spatial_grid_host(60, 60, 104, hg.ctypes.data) == 0
     assert np.array_equal(hg, pos[512:512 + 30 * 52:52, 1])
+
+
+def test_cpp_shim_compiles_and_links(tmp_path, L):
+    """include/mx_ops.h (the reference's namespace mx signatures over the C ABI) builds with g++ against
+    libmxk and reports a bad argument as std::runtime_error, like the reference's MX_CHECK."""
+    import shutil
+    if not shutil.which("g++") or not Path("/usr/local/cuda/include/cuda_runtime.h").exists():
+        pytest.skip("no g++ / CUDA headers")
+    src = tmp_path / "shim.cpp"
+    src.write_text(r'''
+#include <cstdio>
+#include <cstring>
+#include "mx_ops.h"
+int main() {
+  mx::layernorm_mod(nullptr, 0, 3072, 1e-6f, mx::RowMod{}, mx::RowMod{}, nullptr, nullptr);   // rows == 0: no-op
+  mx::gated_residual(nullptr, nullptr, -1, 3072, mx::RowMod{}, 1, nullptr);
+  try {
+    mx::head_norm_rope((const mx::bf16*)16, 4, 1024, 0, 8, 7, nullptr, 1e-6f, nullptr, nullptr, 4, mx::ROPE_HALF,
+                       (mx::bf16*)16, nullptr);
+  } catch (const std::runtime_error& e) {
+    std::printf("THROWN %s\n", e.what());
+    return std::strstr(e.what(), "head_norm_rope") ? 0 : 2;
+  }
+  return 1;
+}
+''')
+    exe = tmp_path / "shim"
+    lib = L.lib_path()
+    r = subprocess.run(["g++", "-std=c++17", str(src), "-I", str(ROOT / "include"), "-I", "/usr/local/cuda/include",
+                        "-L", str(lib.parent), "-lmxk", f"-Wl,-rpath,{lib.parent}", "-o", str(exe)],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and "THROWN" in r.stdout, r.stdout + r.stderr
