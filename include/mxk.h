@@ -284,6 +284,29 @@ void mxk_host_pipeline_destroy(MxkHostPipeline* p);
 int mxk_dit_block_ops_host(MxkHostPipeline* p, const MxkBlockArgs* a, int64_t* h2d_bytes,
                            int64_t* d2h_bytes);
 
+/* No counterpart in the reference.  mxk_dit_block_ops_host for callers that must not allocate
+ * device memory: code that runs after start-up inside a fixed memory budget (an engine that sized its
+ * arena once and may never grow it, a plugin loaded into a host process that forbids cudaMalloc on its
+ * threads) or at a point where an allocation would synchronise the whole device.  It runs the same op
+ * sequence on HOST buffers, one chunk of rows at a time, on the caller's stream and without overlap
+ * between copies and kernels; its device staging is a fixed array of MXK_STATIC_STAGE_MIB MiB inside
+ * the library's device image (mxk_static_stage_bytes() returns the size; every GPU that loads the
+ * library holds it until the process exits).  It calls no cudaMalloc / cudaFree and creates no streams
+ * or events.
+ *  - Limit: 64 rows of staging must fit the array (for a 3072-wide block one row stages about 85 KB);
+ *    wider blocks return MXK_ERR_TOO_LARGE.  The number of rows is not limited.
+ *  - The first call on each device looks the array's address up (cudaGetSymbolAddress, with that
+ *    device current); make that first call before any stream capture begins.
+ *  - All calls on a device share the one array.  It keeps the previous call's bytes, which is harmless:
+ *    every byte a chunk's kernels read is first written by that chunk's own copies or kernels, so
+ *    nothing has to start at zero.  Two calls whose work overlaps on the GPU (different streams or
+ *    threads) race on the array and corrupt each other's results: serialise them.
+ * `a` is laid out as for mxk_dit_block_ops_host; returns after the results are in host memory. */
+#define MXK_STATIC_STAGE_MIB 32
+int64_t mxk_static_stage_bytes(void);
+int mxk_dit_block_ops_host_static(const MxkBlockArgs* a, mxk_stream_t stream, int64_t* h2d_bytes,
+                                  int64_t* d2h_bytes);
+
 /* Reads (and with clear != 0 resets) the current device's error word: 0, or 1 when a kernel's bounded
  * wait on a bulk copy ran out and the kernel returned early (its outputs are then incomplete).
  * Synchronises with the device. */

@@ -93,6 +93,8 @@ PROTOTYPES = {
     "mxk_op_times_read": (_I, [_P, C.POINTER(C.c_float), _I]),
     "mxk_host_pipeline_create": (_I, [_I64, _I64, _I64, _I, _I, _I, _I, _I, C.POINTER(_P)]),
     "mxk_host_pipeline_destroy": (None, [_P]),
+    "mxk_static_stage_bytes": (_I64, []),
+    "mxk_dit_block_ops_host_static": (_I, [C.POINTER(BlockArgs), _P, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
     "mxk_dit_block_ops_host": (_I, [_P, C.POINTER(BlockArgs), C.POINTER(C.c_int64), C.POINTER(C.c_int64)]),
 }
 

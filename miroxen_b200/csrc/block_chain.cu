@@ -2,6 +2,7 @@
 // attention calls (reference: src/models/qwen_image/dit.cpp:245-315 run_block,
 // src/models/minimax_h3/dit.cpp:183-248 attn_mlp), on device buffers and - streamed in row
 // chunks over three streams - on host buffers.
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
@@ -340,6 +341,154 @@ int mxk_dit_block_ops_host(MxkHostPipeline* p, const MxkBlockArgs* a, int64_t* h
     MXK_CU(cudaEventRecord(s.d2h_done, p->d2h));
   }
   MXK_CU(cudaStreamSynchronize(p->d2h));
+#undef MXK_CU
+  if (h2d_bytes) *h2d_bytes = up;
+  if (d2h_bytes) *d2h_bytes = down;
+  return MXK_OK;
+}
+
+
+// ---- block ops on host buffers without any allocation -------------------------------------------
+//
+// Staging for mxk_dit_block_ops_host_static.  The array lives in the library's device image: every
+// GPU whose context loads libmxk holds these bytes until the process exits.  In host code the
+// name g_static_stage is only a handle for the symbol - it is not a device address and must never
+// be handed to a kernel or a copy; static_stage_base() asks the runtime for the real address.
+constexpr size_t kStaticStageBytes = size_t(MXK_STATIC_STAGE_MIB) << 20;
+static __device__ __align__(256) unsigned char g_static_stage[kStaticStageBytes];
+
+namespace {
+constexpr int kStaticMaxDevices = 64;
+std::atomic<unsigned char*> g_static_base[kStaticMaxDevices];
+
+// Device address of g_static_stage on the CURRENT device; looked up once per device (with that
+// device current, as cudaGetSymbolAddress answers for the current device) and then cached.
+int static_stage_base(unsigned char** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "dit_block_ops_host_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kStaticMaxDevices) return fail(MXK_ERR_INVALID_ARG, "dit_block_ops_host_static: device ordinal %d", dev);
+  unsigned char* p = g_static_base[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void* addr = nullptr;
+    e = cudaGetSymbolAddress(&addr, g_static_stage);
+    if (e != cudaSuccess || !addr)
+      return fail(MXK_ERR_CUDA, "dit_block_ops_host_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    p = static_cast<unsigned char*>(addr);
+    g_static_base[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return MXK_OK;
+}
+}  // namespace
+
+int64_t mxk_static_stage_bytes(void) { return int64_t(kStaticStageBytes); }
+
+int mxk_dit_block_ops_host_static(const MxkBlockArgs* a, mxk_stream_t stream, int64_t* h2d_bytes,
+                                  int64_t* d2h_bytes) {
+  if (int rc = check_block(a)) return rc;
+  if (a->rot < 0 || a->rot > a->D) return fail(MXK_ERR_INVALID_ARG, "dit_block_ops_host_static: rot=%d", a->rot);
+  const bool rope = a->rot > 0 && a->rope_mode != MXK_ROPE_NONE;
+  if (rope && (!a->cos || !a->sin)) return fail(MXK_ERR_INVALID_ARG, "dit_block_ops_host_static: rotary mode needs cos and sin");
+  const bool with_v = a->v_in != nullptr;
+  const int64_t dim = a->dim, inner = int64_t(a->H) * a->D, F = a->F, half = a->rot / 2;
+  // bytes of staging one row needs, each array rounded up so that every array of a chunk starts on
+  // a 256-byte boundary whatever the chunk's row count (the row count is kept a multiple of 64)
+  auto pad = [](int64_t b) { return (b + 3) / 4 * 4; };  // per row: multiples of 4 bytes x 64 rows = 256
+  const int64_t bx = pad(dim * 4), bh = pad(dim * 2), bi = pad(inner * 2), bf = pad(F * 2),
+                bf2 = a->act_mode == 1 ? pad(2 * F * 2) : 0, bt = pad((half > 0 ? half : 1) * 4);
+  const int64_t per_row = bx + 4 * bh + (with_v ? 6 : 4) * bi + bf + bf2 + 2 * bt;
+  int64_t chunk = int64_t(kStaticStageBytes) / per_row / 64 * 64;
+  if (chunk < 64)
+    return fail(MXK_ERR_TOO_LARGE,
+                "dit_block_ops_host_static: one row stages %lld bytes; 64 rows do not fit the %lld-byte static "
+                "staging array (use mxk_dit_block_ops_host, whose pipeline allocates its own)",
+                (long long)per_row, (long long)kStaticStageBytes);
+  unsigned char* base = nullptr;
+  if (int rc = static_stage_base(&base)) return rc;
+  cudaStream_t s = as_stream(stream);
+
+  unsigned char* c = base;
+  auto take = [&](int64_t row_bytes) { unsigned char* r = c; c += row_bytes * chunk; return r; };
+  float* sx = reinterpret_cast<float*>(take(bx));
+  mxk_bf16* sh1 = reinterpret_cast<mxk_bf16*>(take(bh));
+  mxk_bf16* sh2 = reinterpret_cast<mxk_bf16*>(take(bh));
+  mxk_bf16* sattn = reinterpret_cast<mxk_bf16*>(take(bh));
+  mxk_bf16* smlp = reinterpret_cast<mxk_bf16*>(take(bh));
+  mxk_bf16* sq_in = reinterpret_cast<mxk_bf16*>(take(bi));
+  mxk_bf16* sk_in = reinterpret_cast<mxk_bf16*>(take(bi));
+  mxk_bf16* sq_out = reinterpret_cast<mxk_bf16*>(take(bi));
+  mxk_bf16* sk_out = reinterpret_cast<mxk_bf16*>(take(bi));
+  mxk_bf16* sv_in = with_v ? reinterpret_cast<mxk_bf16*>(take(bi)) : nullptr;
+  mxk_bf16* sv_out = with_v ? reinterpret_cast<mxk_bf16*>(take(bi)) : nullptr;
+  mxk_bf16* sact = reinterpret_cast<mxk_bf16*>(take(bf));
+  mxk_bf16* sact2 = a->act_mode == 1 ? reinterpret_cast<mxk_bf16*>(take(bf2)) : nullptr;
+  float* scos = reinterpret_cast<float*>(take(bt));
+  float* ssin = reinterpret_cast<float*>(take(bt));
+
+  int64_t up = 0, down = 0;
+  cudaError_t e = cudaSuccess;
+#define MXK_CU(call)                                                                                \
+  do {                                                                                              \
+    if ((e = (call)) != cudaSuccess) {                                                              \
+      cudaStreamSynchronize(s);                                                                     \
+      return fail(MXK_ERR_CUDA, "dit_block_ops_host_static: %s: %s", #call, cudaGetErrorString(e)); \
+    }                                                                                               \
+  } while (0)
+  for (int64_t r0 = 0; r0 < a->rows; r0 += chunk) {
+    const int64_t n = a->rows - r0 < chunk ? a->rows - r0 : chunk;
+    auto in = [&](void* dst, const void* src, int64_t bytes) {
+      up += bytes;
+      return cudaMemcpyAsync(dst, src, size_t(bytes), cudaMemcpyHostToDevice, s);
+    };
+    auto in2d = [&](mxk_bf16* dst, const mxk_bf16* src, int64_t col0) {
+      up += n * inner * 2;
+      return cudaMemcpy2DAsync(dst, size_t(inner) * 2, src + r0 * a->qkv_stride + col0, size_t(a->qkv_stride) * 2,
+                               size_t(inner) * 2, size_t(n), cudaMemcpyHostToDevice, s);
+    };
+    // Everything a kernel of this chunk reads is written first, by these copies or by an earlier
+    // kernel of the chunk, so what the previous call left in the array is never seen and nothing
+    // needs to be cleared.
+    MXK_CU(in(sx, a->x + r0 * dim, n * dim * 4));
+    MXK_CU(in2d(sq_in, a->q_in, a->q_col0));
+    MXK_CU(in2d(sk_in, a->k_in, a->k_col0));
+    if (with_v) MXK_CU(in2d(sv_in, a->v_in, a->v_col0));
+    if (rope) {
+      MXK_CU(in(scos, a->cos + r0 * half, n * half * 4));
+      MXK_CU(in(ssin, a->sin + r0 * half, n * half * 4));
+    }
+    MXK_CU(in(sattn, a->attn_o + r0 * dim, n * dim * 2));
+    if (a->act_mode == 0) MXK_CU(in(sact, a->act + r0 * F, n * F * 2));
+    else MXK_CU(in(sact2, a->act2 + r0 * 2 * F, n * 2 * F * 2));
+    MXK_CU(in(smlp, a->mlp_o + r0 * dim, n * dim * 2));
+
+    MxkBlockArgs d = *a;
+    d.rows = n, d.chunk_rows = 0;
+    d.x = sx, d.h1 = sh1, d.h2 = sh2, d.attn_o = sattn, d.mlp_o = smlp, d.act = sact, d.act2 = sact2;
+    d.q_in = sq_in, d.k_in = sk_in, d.v_in = sv_in;
+    d.qkv_stride = inner, d.q_col0 = d.k_col0 = d.v_col0 = 0;
+    d.q_out = sq_out, d.k_out = sk_out, d.v_out = sv_out;
+    d.cos = rope ? scos : nullptr, d.sin = rope ? ssin : nullptr;
+    d.scale1 = shifted(a->scale1, r0), d.shift1 = shifted(a->shift1, r0), d.gate1 = shifted(a->gate1, r0);
+    d.scale2 = shifted(a->scale2, r0), d.shift2 = shifted(a->shift2, r0), d.gate2 = shifted(a->gate2, r0);
+    if (int rc = block_rows(d, 0, n, stream)) {
+      cudaStreamSynchronize(s);
+      return rc;
+    }
+
+    auto outc = [&](void* dst, const void* src, int64_t bytes) {
+      down += bytes;
+      return cudaMemcpyAsync(dst, src, size_t(bytes), cudaMemcpyDeviceToHost, s);
+    };
+    MXK_CU(outc(a->h1 + r0 * dim, sh1, n * dim * 2));
+    MXK_CU(outc(a->q_out + r0 * inner, sq_out, n * inner * 2));
+    MXK_CU(outc(a->k_out + r0 * inner, sk_out, n * inner * 2));
+    if (with_v) MXK_CU(outc(a->v_out + r0 * inner, sv_out, n * inner * 2));
+    MXK_CU(outc(a->h2 + r0 * dim, sh2, n * dim * 2));
+    MXK_CU(outc(a->act + r0 * F, sact, n * F * 2));
+    MXK_CU(outc(a->x + r0 * dim, sx, n * dim * 4));
+  }
+  MXK_CU(cudaStreamSynchronize(s));
 #undef MXK_CU
   if (h2d_bytes) *h2d_bytes = up;
   if (d2h_bytes) *d2h_bytes = down;

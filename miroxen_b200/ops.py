@@ -22,7 +22,7 @@ __all__ = [
     "gated_residual", "add_inplace_bf16", "head_norm_rope", "silu_mul", "gelu_tanh_inplace", "gelu_erf_inplace",
     "scatter_rows", "silu_inplace_f32", "add_bias_bf16", "add_bias_f32", "f32_to_bf16", "bf16_to_f32", "axpy_f32",
     "axpby_f32", "gated_residual_norm", "qkv_norm_rope", "HeadSpec", "dit_block_ops", "BlockArgs", "RowMod",
-    "HostPipeline", "OpTimes", "device_error", "launch_count", "reset_launch_count", "set_tuning",
+    "HostPipeline", "OpTimes", "dit_block_ops_host_static", "device_error", "launch_count", "reset_launch_count", "set_tuning",
 ]
 
 
@@ -198,6 +198,15 @@ class HostPipeline:
             self.close()
         except Exception:
             pass
+
+
+def dit_block_ops_host_static(args: BlockArgs, stream=None):
+    """mxk_dit_block_ops_host_static: the block sequence on HOST buffers for callers that may not allocate
+    device memory; staging is a fixed array inside the library (see include/mxk.h for the limit and the
+    sharing rules).  Returns (h2d_bytes, d2h_bytes) once the results are in host memory."""
+    up, down = C.c_int64(0), C.c_int64(0)
+    check(lib().mxk_dit_block_ops_host_static(C.byref(args), _stream(stream), C.byref(up), C.byref(down)))
+    return up.value, down.value
 
 
 def device_error(clear: bool = True) -> int:
