@@ -10,11 +10,13 @@
 // then a butterfly over the per-warp totals (src/kernels/ops.cu:8-30).
 //
 // Pinning: the reference holds no unit test, golden vector or CPU implementation for these ops
-// (its only checks are whole-model comparisons that need checkpoints).  The oracle is pinned
+// (its only checks are whole-model comparisons that need checkpoints).  The ops are pinned
 // against outputs of the reference's own kernels - src/kernels/ops.cu compiled unmodified for
-// sm_100a (oracle/Makefile, target _ref) and run on a B200 - stored under tests/golden/.  The
-// table builders have no runnable counterpart outside the reference's model classes: for them
-// parity is unpinned beyond the closed-form spot checks in the tests.
+// sm_100a (oracle/Makefile, target _ref) and run on a B200 - stored in
+// tests/golden/ref_ops_sm100a.npz, and the H3 rotary positions against the reference's own host
+// code (tests/golden/h3_positions.npz).  The Qwen table builder and the timestep embedding have
+// no runnable counterpart outside the reference's model classes: for those two parity is
+// unpinned beyond the closed-form spot checks against libm in the tests.
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
