@@ -209,9 +209,7 @@ def ref_cuda_chain(w, buf, stream_ptr):
     import ctypes as C
     from oracle import binding as orc
     L = orc.ref_ops()
-
-    class RM(C.Structure):
-        _fields_ = [("target", C.c_void_p), ("prefix", C.c_void_p), ("prefix_len", C.c_int64)]
+    RM = orc.RowMod  # same layout as the reference's RowMod
 
     a = buf.args
     conv = lambda m: RM(m.target, m.prefix, m.prefix_len)

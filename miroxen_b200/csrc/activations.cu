@@ -1,23 +1,24 @@
 // silu_mul, gelu_tanh_inplace, gelu_erf_inplace, silu_inplace_f32
 // (reference: src/kernels/ops.cu:121-128, 212-233, 244-246).
 #include "flat_map.cuh"
+#include "stream_pipe.cuh"
 
 namespace mxk {
 namespace {
 
 // 0.5 v (1 + tanh(u)), u = 0.7978845608 (v + 0.044715 v^3)  (src/kernels/ops.cu:222-224).
-// With e = exp(-2|u|) in (0, 1]:  1 + tanh(u) = 2 / (1 + e) for u >= 0 and 2 e / (1 + e) for
-// u < 0, so the value is v / (1 + e), times e when v < 0 (u has the sign of v): one ex2 and one
-// reciprocal, no cancellation in the negative tail and no overflow.  The constants fold
-// 2 log2(e) into the polynomial: 2 log2(e) u = v (A0 + A1 v^2).  Ten issue slots per element;
-// the kernel has to sustain more than one element per clock per SM quarter to keep up with HBM.
+// 0.5 (1 + tanh(u)) is the logistic function of 2u, so the value is v / (1 + exp(-2u)) =
+// v / (1 + 2^z) with z = -2 log2(e) u = v (B0 + B1 v^2): three multiply-adds, one ex2, one add,
+// one reciprocal, one multiply.  There is no cancellation anywhere (the negative tail divides
+// by a large number instead of adding 1 to a tanh near -1), and when 2^z overflows for very
+// negative v the reciprocal is 0 and the result the correct limit -0.  Seven issue slots per
+// element plus unpack and pack; at HBM speed the SM has to retire more than one element per
+// clock per scheduler, so every slot counts.
 __device__ __forceinline__ float gelu_tanh_f(float v) {
-  constexpr float A0 = 2.f * 1.4426950408889634f * 0.7978845608f;
-  constexpr float A1 = A0 * 0.044715f;
-  const float w = v * fmaf(v * v, A1, A0);
-  const float e = ex2_approx(-fabsf(w));
-  const float m = v * rcp_approx(1.f + e);
-  return v >= 0.f ? m : m * e;
+  constexpr float B0 = -2.f * 1.4426950408889634f * 0.7978845608f;
+  constexpr float B1 = B0 * 0.044715f;
+  const float z = v * fmaf(v * v, B1, B0);
+  return v * rcp_approx(1.f + ex2_approx(z));
 }
 
 __device__ __forceinline__ float gelu_erf_f(float v) {
@@ -59,6 +60,72 @@ struct SiluF32Op {
   }
   __device__ void scalar(int64_t i) const { x[i] = f(x[i]); }
 };
+
+// GELU in place over a flat array, for the streaming pipeline: chunk i is bytes [i*chunk, ...).
+template <int KIND>
+struct GeluPipeOp {
+  static constexpr int NSRC = 1;
+  unsigned char* x;
+  int64_t nbytes;
+  int chunk_bytes;
+  __device__ void locate(int64_t chunk, Chunk& c) const {
+    const int64_t off = chunk * chunk_bytes;
+    c.src0 = x + off, c.src1 = nullptr, c.dst = x + off;
+    c.bytes = unsigned(nbytes - off < chunk_bytes ? nbytes - off : chunk_bytes);
+  }
+  __device__ uint4 apply(const uint4& a, const uint4&) const {
+    float v[8];
+    unpack8(a, v);
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = GeluOp<KIND>::f(v[i]);
+    return pack8(v);
+  }
+};
+
+// silu(gate) * up for the streaming pipeline: a row of gu is cut into chunks_per_row column chunks.
+struct SiluPipeOp {
+  static constexpr int NSRC = 2;
+  const unsigned char* gu;
+  unsigned char* out;
+  int64_t F;
+  int chunks_per_row, chunk_elems;
+  __device__ void locate(int64_t chunk, Chunk& c) const {
+    const int64_t row = chunk / chunks_per_row;
+    const int64_t col = (chunk - row * chunks_per_row) * chunk_elems;
+    const int64_t n = F - col < chunk_elems ? F - col : chunk_elems;
+    c.src0 = gu + (row * 2 * F + col) * 2;
+    c.src1 = c.src0 + F * 2;
+    c.dst = out + (row * F + col) * 2;
+    c.bytes = unsigned(n * 2);
+  }
+  __device__ uint4 apply(const uint4& g, const uint4& u) const {
+    float a[8], b[8];
+    unpack8(g, a);
+    unpack8(u, b);
+#pragma unroll
+    for (int i = 0; i < 8; i++) a[i] = silu_f(a[i]) * b[i];
+    return pack8(a);
+  }
+};
+
+template <int KIND>
+int run_gelu(const char* name, mxk_bf16* x, int64_t n, cudaStream_t s) {
+  bf16* xb = reinterpret_cast<bf16*>(x);
+  const int64_t body = n / 8 * 8;
+  // GELU is limited by issue slots as much as by HBM: the register kernel (more warps per SM)
+  // measured faster than the pipeline for it, so the pipeline is opt-in here.
+  if (tune(TUNE_ACT_PATH, 2) == 1 && aligned(x, 16) && body >= (int64_t(1) << 16)) {
+    const int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 8) * 1024;
+    GeluPipeOp<KIND> op{reinterpret_cast<unsigned char*>(x), body * 2, chunk_bytes};
+    if (int rc = run_stream_pipe(name, op, ceil_div(body * 2, chunk_bytes), chunk_bytes, s)) return rc;
+    if (n > body) {  // fewer than 8 ragged elements at the end
+      flat_scalar_kernel<GeluOp<KIND>><<<1, 32, 0, s>>>(n - body, GeluOp<KIND>{xb + body});
+      return after_launch(name);
+    }
+    return MXK_OK;
+  }
+  return run_flat(name, n, GeluOp<KIND>{xb}, s);
+}
 
 constexpr int kActRowsInFlight = 4;
 
@@ -123,6 +190,13 @@ int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk
   cudaStream_t s = as_stream(stream);
   const bf16* in = reinterpret_cast<const bf16*>(gu);
   bf16* o = reinterpret_cast<bf16*>(out);
+  if (tune(TUNE_ACT_PATH, 1) == 1 && F % 8 == 0 && aligned(gu, 16) && aligned(out, 16) && rows * F >= (int64_t(1) << 16)) {
+    const int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 8) * 1024;
+    const int cpr = int(ceil_div(F * 2, chunk_bytes));
+    const int chunk_elems = int(ceil_div(ceil_div(F, cpr), 8) * 8);
+    SiluPipeOp op{reinterpret_cast<const unsigned char*>(gu), reinterpret_cast<unsigned char*>(out), F, cpr, chunk_elems};
+    return run_stream_pipe("silu_mul", op, rows * cpr, chunk_elems * 2, s);
+  }
   if (F % 8 == 0 && aligned(gu, 16) && aligned(out, 16)) {
     const int threads = 256;
     const int rpc = tune(TUNE_ACT_ROWS_PER_CTA, 4);
@@ -143,13 +217,13 @@ int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk
 int mxk_gelu_tanh_inplace(mxk_bf16* x, int64_t n, mxk_stream_t stream) {
   if (n <= 0) return MXK_OK;
   if (!x) return fail(MXK_ERR_INVALID_ARG, "gelu_tanh_inplace: null x");
-  return run_flat("gelu_tanh_inplace", n, GeluOp<0>{reinterpret_cast<bf16*>(x)}, as_stream(stream));
+  return run_gelu<0>("gelu_tanh_inplace", x, n, as_stream(stream));
 }
 
 int mxk_gelu_erf_inplace(mxk_bf16* x, int64_t n, mxk_stream_t stream) {
   if (n <= 0) return MXK_OK;
   if (!x) return fail(MXK_ERR_INVALID_ARG, "gelu_erf_inplace: null x");
-  return run_flat("gelu_erf_inplace", n, GeluOp<1>{reinterpret_cast<bf16*>(x)}, as_stream(stream));
+  return run_gelu<1>("gelu_erf_inplace", x, n, as_stream(stream));
 }
 
 int mxk_silu_inplace_f32(float* x, int64_t n, mxk_stream_t stream) {

@@ -278,6 +278,45 @@ __device__ __forceinline__ void rope_tokens(const unsigned char* src, int tok_by
   }
 }
 
+// The producer lane's loop: one group of `tpc` tokens per stage, in order; returns false when a
+// bounded wait on an `empty` barrier ran out.  `issued` counts the groups whose copies went out.
+__device__ __forceinline__ bool rope_produce(const RopeArgs& a, unsigned char* dyn, unsigned long long* full,
+                                             unsigned long long* empty, int64_t g_begin, int my_groups, int& issued) {
+  const int half = a.rot >> 1;
+  const bool rope = a.mode != MXK_ROPE_NONE && a.rot > 0;
+  int st = 0;
+  // Parity of the `empty` phase to wait for: the k-th refill of a stage (k >= 1) follows the
+  // completion of its phase k - 1, so the first wait uses parity 0 and it flips per trip after that.
+  unsigned ph = 0;
+  int64_t s0 = g_begin * a.tpc;
+  for (int it = 0; it < my_groups; it++, s0 += a.tpc) {
+    if (it >= a.stages && !mbar_wait(smem_u32(&empty[st]), ph)) return false;
+    const unsigned ntok = unsigned(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
+    const unsigned bar = smem_u32(&full[st]);
+    const unsigned dst = smem_u32(dyn + size_t(st) * a.stage_bytes);
+    unsigned bytes = rope ? 2u * ntok * unsigned(half) * 4u : 0u;
+    for (int i = 0; i < a.n_seg; i++) bytes += ntok * unsigned(a.seg[i].token_bytes);
+    mbar_expect_tx(bar, bytes);
+    for (int i = 0; i < a.n_seg; i++) {
+      const CopySeg& sg = a.seg[i];
+      const unsigned char* src = sg.base + s0 * sg.token_stride;
+      if (sg.dense) {
+        bulk_g2s(dst + sg.smem_off, src, ntok * unsigned(sg.token_bytes), bar);
+      } else {
+        for (unsigned t = 0; t < ntok; t++)
+          bulk_g2s(dst + sg.smem_off + t * unsigned(sg.token_bytes), src + t * sg.token_stride, unsigned(sg.token_bytes), bar);
+      }
+    }
+    if (rope) {
+      bulk_g2s(dst + a.cos_off, a.cos + s0 * half, ntok * unsigned(half) * 4u, bar);
+      bulk_g2s(dst + a.sin_off, a.sin + s0 * half, ntok * unsigned(half) * 4u, bar);
+    }
+    issued++;
+    if (++st == a.stages) st = 0, ph ^= (it >= a.stages ? 1u : 0u);
+  }
+  return true;
+}
+
 template <int LPH>
 __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
   extern __shared__ __align__(128) unsigned char dyn[];
@@ -308,42 +347,7 @@ __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
   bool ok = true;
   int issued = 0;  // producer: groups whose copies were issued
   if (warp == n_cons_warps) {
-    if (lane == 0) {
-      int st = 0;
-      // Parity of the `empty` phase to wait for: the k-th refill of a stage (k >= 1) follows the
-      // completion of its phase k - 1, so the first wait uses parity 0 and it flips per trip after that.
-      unsigned ph = 0;
-      int64_t s0 = g_begin * a.tpc;
-      for (int it = 0; it < my_groups; it++, s0 += a.tpc) {
-        if (it >= a.stages && !mbar_wait(smem_u32(&empty[st]), ph)) {
-          ok = false;
-          break;
-        }
-        const unsigned ntok = unsigned(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
-        const unsigned bar = smem_u32(&full[st]);
-        const unsigned dst = smem_u32(dyn + size_t(st) * a.stage_bytes);
-        unsigned bytes = rope ? 2u * ntok * unsigned(half) * 4u : 0u;
-        for (int i = 0; i < a.n_seg; i++) bytes += ntok * unsigned(a.seg[i].token_bytes);
-        mbar_expect_tx(bar, bytes);
-        for (int i = 0; i < a.n_seg; i++) {
-          const CopySeg& sg = a.seg[i];
-          const unsigned char* src = sg.base + s0 * sg.token_stride;
-          if (sg.dense) {
-            bulk_g2s(dst + sg.smem_off, src, ntok * unsigned(sg.token_bytes), bar);
-          } else {
-            for (unsigned t = 0; t < ntok; t++)
-              bulk_g2s(dst + sg.smem_off + t * unsigned(sg.token_bytes), src + t * sg.token_stride,
-                       unsigned(sg.token_bytes), bar);
-          }
-        }
-        if (rope) {
-          bulk_g2s(dst + a.cos_off, a.cos + s0 * half, ntok * unsigned(half) * 4u, bar);
-          bulk_g2s(dst + a.sin_off, a.sin + s0 * half, ntok * unsigned(half) * 4u, bar);
-        }
-        issued++;
-        if (++st == a.stages) st = 0, ph ^= (it >= a.stages ? 1u : 0u);
-      }
-    }
+    if (lane == 0) ok = rope_produce(a, dyn, full, empty, g_begin, my_groups, issued);
   } else {
     const int l = tid % LPH;
     LaneRole r;

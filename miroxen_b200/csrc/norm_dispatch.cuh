@@ -45,7 +45,9 @@ inline void launch_norm_inst(const NormPlan& p, NormArgs a, bool tma, cudaStream
     const int xb = (a.dim * int(sizeof(TIN)) + 127) & ~127;
     const int stage_bytes = xb + (FUSE_RES ? ((a.dim * 2 + 127) & ~127) : 0);
     int stages = tune(TUNE_NORM_STAGES, 0);
-    if (stages <= 0) stages = 49152 / stage_bytes;  // about 48 KB of rows in flight per CTA
+    // Two stages per CTA measured best on B200: small stages leave room for more resident CTAs,
+    // and the CTAs of one SM together keep enough rows in flight.
+    if (stages <= 0) stages = 2;
     if (stages < 2) stages = 2;
     if (stages > kNormMaxStages) stages = kNormMaxStages;
     const size_t smem = size_t(stages) * stage_bytes;

@@ -22,6 +22,11 @@ enum TuneKey {
   TUNE_EW_CTAS_PER_SM,     // CTAs per SM the flat elementwise grid is sized for
   TUNE_RES_PATH,           // 1 bulk-copy pipelined gated_residual, 2 column-strip register kernel
   TUNE_ROPE_TOKENS,        // tokens per stage of the bulk-copy head kernel (1..16)
+  TUNE_STREAM_WARPS,       // consumer warps per CTA of the streaming pipeline
+  TUNE_STREAM_STAGES,      // its stages (2..8)
+  TUNE_STREAM_CTAS_PER_SM,
+  TUNE_STREAM_CHUNK_KB,    // bytes per source per chunk, in KB
+  TUNE_ACT_PATH,           // 1 bulk-copy streaming pipeline for GELU / SiLU-mul, 2 register kernels
   TUNE_COUNT
 };
 

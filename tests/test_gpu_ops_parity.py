@@ -468,3 +468,33 @@ def test_head_pipeline_many_trips(mx, tokens, stages, threads, layout):
         orc.set_threads(1)
         for k in ("rope_stages", "rope_tokens", "rope_threads", "rope_ctas_per_sm"):
             mx.set_tuning(k, 0)
+
+
+@pytest.mark.parametrize("stages,warps,chunk_kb", [(2, 4, 8), (3, 8, 16), (4, 2, 4)])
+def test_stream_pipeline_many_trips(mx, stages, warps, chunk_kb):
+    """GELU and SiLU-mul through the streaming pipeline with every stage refilled many times
+    (one CTA per SM), ragged array length and a ragged last chunk per row."""
+    g = H.rng(stages + warps)
+    orc.set_threads(8)
+    for k, v in (("stream_stages", stages), ("stream_warps", warps), ("stream_chunk_kb", chunk_kb), ("stream_ctas_per_sm", 1),
+                 ("act_path", 1)):
+        mx.set_tuning(k, v)
+    try:
+        n = 12 * 1000 * 1000 + 5
+        x = H.normal_bf16(g, n, 2.0)
+        ref = orc.gelu_tanh_inplace(x.copy())
+        xd = H.Guarded(torch, (n,), torch.bfloat16, fill=H.to_dev(torch, x))
+        mx.gelu_tanh_inplace(xd.t, n)
+        rows, F = 700, 13824
+        gu = H.normal_bf16(g, (rows, 2 * F), 2.0)
+        rs = orc.silu_mul(gu, F)
+        out = H.Guarded(torch, (rows, F), torch.bfloat16)
+        mx.silu_mul(H.to_dev(torch, gu), rows, F, out.t)
+        torch.cuda.synchronize()
+        xd.check("gelu pipeline"), out.check("silu pipeline")
+        H.assert_bf16_close(H.bits(xd.t), ref, "gelu pipeline")
+        H.assert_bf16_close(H.bits(out.t), rs, "silu pipeline")
+    finally:
+        orc.set_threads(1)
+        for k in ("stream_stages", "stream_warps", "stream_chunk_kb", "stream_ctas_per_sm", "act_path"):
+            mx.set_tuning(k, 0)
