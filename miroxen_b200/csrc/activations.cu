@@ -134,6 +134,8 @@ __global__ void __launch_bounds__(256)
     silu_mul_kernel(const bf16* __restrict__ gu, int64_t rows, int F, bf16* __restrict__ out,
                     int rows_per_chunk) {
   constexpr int U = kActRowsInFlight;
+  pdl_launch_dependents();
+  pdl_wait();
   const int col = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
   if (col >= F) return;
   const int64_t nchunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
@@ -205,7 +207,7 @@ int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk
     int64_t gx = ceil_div(int64_t(sm_count()) * resident_ctas(silu_mul_kernel, threads), gy);
     if (gx > nchunks) gx = nchunks;
     if (gx < 1) gx = 1;
-    silu_mul_kernel<<<dim3(unsigned(gx), gy), threads, 0, s>>>(in, rows, int(F), o, rpc);
+    launch_pdl(silu_mul_kernel, dim3(unsigned(gx), gy), dim3(threads), 0, s, in, rows, int(F), o, rpc);
   } else {
     const unsigned gy = unsigned(ceil_div(F, 256));
     int64_t gx = rows < int64_t(sm_count()) * 16 ? rows : int64_t(sm_count()) * 16;

@@ -16,6 +16,8 @@ namespace mxk {
 
 template <int UNROLL, class Op>
 __global__ void __launch_bounds__(512) flat_vec_kernel(int64_t n, Op op) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int64_t nvec = n / Op::VEC;
   const int T = blockDim.x;
   const int64_t tile = int64_t(T) * UNROLL;
@@ -58,7 +60,7 @@ inline int run_flat(const char* name, int64_t n, const Op& op, cudaStream_t s) {
       int64_t grid = ceil_div(nvec, int64_t(threads) * unroll);
       const int64_t wave = int64_t(sm_count()) * tune(TUNE_EW_CTAS_PER_SM, resident_ctas(kern, threads));
       if (grid > wave) grid = wave;
-      kern<<<unsigned(grid), threads, 0, s>>>(n, op);
+      launch_pdl(kern, dim3(unsigned(grid)), dim3(threads), 0, s, n, op);
     };
     switch (unroll) {
       case 1: go(flat_vec_kernel<1, Op>); break;

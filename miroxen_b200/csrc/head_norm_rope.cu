@@ -56,6 +56,8 @@ struct RopeArgs {
 template <int LPH>
 __global__ void __launch_bounds__(512) head_rope_kernel(const RopeArgs a) {
   constexpr int U = kHeadsInFlight;
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int l = threadIdx.x % LPH;  // lane within the head: channels 8l .. 8l+7
   const int group = threadIdx.x / LPH;
@@ -324,10 +326,6 @@ __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
   __shared__ __align__(16) float wsm[kMaxTensors][256];  // the tensors' norm weights
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n_cons_warps = (blockDim.x >> 5) - 1;
-  for (int i = tid; i < a.n_tensors * a.D; i += blockDim.x) {
-    const int ti = i / a.D, d = i - ti * a.D;
-    wsm[ti][d] = a.t[ti].norm_w ? a.t[ti].norm_w[d] : 1.f;
-  }
   const int half = a.rot >> 1;
   const bool rope = a.mode != MXK_ROPE_NONE && a.rot > 0;
   const int64_t n_groups = (a.S + a.tpc - 1) / a.tpc;
@@ -341,6 +339,12 @@ __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
       mbar_init(smem_u32(&empty[i]), unsigned(n_cons_warps));
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  pdl_launch_dependents();
+  pdl_wait();  // nothing above touches global memory
+  for (int i = tid; i < a.n_tensors * a.D; i += blockDim.x) {
+    const int ti = i / a.D, d = i - ti * a.D;
+    wsm[ti][d] = a.t[ti].norm_w ? a.t[ti].norm_w[d] : 1.f;
   }
   __syncthreads();
 
@@ -565,7 +569,7 @@ int launch_pipe(const char* name, RopeArgs a, cudaStream_t stream) {
   if (ctas > n_groups) ctas = n_groups;
   a.groups_per_cta = ceil_div(n_groups, ctas);
   a.err = device_error_word();
-  k<<<unsigned(ceil_div(n_groups, a.groups_per_cta)), threads, smem, stream>>>(a);
+  launch_pdl(k, dim3(unsigned(ceil_div(n_groups, a.groups_per_cta))), dim3(threads), smem, stream, a);
   return after_launch(name);
 }
 
@@ -593,7 +597,7 @@ int run(const char* name, RopeArgs a, cudaStream_t stream) {
         int64_t grid = ceil_div(a.S, tpp);
         const int64_t cap = int64_t(sm_count()) * (per_sm > 0 ? per_sm : 1);
         if (grid > cap) grid = cap;
-        kern<<<unsigned(grid), threads, 0, stream>>>(a);
+        launch_pdl(kern, dim3(unsigned(grid)), dim3(threads), 0, stream, a);
       };
       switch (lph) {
         case 4: go(head_rope_kernel<4>); break;

@@ -8,8 +8,8 @@ namespace mxk {
 
 // Picks threads per CTA and 4-element vectors per thread so that threads * vpt covers dim / 4
 // with the least padding; among equal paddings the CTA size nearest the preferred one wins.
-inline bool plan_norm(int nvec, int64_t rows, NormPlan& p) {
-  const int want = tune(TUNE_NORM_THREADS, 256);
+inline bool plan_norm(int nvec, int64_t rows, NormPlan& p, int want_default = 128) {
+  const int want = tune(TUNE_NORM_THREADS, want_default);  // 128 measured best for the norms on B200
   int best_waste = 1 << 30, best_dist = 1 << 30;
   p.threads = 0;
   for (int vpt = 1; vpt <= kNormMaxVpt; vpt++) {
@@ -54,11 +54,12 @@ inline void launch_norm_inst(const NormPlan& p, NormArgs a, bool tma, cudaStream
     // static shared memory (reduction scratch, barriers) counts against the 48 KB default too
     if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     const unsigned grid = norm_grid(a, tune(TUNE_NORM_CTAS_PER_SM, resident_ctas(k, p.threads, smem)));
-    k<<<grid, p.threads, smem, s>>>(a, stages, stage_bytes);
+    a.row_step = tune(TUNE_NORM_INTERLEAVE, 1) == 1 ? int64_t(grid) : 1;
+    launch_pdl(k, dim3(grid), dim3(p.threads), smem, s, a, stages, stage_bytes);
   } else {
     auto k = norm_rows_kernel<MODE, TIN, VPT, HAS_W, FUSE_RES, EXACT>;
     const unsigned grid = norm_grid(a, tune(TUNE_NORM_CTAS_PER_SM, resident_ctas(k, p.threads)));
-    k<<<grid, p.threads, 0, s>>>(a);
+    launch_pdl(k, dim3(grid), dim3(p.threads), 0, s, a);
   }
 }
 

@@ -33,6 +33,7 @@ struct NormArgs {
   MxkRowMod scale, shift;
   bf16* out;
   int rows_per_cta;
+  int64_t row_step;  // bulk-copy kernel: 1 = contiguous row range per CTA, gridDim.x = interleaved rows
   int* err;  // device error word (bounded waits report here)
 };
 
@@ -69,6 +70,8 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
     norm_rows_kernel(const NormArgs a) {
   using raw_t = typename Raw4<TIN>::type;
   __shared__ float red[2][16];
+  pdl_launch_dependents();
+  pdl_wait();
   const int tid = threadIdx.x, T = blockDim.x, nwarps = T >> 5;
   const int64_t r0 = int64_t(blockIdx.x) * a.rows_per_cta;
   const int64_t r1 = r0 + a.rows_per_cta < a.rows ? r0 + a.rows_per_cta : a.rows;
@@ -215,19 +218,24 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
   __shared__ float red[2][16];
   __shared__ __align__(8) unsigned long long bars[8];
   const int tid = threadIdx.x, T = blockDim.x, nwarps = T >> 5;
-  const int64_t r0 = int64_t(blockIdx.x) * a.rows_per_cta;
-  const int64_t r1 = r0 + a.rows_per_cta < a.rows ? r0 + a.rows_per_cta : a.rows;
+  // Rows of this CTA: a contiguous range (row_step 1) or every gridDim.x-th row (row_step =
+  // gridDim.x), in which case the CTAs of the grid sweep one compact window of rows together.
+  const int64_t step = a.row_step;
+  const int64_t r0 = step == 1 ? int64_t(blockIdx.x) * a.rows_per_cta : int64_t(blockIdx.x);
+  const int64_t r1 = step == 1 ? (r0 + a.rows_per_cta < a.rows ? r0 + a.rows_per_cta : a.rows) : a.rows;
   const TIN* x = static_cast<const TIN*>(a.x);
   const float fdim = float(a.dim);
   const unsigned xbytes = unsigned(a.dim) * sizeof(TIN);
   const unsigned ybytes = FUSE_RES ? unsigned(a.dim) * 2u : 0u;
   const unsigned yoff = (xbytes + 127u) & ~127u;  // y row sits after the x row inside a stage
 
+  pdl_launch_dependents();
   if (tid == 0) {
     for (int i = 0; i < stages; i++) mbar_init(smem_u32(&bars[i]), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  pdl_wait();  // nothing above touches global memory
 
   auto issue = [&](int64_t row, int st) {  // thread 0 only
     const unsigned bar = smem_u32(&bars[st]);
@@ -237,7 +245,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
     if (FUSE_RES) bulk_g2s(dst + yoff, a.y + row * a.dim, ybytes, bar);
   };
   if (tid == 0)
-    for (int i = 0; i < stages && r0 + i < r1; i++) issue(r0 + i, i);
+    for (int i = 0; i < stages && r0 + i * step < r1; i++) issue(r0 + i * step, i);
 
   bool on[VPT];
 #pragma unroll
@@ -256,7 +264,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
   int parity = 0;
   bool failed = false;
   int64_t row = r0;
-  for (; row < r1; row++) {
+  for (; row < r1; row += step) {
     const int set = (row < a.scale.prefix_len ? 1 : 0) | (row < a.shift.prefix_len ? 2 : 0) |
                     (FUSE_RES && row < a.gate.prefix_len ? 4 : 0);
     if (set != cur_set) {
@@ -315,7 +323,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
         failed = true;
         break;
       }
-      if (tid == 0 && row + stages < r1) issue(row + stages, st);
+      if (tid == 0 && row + stages * step < r1) issue(row + stages * step, st);
       if (++st == stages) st = 0, phase ^= 1u;
     } else {
       // first reduction: its barrier also tells every thread whether all of them saw the row arrive
@@ -345,7 +353,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
         break;
       }
       // every thread has its part of the row in registers: the stage can take row + stages
-      if (tid == 0 && row + stages < r1) issue(row + stages, st);
+      if (tid == 0 && row + stages * step < r1) issue(row + stages * step, st);
       if (++st == stages) st = 0, phase ^= 1u;
 
       const float rstd = rsqrtf(total / fdim + a.eps);
@@ -370,7 +378,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
     // shared memory: give each a bounded chance to land before the CTA goes away.
     int s2 = st;
     unsigned ph = phase;
-    for (int64_t r = row; r < r1 && r < row + stages; r++) {
+    for (int64_t r = row; r < r1 && r < row + stages * step; r += step) {
       mbar_wait(smem_u32(&bars[s2]), ph);
       if (++s2 == stages) s2 = 0, ph ^= 1u;
     }

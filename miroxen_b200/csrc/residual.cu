@@ -77,6 +77,8 @@ template <int CPT>
 __global__ void __launch_bounds__(256)
     gated_residual_kernel(float* __restrict__ x, const bf16* __restrict__ y, int64_t rows, int dim,
                           MxkRowMod gate, int gate_tanh, int rows_per_chunk) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int col = (blockIdx.y * blockDim.x + threadIdx.x) * CPT;
   if (col >= dim) return;
   const int64_t plen = gate.target ? gate.prefix_len : 0;
@@ -140,7 +142,7 @@ int mxk_gated_residual(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, M
     a.x = x, a.xw = x, a.y = yb, a.gate = gate, a.gate_tanh = gate_tanh;
     a.rows = rows, a.dim = int(dim), a.nvec = int(dim / 4);
     NormPlan p;
-    if (plan_norm(a.nvec, rows, p)) {
+    if (plan_norm(a.nvec, rows, p, 256)) {  // the residual-only mode measured best with 256-thread CTAs
       launch_norm<2, float, false, true>(p, a, true, s);
       return after_launch("gated_residual");
     }
@@ -152,10 +154,10 @@ int mxk_gated_residual(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, M
   };
   if (dim % 8 == 0 && aligned(x, 16) && aligned(y, 16) && gate_ok) {
     const unsigned gy = unsigned(ceil_div(dim / 8, threads));
-    gated_residual_kernel<8><<<dim3(wave_x(gated_residual_kernel<8>, gy), gy), threads, 0, s>>>(x, yb, rows, int(dim), gate, gate_tanh, rpc);
+    launch_pdl(gated_residual_kernel<8>, dim3(wave_x(gated_residual_kernel<8>, gy), gy), dim3(threads), 0, s, x, yb, rows, int(dim), gate, gate_tanh, rpc);
   } else if (dim % 4 == 0 && aligned(x, 16) && aligned(y, 8) && gate_ok) {
     const unsigned gy = unsigned(ceil_div(dim / 4, threads));
-    gated_residual_kernel<4><<<dim3(wave_x(gated_residual_kernel<4>, gy), gy), threads, 0, s>>>(x, yb, rows, int(dim), gate, gate_tanh, rpc);
+    launch_pdl(gated_residual_kernel<4>, dim3(wave_x(gated_residual_kernel<4>, gy), gy), dim3(threads), 0, s, x, yb, rows, int(dim), gate, gate_tanh, rpc);
   } else {
     const unsigned gy = unsigned(ceil_div(dim, 256));
     int64_t gx = rows < int64_t(sm_count()) * 16 ? rows : int64_t(sm_count()) * 16;

@@ -20,6 +20,7 @@ const char* const kTuneNames[TUNE_COUNT] = {
     "res_threads",  "ew_threads",       "ew_unroll",    "act_rows_per_cta", "norm_path",
     "norm_stages",  "rope_path",        "rope_stages",  "ew_ctas_per_sm",   "res_path",     "rope_tokens",
     "stream_warps", "stream_stages",    "stream_ctas_per_sm", "stream_chunk_kb", "act_path",
+    "pdl",          "norm_interleave",
 };
 }  // namespace
 
@@ -106,6 +107,8 @@ int resident_ctas_lookup(const void* kernel, int threads, size_t smem) {
   if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, threads, smem) != cudaSuccess || n < 1) return 1;
   return n;
 }
+
+bool pdl_enabled() { return g_tune[TUNE_PDL].load(std::memory_order_relaxed) != 2; }
 
 int tune(int key, int dflt) {
   int v = g_tune[key].load(std::memory_order_relaxed);

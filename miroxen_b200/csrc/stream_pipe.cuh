@@ -48,7 +48,9 @@ __global__ void __launch_bounds__(544) stream_pipe_kernel(const Op op, const int
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  pdl_launch_dependents();
   __syncthreads();
+  pdl_wait();  // nothing above touches global memory
 
   bool ok = true;
   int issued = 0;
@@ -137,8 +139,8 @@ inline int run_stream_pipe(const char* name, const Op& op, int64_t n_chunks, int
   int64_t ctas = int64_t(sm_count()) * (per_sm > 0 ? per_sm : 1);
   if (ctas > n_chunks) ctas = n_chunks;
   const int64_t per_cta = ceil_div(n_chunks, ctas);
-  k<<<unsigned(ceil_div(n_chunks, per_cta)), threads, smem, s>>>(op, n_chunks, per_cta, stages, stage_bytes, padded,
-                                                                  device_error_word());
+  launch_pdl(k, dim3(unsigned(ceil_div(n_chunks, per_cta))), dim3(threads), smem, s, op, n_chunks, per_cta, stages,
+             stage_bytes, padded, device_error_word());
   return after_launch(name);
 }
 

@@ -27,6 +27,8 @@ enum TuneKey {
   TUNE_STREAM_CTAS_PER_SM,
   TUNE_STREAM_CHUNK_KB,    // bytes per source per chunk, in KB
   TUNE_ACT_PATH,           // 1 bulk-copy streaming pipeline for GELU / SiLU-mul, 2 register kernels
+  TUNE_PDL,                // 2 disables programmatic dependent launch (default: on)
+  TUNE_NORM_INTERLEAVE,    // 1: CTA i of the bulk-copy row kernels takes rows i, i + grid, ...; 2: contiguous ranges
   TUNE_COUNT
 };
 
