@@ -45,6 +45,7 @@ struct RopeArgs {
   int rot, mode;    // shared by every rotating tensor of the launch
   int tpc;          // tokens per stage (one group)
   int64_t groups_per_cta;
+  int interleave;   // 1: CTA i takes groups i, i + grid, ...; 0: a contiguous range of groups
   CopySeg seg[kMaxTensors];
   int n_seg;
   int t_seg[kMaxTensors];  // segment that holds tensor ti
@@ -283,7 +284,7 @@ __device__ __forceinline__ void rope_tokens(const unsigned char* src, int tok_by
 // The producer lane's loop: one group of `tpc` tokens per stage, in order; returns false when a
 // bounded wait on an `empty` barrier ran out.  `issued` counts the groups whose copies went out.
 __device__ __forceinline__ bool rope_produce(const RopeArgs& a, unsigned char* dyn, unsigned long long* full,
-                                             unsigned long long* empty, int64_t g_begin, int my_groups, int& issued) {
+                                             unsigned long long* empty, int64_t g_begin, int64_t g_step, int my_groups, int& issued) {
   const int half = a.rot >> 1;
   const bool rope = a.mode != MXK_ROPE_NONE && a.rot > 0;
   int st = 0;
@@ -291,7 +292,7 @@ __device__ __forceinline__ bool rope_produce(const RopeArgs& a, unsigned char* d
   // completion of its phase k - 1, so the first wait uses parity 0 and it flips per trip after that.
   unsigned ph = 0;
   int64_t s0 = g_begin * a.tpc;
-  for (int it = 0; it < my_groups; it++, s0 += a.tpc) {
+  for (int it = 0; it < my_groups; it++, s0 += g_step * a.tpc) {
     if (it >= a.stages && !mbar_wait(smem_u32(&empty[st]), ph)) return false;
     const unsigned ntok = unsigned(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
     const unsigned bar = smem_u32(&full[st]);
@@ -329,9 +330,12 @@ __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
   const int half = a.rot >> 1;
   const bool rope = a.mode != MXK_ROPE_NONE && a.rot > 0;
   const int64_t n_groups = (a.S + a.tpc - 1) / a.tpc;
-  const int64_t g_begin = int64_t(blockIdx.x) * a.groups_per_cta;
-  const int64_t g_end = g_begin + a.groups_per_cta < n_groups ? g_begin + a.groups_per_cta : n_groups;
-  const int my_groups = g_end > g_begin ? int(g_end - g_begin) : 0;
+  // This CTA's groups: a contiguous range, or every gridDim.x-th group so that the grid sweeps one
+  // compact window of tokens together.
+  const int64_t g_step = a.interleave ? int64_t(gridDim.x) : 1;
+  const int64_t g_begin = a.interleave ? int64_t(blockIdx.x) : int64_t(blockIdx.x) * a.groups_per_cta;
+  const int64_t g_end = a.interleave ? n_groups : (g_begin + a.groups_per_cta < n_groups ? g_begin + a.groups_per_cta : n_groups);
+  const int my_groups = g_end > g_begin ? int((g_end - g_begin + g_step - 1) / g_step) : 0;
 
   if (tid == 0) {
     for (int i = 0; i < a.stages; i++) {
@@ -351,7 +355,7 @@ __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
   bool ok = true;
   int issued = 0;  // producer: groups whose copies were issued
   if (warp == n_cons_warps) {
-    if (lane == 0) ok = rope_produce(a, dyn, full, empty, g_begin, my_groups, issued);
+    if (lane == 0) ok = rope_produce(a, dyn, full, empty, g_begin, g_step, my_groups, issued);
   } else {
     const int l = tid % LPH;
     LaneRole r;
@@ -376,7 +380,7 @@ __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
     int st = 0;
     unsigned ph = 0;
     int64_t s0 = g_begin * a.tpc;
-    for (int it = 0; it < my_groups; it++, s0 += a.tpc) {
+    for (int it = 0; it < my_groups; it++, s0 += g_step * a.tpc) {
       if (!mbar_wait(smem_u32(&full[st]), ph)) {
         ok = false;
         break;
@@ -568,6 +572,7 @@ int launch_pipe(const char* name, RopeArgs a, cudaStream_t stream) {
   int64_t ctas = int64_t(sm_count()) * (per_sm > 0 ? per_sm : 1);
   if (ctas > n_groups) ctas = n_groups;
   a.groups_per_cta = ceil_div(n_groups, ctas);
+  a.interleave = tune(TUNE_PIPE_INTERLEAVE, 1) == 1;
   a.err = device_error_word();
   launch_pdl(k, dim3(unsigned(ceil_div(n_groups, a.groups_per_cta))), dim3(threads), smem, stream, a);
   return after_launch(name);

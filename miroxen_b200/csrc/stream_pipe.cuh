@@ -32,14 +32,17 @@ __device__ __forceinline__ void mbar_arrive_one(unsigned bar) {
 template <class Op>
 __global__ void __launch_bounds__(544) stream_pipe_kernel(const Op op, const int64_t n_chunks, const int64_t chunks_per_cta,
                                                           const int stages, const int stage_bytes, const int src_bytes,
-                                                          int* err) {
+                                                          const int interleave, int* err) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ __align__(8) unsigned long long full[8], empty[8];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n_cons_warps = (blockDim.x >> 5) - 1, n_cons = n_cons_warps * 32;
-  const int64_t c_begin = int64_t(blockIdx.x) * chunks_per_cta;
-  const int64_t c_end = c_begin + chunks_per_cta < n_chunks ? c_begin + chunks_per_cta : n_chunks;
-  const int mine = c_end > c_begin ? int(c_end - c_begin) : 0;
+  // This CTA's chunks: a contiguous range, or every gridDim.x-th chunk (the grid then sweeps one
+  // compact window of memory together).
+  const int64_t c_step = interleave ? int64_t(gridDim.x) : 1;
+  const int64_t c_begin = interleave ? int64_t(blockIdx.x) : int64_t(blockIdx.x) * chunks_per_cta;
+  const int64_t c_end = interleave ? n_chunks : (c_begin + chunks_per_cta < n_chunks ? c_begin + chunks_per_cta : n_chunks);
+  const int mine = c_end > c_begin ? int((c_end - c_begin + c_step - 1) / c_step) : 0;
 
   if (tid == 0) {
     for (int i = 0; i < stages; i++) {
@@ -64,7 +67,7 @@ __global__ void __launch_bounds__(544) stream_pipe_kernel(const Op op, const int
           break;
         }
         Chunk c;
-        op.locate(c_begin + it, c);
+        op.locate(c_begin + it * c_step, c);
         const unsigned bar = smem_u32(&full[st]);
         const unsigned dst = smem_u32(dyn + size_t(st) * stage_bytes);
         mbar_expect_tx(bar, c.bytes * Op::NSRC);
@@ -83,7 +86,7 @@ __global__ void __launch_bounds__(544) stream_pipe_kernel(const Op op, const int
         break;
       }
       Chunk c;
-      op.locate(c_begin + it, c);
+      op.locate(c_begin + it * c_step, c);
       const uint4* s0 = reinterpret_cast<const uint4*>(dyn + size_t(st) * stage_bytes);
       const uint4* s1 = reinterpret_cast<const uint4*>(dyn + size_t(st) * stage_bytes + src_bytes);
       uint4* d = reinterpret_cast<uint4*>(c.dst);
@@ -122,15 +125,16 @@ __global__ void __launch_bounds__(544) stream_pipe_kernel(const Op op, const int
 
 // Launches the pipeline over n_chunks chunks whose sources are at most src_bytes long.
 template <class Op>
-inline int run_stream_pipe(const char* name, const Op& op, int64_t n_chunks, int src_bytes, cudaStream_t s) {
+inline int run_stream_pipe(const char* name, const Op& op, int64_t n_chunks, int src_bytes, cudaStream_t s,
+                           int default_warps, int default_stages) {
   auto k = stream_pipe_kernel<Op>;
-  int warps = tune(TUNE_STREAM_WARPS, 4);
+  int warps = tune(TUNE_STREAM_WARPS, default_warps);
   if (warps < 1) warps = 1;
   if (warps > 16) warps = 16;
   const int threads = warps * 32 + 32;
   const int padded = (src_bytes + 127) & ~127;
   const int stage_bytes = padded * Op::NSRC;
-  int stages = tune(TUNE_STREAM_STAGES, 3);
+  int stages = tune(TUNE_STREAM_STAGES, default_stages);
   if (stages < 2) stages = 2;
   if (stages > 8) stages = 8;
   const size_t smem = size_t(stages) * stage_bytes;
@@ -140,7 +144,7 @@ inline int run_stream_pipe(const char* name, const Op& op, int64_t n_chunks, int
   if (ctas > n_chunks) ctas = n_chunks;
   const int64_t per_cta = ceil_div(n_chunks, ctas);
   launch_pdl(k, dim3(unsigned(ceil_div(n_chunks, per_cta))), dim3(threads), smem, s, op, n_chunks, per_cta, stages,
-             stage_bytes, padded, device_error_word());
+             stage_bytes, padded, int(tune(TUNE_PIPE_INTERLEAVE, 1) == 1), device_error_word());
   return after_launch(name);
 }
 
