@@ -36,8 +36,15 @@ __device__ __forceinline__ bool mbar_try(unsigned bar, unsigned parity) {
 }
 // Bounded wait; false when the limit ran out.
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-  for (unsigned i = 0; i < kWaitTries; i++)
+  if (mbar_try(bar, parity)) return true;
+  // try_wait may come back early; sleep between tries so that a waiting warp leaves the issue
+  // slots to the warps that have data (these kernels are short of issue slots, not of warps).
+  unsigned ns = 32;
+  for (unsigned i = 1; i < kWaitTries; i++) {
+    __nanosleep(ns);
+    if (ns < 256) ns <<= 1;
     if (mbar_try(bar, parity)) return true;
+  }
   return false;
 }
 // 1-D bulk copy global -> this CTA's shared memory; src, dst and bytes are multiples of 16.
