@@ -434,6 +434,31 @@ def main():
         for b in sets:
             b.args.fused = 1 if args.chain == "fused" else 0
 
+    if not args.no_extras and n_gpus == 1:
+        # the step that follows these ops on the reference's fp8 / fp4 path: the activation block-scale
+        # quantiser, timed on this block's norm output [rows, dim] and MLP activation [rows, F]
+        q_ops = []
+        for mode, mname, per_el in ((mx.ops.Q_MXFP8, "mxfp8", 2 + 1 + 1 / 32), (mx.ops.Q_NVFP4, "nvfp4", 2 + 2 + 0.5 + 1 / 16)):
+            for src_name, cols in (("h1", w.dim), ("act", w.F)):
+                srcs = [getattr(b, src_name) for b in sets]
+                outs = [mx.ops.quantize_blockscaled(mode, t, cols, rows, cols, stream=stream) for t in srcs]
+                for i in range(3):
+                    mx.ops.quantize_blockscaled(mode, srcs[i % n_sets], cols, rows, cols, outs[i % n_sets], stream)
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for i in range(K):
+                    mx.ops.quantize_blockscaled(mode, srcs[i % n_sets], cols, rows, cols, outs[i % n_sets], stream)
+                e1.record(stream)
+                barrier()
+                us = e0.elapsed_time(e1) / K * 1e3
+                by = per_el * rows * cols
+                q_ops.append({"op": f"quantize_{mname}", "input": f"{src_name} [{rows}, {cols}]", "us": round(us, 2),
+                              "bytes": int(by), "gbs": round(by / us / 1e3, 1), "frac": round(by / us / 1e3 / peak_gbs, 3)})
+                del outs
+        line["next_rows"] = {"quantize_blockscaled": q_ops,
+                             "note": "bytes = bf16 read + codes + scales; nvfp4 reads the input twice (tensor amax first)"}
+
     if not args.no_e2e:
         # end to end: pinned host buffers in, results back in host memory, every step
         hb = BlockBuffers(w, rows, prefix_rows, seed=7, mods=mods, cos=cos, sin=sin, host=True)

@@ -312,6 +312,30 @@ int mxk_dit_block_ops_host_static(const MxkBlockArgs* a, mxk_stream_t stream, in
  * Synchronises with the device. */
 int mxk_device_error(int* out_host, int clear);
 
+/* Self-test of the kernels' failure path: launches one small CTA that waits, with a budget of four
+ * tries (under 100 microseconds), on a barrier that is never completed; the kernel gives up, sets the
+ * device error word to 1 and returns, leaving the context usable.  mxk_device_error() then reads 1. */
+int mxk_selftest_bounded_wait(mxk_stream_t stream);
+
+/* ---- activation block-scale quantiser (the step after this library's ops on the fp8 / fp4 path) ----
+ *
+ * Replaces quantize_blockscaled(), qdata_bytes() and qscale_bytes() of src/kernels/blockscale.h:27-43
+ * (kernels at src/kernels/blockscale.cu:47-129, launcher 147-164; called on every activation by
+ * src/core/weights.cpp:189-195).  x is bf16 [rows, K] with row stride ldx (elements).
+ *   MXK_Q_MXFP8: q = rows * K e4m3 bytes, sf = one ue8m0 byte per 32 elements of a row.
+ *   MXK_Q_NVFP4: q = rows * K / 2 bytes (two e2m1 codes per byte, low nibble first), sf = one e4m3 byte
+ *                per 16 elements, *amax (device fp32, required) receives max|x|; the tensor scale the
+ *                GEMM needs is amax / 2688.
+ * sf has mxk_qscale_bytes() bytes in cuBLASLt's VEC32_UE8M0 / VEC16_UE4M3 layout (rows padded to 128,
+ * scale columns to 4, 128 x 4 tiles interleaved) and is cleared first, padding included.
+ * Requirements as the reference's: K % 32 == 0, ldx % 8 == 0, x 16-byte aligned; q 8-byte aligned.
+ * Outputs are byte-identical to the reference kernel's. */
+enum { MXK_Q_MXFP8 = 1, MXK_Q_NVFP4 = 2 };
+int64_t mxk_qdata_bytes(int mode, int64_t rows, int64_t K);
+int64_t mxk_qscale_bytes(int mode, int64_t rows, int64_t K);
+int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t rows, int64_t K, void* q, uint8_t* sf,
+                             float* amax, mxk_stream_t stream);
+
 /* Development knob: overrides a launch-shape default (see tuning.h for the names); value 0
  * restores the default.  Results do not depend on it. */
 int mxk_set_tuning(const char* name, int value);

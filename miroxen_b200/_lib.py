@@ -57,6 +57,10 @@ PROTOTYPES = {
     "mxk_reset_launch_count": (None, []),
     "mxk_set_tuning": (_I, [C.c_char_p, _I]),
     "mxk_device_error": (_I, [C.POINTER(_I), _I]),
+    "mxk_selftest_bounded_wait": (_I, [_P]),
+    "mxk_qdata_bytes": (_I64, [_I, _I64, _I64]),
+    "mxk_qscale_bytes": (_I64, [_I, _I64, _I64]),
+    "mxk_quantize_blockscaled": (_I, [_I, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "mxk_layernorm_mod": (_I, [_P, _I64, _I64, _F, RowMod, RowMod, _P, _P]),
     "mxk_rmsnorm_mod": (_I, [_P, _I64, _I64, _F, _P, RowMod, RowMod, _P, _P]),
     "mxk_rmsnorm_bf16": (_I, [_P, _I64, _I64, _F, _P, _P, _P]),

@@ -10,7 +10,16 @@
 //   static constexpr int NSRC;                                   1 or 2 source streams
 //   __device__ void locate(int64_t chunk, Chunk& c) const;        fills sources, destination, bytes
 //   __device__ uint4 apply(const uint4& a, const uint4& b) const; 8 bf16 (+8) in, 8 bf16 out
+//
+// An op whose output is not 16 bytes per 16 bytes (the block-scale quantiser, a reduction) defines a
+// per-thread `State` type instead of apply() and consumes a landed chunk itself:
+//   __device__ State init() const;                                 once per consumer thread, after the
+//                                                                  dependency wait
+//   __device__ void consume(State&, int64_t chunk, const unsigned char* stage, int tid, int n_cons) const;
+//   __device__ void finish(State&, int lane) const;                after the thread's last chunk
 #pragma once
+
+#include <type_traits>
 
 #include "bulk_copy.cuh"
 #include "common.cuh"
@@ -24,6 +33,11 @@ struct Chunk {
   unsigned char* dst;
   unsigned bytes;  // per source and of the destination; multiple of 16
 };
+
+template <class Op, class = void>
+struct consumes_itself : std::false_type {};
+template <class Op>
+struct consumes_itself<Op, std::void_t<typename Op::State>> : std::true_type {};
 
 __device__ __forceinline__ void mbar_arrive_one(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
@@ -77,6 +91,21 @@ __global__ void __launch_bounds__(544) stream_pipe_kernel(const Op op, const int
         if (++st == stages) st = 0, ph ^= (it >= stages ? 1u : 0u);
       }
     }
+  } else if constexpr (consumes_itself<Op>::value) {
+    typename Op::State state = op.init();
+    int st = 0;
+    unsigned ph = 0;
+    for (int it = 0; it < mine; it++) {
+      if (!mbar_wait(smem_u32(&full[st]), ph)) {
+        ok = false;
+        break;
+      }
+      op.consume(state, c_begin + it * c_step, dyn + size_t(st) * stage_bytes, tid, n_cons);
+      __syncwarp();
+      if (lane == 0) mbar_arrive_one(smem_u32(&empty[st]));
+      if (++st == stages) st = 0, ph ^= 1u;
+    }
+    op.finish(state, lane);
   } else {
     int st = 0;
     unsigned ph = 0;

@@ -9,6 +9,7 @@
 #include <cmath>
 #include <vector>
 
+#include "bulk_copy.cuh"
 #include "common.cuh"
 
 namespace mxk {
@@ -83,6 +84,20 @@ __global__ void __launch_bounds__(256)
   const float fr = __fsub_rn(pos, float(lo));
   const float a = table[lo * basis + j], b = table[(lo + 1) * basis + j];
   out[e] = __fadd_rn(a, __fmul_rn(__fsub_rn(b, a), fr));
+}
+
+// Self-test of the bounded wait: waits on an mbarrier that nothing ever completes, with a small try
+// budget, and reports the give-up the same way the pipelined kernels do (error word = 1).
+__global__ void bounded_wait_selftest_kernel(int tries, int* err) {
+  __shared__ __align__(8) unsigned long long bar;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  bool done = false;
+  for (int i = 0; i < tries && !done; i++) done = mbar_try(smem_u32(&bar), 0);
+  if (!__syncthreads_and(done) && threadIdx.x == 0 && err) atomicExch(err, kErrBulkTimeout);
 }
 
 const float* timestep_freqs() {
@@ -228,6 +243,11 @@ int mxk_qwen_timestep_embedding(float t, float* out, mxk_stream_t stream) {
   a.out = out;
   timestep_embedding_kernel<<<2, 128, 0, as_stream(stream)>>>(a);
   return after_launch("qwen_timestep_embedding");
+}
+
+int mxk_selftest_bounded_wait(mxk_stream_t stream) {
+  bounded_wait_selftest_kernel<<<1, 64, 0, as_stream(stream)>>>(4, device_error_word());
+  return after_launch("selftest_bounded_wait");
 }
 
 int mxk_h3_time_basis(const float* ts, int64_t nt, const float* table, int64_t grid, int64_t basis,

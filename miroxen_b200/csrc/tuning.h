@@ -30,6 +30,8 @@ enum TuneKey {
   TUNE_PDL,                // 2 disables programmatic dependent launch (default: on)
   TUNE_NORM_INTERLEAVE,    // 1: CTA i of the bulk-copy row kernels takes rows i, i + grid, ...; 2: contiguous ranges
   TUNE_PIPE_INTERLEAVE,    // same choice for the head and streaming pipelines (1 interleaved, 2 contiguous)
+  TUNE_QUANT_ROWS_PER_CTA, // rows per work item of the block-scale quantiser
+  TUNE_QUANT_PATH,         // 1 bulk-copy streaming pipeline for the quantiser, 2 register kernels
   TUNE_COUNT
 };
 

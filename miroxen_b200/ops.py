@@ -16,6 +16,7 @@ from . import _lib
 from ._lib import BlockArgs, HeadTensor, RopeRun, RowMod, check, lib
 
 ROPE_NONE, ROPE_INTERLEAVED, ROPE_HALF = 0, 1, 2
+Q_MXFP8, Q_NVFP4 = 1, 2  # QMode of src/kernels/blockscale.h:14 (0 = None is not a quantised mode)
 
 __all__ = [
     "ROPE_NONE", "ROPE_INTERLEAVED", "ROPE_HALF", "row_mod", "layernorm_mod", "rmsnorm_mod", "rmsnorm_bf16",
@@ -23,6 +24,7 @@ __all__ = [
     "scatter_rows", "silu_inplace_f32", "add_bias_bf16", "add_bias_f32", "f32_to_bf16", "bf16_to_f32", "axpy_f32",
     "axpby_f32", "gated_residual_norm", "qkv_norm_rope", "HeadSpec", "dit_block_ops", "BlockArgs", "RowMod",
     "HostPipeline", "OpTimes", "dit_block_ops_host_static", "device_error", "launch_count", "reset_launch_count", "set_tuning",
+    "Q_MXFP8", "Q_NVFP4", "QMat", "qdata_bytes", "qscale_bytes", "quantize_blockscaled",
 ]
 
 
@@ -207,6 +209,35 @@ def dit_block_ops_host_static(args: BlockArgs, stream=None):
     up, down = C.c_int64(0), C.c_int64(0)
     check(lib().mxk_dit_block_ops_host_static(C.byref(args), _stream(stream), C.byref(up), C.byref(down)))
     return up.value, down.value
+
+
+@dataclass
+class QMat:
+    """The reference's QMat (src/kernels/blockscale.h:21-25): quantised data, block scales in
+    cuBLASLt's interleaved layout, and for NVFP4 the device fp32 max|x| (tensor scale = amax / 2688)."""
+    q: torch.Tensor
+    sf: torch.Tensor
+    amax: Optional[torch.Tensor] = None
+
+
+def qdata_bytes(mode: int, rows: int, K: int) -> int:
+    return int(lib().mxk_qdata_bytes(mode, rows, K))
+
+
+def qscale_bytes(mode: int, rows: int, K: int) -> int:
+    return int(lib().mxk_qscale_bytes(mode, rows, K))
+
+
+def quantize_blockscaled(mode: int, x, ldx: int, rows: int, K: int, out: Optional[QMat] = None, stream=None) -> QMat:
+    """quantize_blockscaled(QMode, x, ldx, rows, K, out, stream) of src/kernels/blockscale.h:30; allocates
+    the QMat on x's device when `out` is None."""
+    if out is None:
+        dev = x.device
+        out = QMat(torch.empty(qdata_bytes(mode, rows, K), dtype=torch.uint8, device=dev),
+                   torch.empty(qscale_bytes(mode, rows, K), dtype=torch.uint8, device=dev),
+                   torch.empty(1, dtype=torch.float32, device=dev) if mode == Q_NVFP4 else None)
+    check(lib().mxk_quantize_blockscaled(mode, _p(x), ldx, rows, K, _p(out.q), _p(out.sf), _p(out.amax), _stream(stream)))
+    return out
 
 
 def device_error(clear: bool = True) -> int:

@@ -56,6 +56,15 @@ def have_ref_layout() -> bool:
     return (HERE / "_ref" / "libmx_ref_layout.so").exists()
 
 
+def have_ref_blockscale() -> bool:
+    return (HERE / "_ref" / "libmx_ref_blockscale.so").exists()
+
+
+def ref_blockscale() -> C.CDLL:
+    """The reference's src/kernels/blockscale.cu built for sm_100a (device pointers; needs a GPU)."""
+    return _load("_ref/libmx_ref_blockscale.so")
+
+
 def ref_ops() -> C.CDLL:
     """The reference's src/kernels/ops.cu built for sm_100a (device pointers; needs a GPU)."""
     return _load("_ref/libmx_ref_ops.so")
@@ -288,4 +297,53 @@ def h3_time_basis(ts, table):
     f = oracle().or_h3_time_basis
     f.argtypes, f.restype = [_P, _I64, _P, _I64, _I64, _P], None
     f(_ptr(ts), ts.size, _ptr(table), grid, basis, _ptr(out))
+    return out
+
+
+_U8 = C.c_uint8
+
+
+def f32_to_e4m3(v: np.ndarray) -> np.ndarray:
+    f = oracle().or_f32_to_e4m3
+    f.argtypes, f.restype = [_F], _U8
+    return np.array([f(float(a)) for a in np.asarray(v, np.float32).ravel()], np.uint8).reshape(np.shape(v))
+
+
+def e4m3_to_f32(b: np.ndarray) -> np.ndarray:
+    f = oracle().or_e4m3_to_f32
+    f.argtypes, f.restype = [_U8], _F
+    return np.array([f(int(a)) for a in np.asarray(b, np.uint8).ravel()], np.float32).reshape(np.shape(b))
+
+
+def qscale_bytes(mode, rows, K) -> int:
+    f = oracle().or_qscale_bytes
+    f.argtypes, f.restype = [C.c_int, _I64, _I64], _I64
+    return int(f(mode, rows, K))
+
+
+def sf_offset(r, kb, nkb_pad) -> int:
+    f = oracle().or_sf_offset
+    f.argtypes, f.restype = [_I64, _I64, _I64], _I64
+    return int(f(r, kb, nkb_pad))
+
+
+def quantize_blockscaled(mode, x, K=None):
+    """x: bf16 bits [rows, ldx] (uint16); quantises columns [0, K).  Returns (q, sf, amax)."""
+    x = np.ascontiguousarray(x, np.uint16)
+    rows, ldx = x.shape
+    K = ldx if K is None else K
+    q = np.zeros(rows * K // (2 if mode == 2 else 1), np.uint8)
+    sf = np.full(qscale_bytes(mode, rows, K), 0xAA, np.uint8)
+    amax = np.zeros(1, np.float32)
+    f = oracle().or_quantize_blockscaled
+    f.argtypes, f.restype = [C.c_int, _P, _I64, _I64, _I64, _P, _P, _P], None
+    f(mode, _ptr(x), ldx, rows, K, _ptr(q), _ptr(sf), _ptr(amax))
+    return q, sf, float(amax[0])
+
+
+def dequantize_blockscaled(mode, q, sf, amax, rows, K):
+    out = np.empty((rows, K), np.float32)
+    f = oracle().or_dequantize_blockscaled
+    f.argtypes, f.restype = [C.c_int, _P, _P, _F, _I64, _I64, _P], None
+    f(mode, _ptr(q), _ptr(sf), amax, rows, K, _ptr(out))
     return out

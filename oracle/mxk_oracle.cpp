@@ -17,6 +17,10 @@
 // code (tests/golden/h3_positions.npz).  The Qwen table builder and the timestep embedding have
 // no runnable counterpart outside the reference's model classes: for those two parity is
 // unpinned beyond the closed-form spot checks against libm in the tests.
+// The block-scale quantiser at the end of this file (src/kernels/blockscale.cu) is pinned the same
+// way as the ops: byte outputs of the reference's kernel on a B200 (tests/golden/
+// ref_blockscale_sm100a.npz), plus the error bounds of the reference's own test
+// (tests/blockscale_test.cpp:83-105) on the decoded values.
 #include <algorithm>
 #include <cmath>
 #include <cstdint>
@@ -412,6 +416,133 @@ void or_h3_time_basis(const float* ts, int64_t nt, const float* table, int64_t g
       out[i * basis + j] = a + (b - a) * fr;
     }
   }
+}
+
+}  // extern "C"
+
+// ---- activation block-scale quantiser (src/kernels/blockscale.cu:39-129) ----------------------
+//
+// e4m3 (4 exponent bits, bias 7, 3 mantissa bits, no infinity, 0x7f = NaN, largest finite 448):
+// round to nearest even, saturate to +-448 - what __nv_cvt_float_to_fp8(x, __NV_SATFINITE, __NV_E4M3)
+// of cuda_fp8.h returns, which the reference calls at blockscale.cu:100 and :122.
+static uint8_t f32_to_e4m3_satfinite(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  const uint8_t sign = uint8_t((u >> 24) & 0x80u);
+  const double a = std::fabs(double(f));
+  if (a != a) return 0x7f;
+  if (a >= 464.0) return sign | 0x7e;  // the midpoint 464 ties to the even 480, which saturates
+  if (a < 0.015625) {                  // below 2^-6: multiples of 2^-9; 8 of them is the first normal
+    return sign | uint8_t(std::nearbyint(a * 512.0));
+  }
+  int ex;
+  const double m = std::frexp(a, &ex);  // a = m 2^ex, m in [0.5, 1)
+  int E = ex - 1;
+  int mant = int(std::nearbyint((2.0 * m - 1.0) * 8.0));
+  if (mant == 8) mant = 0, E++;
+  const int code = ((E + 7) << 3) | mant;
+  return sign | uint8_t(code > 0x7e ? 0x7e : code);
+}
+
+static float e4m3_to_f32(uint8_t b) {
+  const int E = (b >> 3) & 15, m = b & 7;
+  if (E == 15 && m == 7) return NAN;
+  const float mag = E == 0 ? std::ldexp(float(m), -9) : std::ldexp(1.f + float(m) / 8.f, E - 7);
+  return (b & 0x80) ? -mag : mag;
+}
+
+// src/kernels/blockscale.cu:39-43
+static uint32_t e2m1_code(float x) {
+  const float a = std::fabs(x);
+  const uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) + (a >= 3.5f) + (a > 5.f);
+  return c | (x < 0.f ? 8u : 0u);
+}
+
+static inline int64_t pad_to(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+// Offset of the scale of (row r, scale block kb) in the 128 x 4 interleaved layout
+// (src/kernels/blockscale.cu:83 and :127).
+static inline int64_t sf_offset(int64_t r, int64_t kb, int64_t nkb_pad) {
+  return (r / 128) * nkb_pad * 128 + (r % 32) * 16 + (r % 128) / 32 * 4 + (kb / 4) * 512 + kb % 4;
+}
+
+extern "C" {
+
+uint8_t or_f32_to_e4m3(float f) { return f32_to_e4m3_satfinite(f); }
+float or_e4m3_to_f32(uint8_t b) { return e4m3_to_f32(b); }
+int64_t or_qscale_bytes(int mode, int64_t rows, int64_t K) { return pad_to(rows, 128) * pad_to(K / (mode == 2 ? 16 : 32), 4); }
+int64_t or_sf_offset(int64_t r, int64_t kb, int64_t nkb_pad) { return sf_offset(r, kb, nkb_pad); }
+
+// mode 1 MXFP8, 2 NVFP4.  x: bf16 bits [rows, ldx]; q, sf as the reference's QMat; amax: one float
+// (NVFP4 only).  The scale buffer is cleared first, padding included (blockscale.cu:154).
+void or_quantize_blockscaled(int mode, const uint16_t* x, int64_t ldx, int64_t rows, int64_t K, uint8_t* q, uint8_t* sf,
+                             float* amax) {
+  const int V = mode == 2 ? 16 : 32;
+  const int64_t nb = K / V, nkb_pad = pad_to(nb, 4);
+  memset(sf, 0, size_t(or_qscale_bytes(mode, rows, K)));
+  float g = 1.f, inv6g = 1.f;
+  if (mode == 2) {
+    float am = 0.f;  // blockscale.cu:47-70
+    for (int64_t r = 0; r < rows; r++)
+      for (int64_t k = 0; k < K; k++) am = std::fmax(am, std::fabs(bf2f(x[r * ldx + k])));
+    *amax = am;
+    g = am > 0.f ? am / (6.f * 448.f) : 1.f;  // blockscale.cu:79
+    inv6g = 1.f / (6.f * g);
+  }
+  parallel_rows(rows, [=](int64_t r0, int64_t r1) {
+    float v[32];
+    for (int64_t r = r0; r < r1; r++)
+      for (int64_t kb = 0; kb < nb; kb++) {
+        float bmax = 0.f;
+        for (int j = 0; j < V; j++) {
+          v[j] = bf2f(x[r * ldx + kb * V + j]);
+          bmax = std::fmax(bmax, std::fabs(v[j]));
+        }
+        uint8_t sbyte;
+        if (mode == 2) {  // blockscale.cu:99-109
+          const uint8_t se = f32_to_e4m3_satfinite(bmax * inv6g);
+          const float sd = e4m3_to_f32(se) * g;
+          const float inv = sd > 0.f ? 1.f / sd : 0.f;
+          uint8_t* dst = q + (r * K + kb * V) / 2;
+          for (int j = 0; j < 16; j += 2)
+            dst[j / 2] = uint8_t(e2m1_code(v[j] * inv) | (e2m1_code(v[j + 1] * inv) << 4));
+          sbyte = se;
+        } else {  // blockscale.cu:111-125
+          int e = -127;
+          if (bmax > 0.f) {
+            int ex;
+            const float mant = std::frexp(bmax / 448.f, &ex);
+            e = mant == 0.5f ? ex - 1 : ex;
+            e = std::max(-127, std::min(127, e));
+          }
+          const float inv = std::ldexp(1.f, -e);
+          for (int j = 0; j < 32; j++) q[r * K + kb * V + j] = f32_to_e4m3_satfinite(v[j] * inv);
+          sbyte = uint8_t(e + 127);
+        }
+        sf[sf_offset(r, kb, nkb_pad)] = sbyte;
+      }
+  });
+}
+
+// Decodes a quantised matrix back to fp32 [rows, K] (what the block-scaled GEMM multiplies by):
+// the test-side inverse, after the reference's own host decoder (tests/blockscale_test.cpp:25-52).
+void or_dequantize_blockscaled(int mode, const uint8_t* q, const uint8_t* sf, float amax, int64_t rows, int64_t K, float* out) {
+  static const float kE2m1[8] = {0.f, 0.5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f};
+  const int V = mode == 2 ? 16 : 32;
+  const int64_t nkb_pad = pad_to(K / V, 4);
+  const float g = mode == 2 ? (amax > 0.f ? amax / (6.f * 448.f) : 1.f) : 1.f;
+  for (int64_t r = 0; r < rows; r++)
+    for (int64_t k = 0; k < K; k++) {
+      const uint8_t sb = sf[sf_offset(r, k / V, nkb_pad)];
+      if (mode == 2) {
+        const uint8_t byte = q[(r * K + k) / 2];
+        const uint32_t c = (k & 1) ? byte >> 4 : byte & 15;
+        const float mag = kE2m1[c & 7] * e4m3_to_f32(sb) * g;
+        out[r * K + k] = (c & 8) ? -mag : mag;
+      } else {
+        out[r * K + k] = e4m3_to_f32(q[r * K + k]) * std::ldexp(1.f, int(sb) - 127);
+      }
+    }
 }
 
 }  // extern "C"

@@ -1,0 +1,156 @@
+"""libmxk's block-scale quantiser through the C ABI: byte-exact against the CPU oracle, against the
+golden outputs of the REFERENCE's kernel, and - where oracle/_ref/libmx_ref_blockscale.so travelled with
+the tree - against that kernel run side by side on the same device buffers."""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import helpers as H
+from oracle import binding as orc
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+sys.path.insert(0, str(GOLD))
+import ref_blockscale_cases  # noqa: E402
+from make_ref_blockscale_golden import run_reference  # noqa: E402
+from test_cpu_blockscale import ELEM_ERR, GOLDEN, bits_to_f32, rel_rms  # noqa: E402
+
+CASES = ref_blockscale_cases.cases()
+
+
+@pytest.fixture(scope="module", params=["bulk_copy", "registers"])
+def mx(request):
+    """Every test runs with the bulk-copy streaming pipeline (the default) and with the register kernels."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import miroxen_b200 as m
+    m.lib()
+    m.set_tuning("quant_path", 1 if request.param == "bulk_copy" else 2)
+    yield m
+    torch.cuda.synchronize()
+    assert m.device_error() == 0, "a kernel's bounded wait ran out"
+    m.set_tuning("quant_path", 0)
+
+
+def mxk_quant(mx, mode, x_bits, K, guard=True):
+    """Runs mxk_quantize_blockscaled; outputs sit between poisoned guard bands."""
+    rows, ldx = x_bits.shape
+    x = torch.from_numpy(np.ascontiguousarray(x_bits)).cuda()
+    q = H.Guarded(torch, (mx.ops.qdata_bytes(mode, rows, K),), torch.uint8)
+    sf = H.Guarded(torch, (mx.ops.qscale_bytes(mode, rows, K),), torch.uint8)
+    sf.t.fill_(0x5A)
+    amax = torch.full((1,), -1.0, dtype=torch.float32, device="cuda") if mode == 2 else None
+    mx.ops.quantize_blockscaled(mode, x, ldx, rows, K, mx.ops.QMat(q.t, sf.t, amax))
+    torch.cuda.synchronize()
+    q.check("q")
+    sf.check("sf")
+    return q.t.cpu().numpy(), sf.t.cpu().numpy(), (float(amax.item()) if mode == 2 else 0.0)
+
+
+def assert_same(name, got, want):
+    (q, sf, amax), (rq, rsf, ramax) = got, want
+    assert np.array_equal(sf, rsf), f"{name}: {(sf != rsf).sum()} scale bytes differ"
+    assert np.array_equal(q, rq), f"{name}: {(q != rq).sum()} of {q.size} data bytes differ"
+    assert np.float32(amax) == np.float32(ramax), name
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_cases_match_oracle_and_golden(mx, name):
+    c = CASES[name]
+    got = mxk_quant(mx, c["mode"], c["x"], c["K"])
+    assert_same(name, got, orc.quantize_blockscaled(c["mode"], c["x"], c["K"]))
+    gold = np.load(GOLDEN)
+    assert_same(name + " (reference kernel bytes)", got,
+                (gold[name + ".q"], gold[name + ".sf"], gold[name + ".amax"][0] if c["mode"] == 2 else 0.0))
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("rows,K,ldx", [(1, 32, 32), (3, 64, 72), (127, 96, 96), (128, 128, 128), (129, 160, 168),
+                                         (257, 2048, 2048), (40, 2080, 2088), (33, 4096 + 32, 4096 + 32),
+                                         (1000, 3072, 3072), (515, 12288, 12288)])
+def test_shapes_match_oracle(mx, mode, rows, K, ldx):
+    g = H.rng(rows * 7 + K + mode)
+    a = H.normal_f32(g, (rows, ldx), 1.5)
+    a[:, ::53] *= 30.0
+    bits = orc.f32_to_bf16_bits(a)
+    assert_same(f"{rows}x{K}", mxk_quant(mx, mode, bits, K), orc.quantize_blockscaled(mode, bits, K))
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("knob,value", [("quant_rows_per_cta", 1), ("quant_rows_per_cta", 3), ("quant_rows_per_cta", 64),
+                                        ("stream_chunk_kb", 1), ("stream_chunk_kb", 2), ("stream_stages", 2),
+                                        ("stream_warps", 3), ("stream_ctas_per_sm", 1)])
+def test_work_split_does_not_change_bytes(mx, mode, knob, value):
+    """Row strips, row pieces (1 KB chunks cut the 2112-byte rows in three), pipeline depth and a grid
+    of one CTA per SM, where every CTA wraps its ring of stages many times."""
+    g = H.rng(90 + value)
+    bits = H.normal_bf16(g, (1777, 1056), 2.0)
+    want = orc.quantize_blockscaled(mode, bits)
+    mx.ops.set_tuning(knob, value)
+    try:
+        assert_same(f"{knob}={value}", mxk_quant(mx, mode, bits, 1056), want)
+    finally:
+        mx.ops.set_tuning(knob, 0)
+
+
+@pytest.mark.parametrize("mode", [1, 2])
+def test_block_size_workload_matches_oracle_and_error_bound(mx, mode):
+    """One image-stream activation of the benchmark's block: 8704 rows of 3072 (> L2 with its outputs)."""
+    g = H.rng(5)
+    rows, K = 8704, 3072
+    a = H.normal_f32(g, (rows, K), 1.0)
+    a[:, ::211] *= 25.0
+    bits = orc.f32_to_bf16_bits(a)
+    orc.set_threads(8)
+    try:
+        want = orc.quantize_blockscaled(mode, bits)
+    finally:
+        orc.set_threads(1)
+    got = mxk_quant(mx, mode, bits, K)
+    assert_same("8704x3072", got, want)
+    d = orc.dequantize_blockscaled(mode, got[0], got[1], got[2], rows, K)
+    assert rel_rms(d, bits_to_f32(bits)) < ELEM_ERR[mode]
+
+
+def test_second_call_reuses_buffers_and_clears_padding(mx):
+    g = H.rng(11)
+    big, small = H.normal_bf16(g, (100, 160), 3.0), H.normal_bf16(g, (100, 160), 0.01)
+    for mode in (1, 2):
+        x = torch.from_numpy(big).cuda()
+        out = mx.ops.quantize_blockscaled(mode, x, 160, 100, 160)
+        x.copy_(torch.from_numpy(small))
+        mx.ops.quantize_blockscaled(mode, x, 160, 100, 160, out)
+        torch.cuda.synchronize()
+        want = orc.quantize_blockscaled(mode, small)
+        assert_same("second call", (out.q.cpu().numpy(), out.sf.cpu().numpy(), float(out.amax.item()) if mode == 2 else 0.0), want)
+
+
+def test_argument_errors(mx):
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
+    out = mx.ops.quantize_blockscaled(1, x, 64, 4, 64)
+    for bad in (dict(mode=0), dict(K=48), dict(ldx=60), dict(ldx=32), dict(mode=3)):
+        kw = dict(mode=1, ldx=64, K=64)
+        kw.update(bad)
+        with pytest.raises(mx.MxkError):
+            mx.ops.quantize_blockscaled(kw["mode"], x, kw["ldx"], 4, kw["K"], out)
+    with pytest.raises(mx.MxkError):  # NVFP4 needs the amax slot
+        mx.ops.quantize_blockscaled(2, x, 64, 4, 64, mx.ops.QMat(out.q, out.sf, None))
+    with pytest.raises(mx.MxkError):  # misaligned input
+        mx.ops.quantize_blockscaled(1, x.view(-1)[1:].data_ptr(), 64, 3, 64, out)
+    mx.ops.quantize_blockscaled(1, x, 64, 0, 64, out)  # no rows: nothing to do
+    torch.cuda.synchronize()
+
+
+@pytest.mark.skipif(not orc.have_ref_blockscale(), reason="oracle/_ref/libmx_ref_blockscale.so not built")
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("rows,K,ldx", [(130, 384, 384), (37, 160, 168), (2049, 3072, 3072), (300, 12288, 12288)])
+def test_side_by_side_with_reference_kernel(mx, mode, rows, K, ldx):
+    g = H.rng(rows + K)
+    a = H.normal_f32(g, (rows, ldx), 1.2)
+    a[:, ::101] *= 17.0
+    bits = orc.f32_to_bf16_bits(a)
+    rq, rsf, ramax = run_reference(orc.ref_blockscale(), mode, bits, K)
+    assert_same("reference kernel", mxk_quant(mx, mode, bits, K), (rq, rsf, float(ramax[0]) if mode == 2 else 0.0))

@@ -207,3 +207,19 @@ def test_host_pipeline_equals_device_chain(mx, cfg):
     for k in ("h1", "q_out", "k_out", "h2", "act"):
         assert np.array_equal(H.bits(td[k]), th[k].view(torch.uint16).numpy()), k
     assert np.array_equal(td["x"].cpu().numpy(), th["x"].numpy())
+
+
+def test_bounded_wait_reports_and_context_survives(mx):
+    """A wait that can never be satisfied (a barrier nothing completes) runs out of its budget, the
+    kernel reports through the device error word and returns; the context keeps working."""
+    from miroxen_b200 import _lib
+    assert mx.device_error() == 0
+    _lib.check(mx.lib().mxk_selftest_bounded_wait(None))
+    torch.cuda.synchronize()
+    assert mx.device_error(clear=True) == 1
+    assert mx.device_error() == 0
+    x = torch.ones(1024, device="cuda")
+    y = torch.full((1024,), 2.0, device="cuda")
+    mx.axpy_f32(x, y, 0.5, 1024)
+    torch.cuda.synchronize()
+    assert float(x.sum()) == 2048.0
