@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the second chain and the per-op pass")
+    ap.add_argument("--quant-only", action="store_true",
+                    help="time only the block-scale quantiser on the block's activations (profiling aid; prints its own line)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
                     help="override a launch-shape knob of libmxk (see miroxen_b200/csrc/tuning.h); repeatable")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (default: chosen for ~10-30 s)")
@@ -351,16 +353,65 @@ def main():
         launches = mx.launch_count()
         return max_over_ranks(e0.elapsed_time(e1)) / K, launches, cs.summary()
 
-    K, Wm = max(args.steps, 1), max(args.warmup, 3)
-    ms, launches, clocks = timed(step, K, Wm)
-    job_bytes = w.bytes_per_row() * total_rows
-    value = job_bytes / (ms * 1e-3) / 1e9
+    def quant_rows():
+        """The step that follows these ops on the reference's fp8 / fp4 path: the activation block-scale
+        quantiser, timed on this block's norm output [rows, dim] and MLP activation [rows, F]."""
+        if args.impl == "reference-cuda":
+            from oracle import binding as orc
+            if not orc.have_ref_blockscale():
+                return {"unavailable": "oracle/_ref/libmx_ref_blockscale.so not built"}
+            import ctypes as C
+            L = orc.ref_blockscale()
+            L.ref_quantize_blockscaled.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
+                                                   C.c_void_p, C.c_void_p, C.c_void_p]
 
+            def quant(mode, t, cols, out):
+                if L.ref_quantize_blockscaled(mode, t.data_ptr(), cols, rows, cols, out.q.data_ptr(), out.sf.data_ptr(),
+                                              out.amax.data_ptr() if out.amax is not None else None, sp):
+                    raise RuntimeError("reference quantize_blockscaled failed")
+        else:
+            def quant(mode, t, cols, out):
+                mx.ops.quantize_blockscaled(mode, t, cols, rows, cols, out, stream)
+        q_ops = []
+        for mode, mname, per_el in ((mx.ops.Q_MXFP8, "mxfp8", 2 + 1 + 1 / 32), (mx.ops.Q_NVFP4, "nvfp4", 2 + 2 + 0.5 + 1 / 16)):
+            for src_name, cols in (("h1", w.dim), ("act", w.F)):
+                srcs = [getattr(b, src_name) for b in sets]
+                outs = [mx.ops.QMat(torch.empty(mx.ops.qdata_bytes(mode, rows, cols), dtype=torch.uint8, device="cuda"),
+                                    torch.empty(mx.ops.qscale_bytes(mode, rows, cols), dtype=torch.uint8, device="cuda"),
+                                    torch.empty(1, dtype=torch.float32, device="cuda") if mode == mx.ops.Q_NVFP4 else None)
+                        for _ in srcs]
+                for i in range(3):
+                    quant(mode, srcs[i % n_sets], cols, outs[i % n_sets])
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for i in range(K):
+                    quant(mode, srcs[i % n_sets], cols, outs[i % n_sets])
+                e1.record(stream)
+                barrier()
+                us = e0.elapsed_time(e1) / K * 1e3
+                by = per_el * rows * cols
+                q_ops.append({"op": f"quantize_{mname}", "input": f"{src_name} [{rows}, {cols}]", "us": round(us, 2),
+                              "bytes": int(by), "gbs": round(by / us / 1e3, 1), "frac": round(by / us / 1e3 / peak_gbs, 3)})
+                del outs
+        return {"quantize_blockscaled": q_ops,
+                "note": "bytes = bf16 read + codes + scales; nvfp4 reads the input twice (tensor amax first)"}
+
+    K, Wm = max(args.steps, 1), max(args.warmup, 3)
     peaks = {}
     pk = ROOT / "MEASURED_PEAKS.json"
     if pk.exists():
         peaks = json.loads(pk.read_text())
     peak_gbs, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+
+    if args.quant_only:
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "workload": w.name, "steps": K, "next_rows": quant_rows()}), flush=True)
+        return
+
+    ms, launches, clocks = timed(step, K, Wm)
+    job_bytes = w.bytes_per_row() * total_rows
+    value = job_bytes / (ms * 1e-3) / 1e9
 
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": n_gpus, "steps": K, "warmup": Wm,
@@ -376,6 +427,8 @@ def main():
     if args.impl != "mxk":
         line["impl"] = args.impl
         line["gpu_launches"] = 7 * K if not w.packed_qkv else 8 * K
+        if not args.no_extras:
+            line["next_rows"] = quant_rows()
         print(json.dumps(line), flush=True)
         return
 
@@ -435,29 +488,7 @@ def main():
             b.args.fused = 1 if args.chain == "fused" else 0
 
     if not args.no_extras and n_gpus == 1:
-        # the step that follows these ops on the reference's fp8 / fp4 path: the activation block-scale
-        # quantiser, timed on this block's norm output [rows, dim] and MLP activation [rows, F]
-        q_ops = []
-        for mode, mname, per_el in ((mx.ops.Q_MXFP8, "mxfp8", 2 + 1 + 1 / 32), (mx.ops.Q_NVFP4, "nvfp4", 2 + 2 + 0.5 + 1 / 16)):
-            for src_name, cols in (("h1", w.dim), ("act", w.F)):
-                srcs = [getattr(b, src_name) for b in sets]
-                outs = [mx.ops.quantize_blockscaled(mode, t, cols, rows, cols, stream=stream) for t in srcs]
-                for i in range(3):
-                    mx.ops.quantize_blockscaled(mode, srcs[i % n_sets], cols, rows, cols, outs[i % n_sets], stream)
-                barrier()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                for i in range(K):
-                    mx.ops.quantize_blockscaled(mode, srcs[i % n_sets], cols, rows, cols, outs[i % n_sets], stream)
-                e1.record(stream)
-                barrier()
-                us = e0.elapsed_time(e1) / K * 1e3
-                by = per_el * rows * cols
-                q_ops.append({"op": f"quantize_{mname}", "input": f"{src_name} [{rows}, {cols}]", "us": round(us, 2),
-                              "bytes": int(by), "gbs": round(by / us / 1e3, 1), "frac": round(by / us / 1e3 / peak_gbs, 3)})
-                del outs
-        line["next_rows"] = {"quantize_blockscaled": q_ops,
-                             "note": "bytes = bf16 read + codes + scales; nvfp4 reads the input twice (tensor amax first)"}
+        line["next_rows"] = quant_rows()
 
     if not args.no_e2e:
         # end to end: pinned host buffers in, results back in host memory, every step

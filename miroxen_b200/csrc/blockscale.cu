@@ -10,12 +10,15 @@
 // e4m3 conversion of cuda_fp8.h with saturation, __frcp_rn for the NVFP4 block reciprocal, and
 // the same threshold ladder for e2m1.
 //
-// Work layout: 4 lanes share a 32-element block (2 lanes a 16-element one), one 128-bit vector per
-// lane, block maximum by 2 (1) shuffle steps, 64-bit (32-bit) packed stores, so a warp's accesses are
-// contiguous segments.  Default path: the bulk-copy streaming pipeline (stream_pipe.cuh) - a producer
-// warp lands row pieces of up to 8 KB in shared memory, consumer warps quantise from there; NVFP4's
-// tensor maximum is a first pass through the same pipeline.  quant_path = 2 selects plain register
-// kernels (also taken when a row piece cannot be cut on a block boundary).
+// Work layout: a thread owns 16 consecutive elements (two 128-bit vectors): a whole NVFP4 block, half
+// an MXFP8 block (one shuffle joins the two halves' maxima).  It stores 128 (64) bits of codes, so a
+// warp's stores are one contiguous segment.  The arithmetic is packed where the result is the same
+// bits: |.|-maxima on bf16 pairs (max.xorsign.abs.bf16x2; a maximum picks one of its inputs), scaling
+// on fp32 pairs (mul.rn.f32x2), conversion two elements per instruction.  Default path: the bulk-copy
+// streaming pipeline (stream_pipe.cuh) - a producer warp lands row pieces of up to 8 KB in shared
+// memory, consumer warps quantise from there; NVFP4's tensor maximum is a first pass through the same
+// pipeline.  quant_path = 2 selects plain register kernels (also taken when a row piece cannot be cut
+// on a block boundary).
 //
 // Three steps are computed differently from the reference but give the same bits:
 //  - the ue8m0 exponent comes from the bits of the block maximum instead of frexpf(bmax / 448): with
@@ -39,17 +42,15 @@ namespace {
 constexpr float kFp4Range = 6.f * 448.f;  // src/kernels/blockscale.cu:33
 constexpr int kRowsInFlight = 4;
 
-__device__ __forceinline__ void st_stream32(unsigned int* p, unsigned int v) { __stcs(p, v); }
-
 __host__ __device__ inline int64_t pad_to(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 
 // Two floats -> two e4m3 bytes (x in the low byte), round to nearest even, saturating.
-__device__ __forceinline__ uint32_t e4m3x2(float x, float y) {
-  return __nv_cvt_float2_to_fp8x2(make_float2(x, y), __NV_SATFINITE, __NV_E4M3);
+__device__ __forceinline__ uint32_t e4m3x2(float2 v) {
+  return __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E4M3);
 }
 
-// Eight floats -> eight e2m1 codes, element 0 in the lowest nibble.
-__device__ __forceinline__ uint32_t e2m1x8(const float (&v)[8]) {
+// Four float pairs -> eight e2m1 codes, element 0 in the lowest nibble.
+__device__ __forceinline__ uint32_t e2m1x8(float2 a, float2 b, float2 c, float2 d) {
   uint32_t w;
   asm("{ .reg .b8 b0, b1, b2, b3;\n"
       "cvt.rn.satfinite.e2m1x2.f32 b0, %2, %1;\n"
@@ -58,8 +59,7 @@ __device__ __forceinline__ uint32_t e2m1x8(const float (&v)[8]) {
       "cvt.rn.satfinite.e2m1x2.f32 b3, %8, %7;\n"
       "mov.b32 %0, {b0, b1, b2, b3}; }"
       : "=r"(w)
-      : "f"(v[0] + 0.f), "f"(v[1] + 0.f), "f"(v[2] + 0.f), "f"(v[3] + 0.f), "f"(v[4] + 0.f), "f"(v[5] + 0.f),
-        "f"(v[6] + 0.f), "f"(v[7] + 0.f));
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y), "f"(d.x), "f"(d.y));
   return w;
 }
 
@@ -79,51 +79,75 @@ __device__ __forceinline__ Fp4Scale fp4_scale(const float* amax) {
   return s;
 }
 
-// Quantises the 8 elements of one lane given the maximum of its scale block; returns the scale byte.
-// MXFP8: codes in (lo, hi); NVFP4: codes in lo.
+// max(|a|, |b|) on both bf16 halves; the sign bits of the result are meaningless.
+__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t absmax_bf16x2(const uint4& u) {
+  return absmax_bf16x2(absmax_bf16x2(u.x, u.y), absmax_bf16x2(u.z, u.w));
+}
+// Largest magnitude of the two halves, as fp32 (a bf16 value).
+__device__ __forceinline__ float bf16x2_max_to_float(uint32_t m) {
+  m = absmax_bf16x2(m, __byte_perm(m, 0, 0x1032));
+  return __uint_as_float((m << 16) & 0x7fff0000u);
+}
+__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
+  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
+
+// Quantises the 16 elements of one thread: raw = two vectors of 8 bf16.  MODE 1: bmax_bits is the
+// packed maximum over the thread's half block; out = 16 e4m3 bytes.  MODE 2: out.x, out.y = 16 e2m1
+// codes.  Returns the scale byte.
 template <int MODE>
-__device__ __forceinline__ uint8_t quant8(const float (&v)[8], float bmax, const Fp4Scale& fs, uint32_t& lo, uint32_t& hi) {
+__device__ __forceinline__ uint8_t quant16(const uint4 (&raw)[2], uint32_t packed_max, const Fp4Scale& fs, uint4& out) {
+  const uint32_t w[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
   if (MODE == 2) {
     // src/kernels/blockscale.cu:100-109
+    const float bmax = bf16x2_max_to_float(packed_max);
     const __nv_fp8_storage_t se = __nv_cvt_float_to_fp8(__fmul_rn(bmax, fs.inv6g), __NV_SATFINITE, __NV_E4M3);
     __nv_fp8_e4m3 sq;
     sq.__x = se;
     const float sd = __fmul_rn(float(sq), fs.g);
     const float inv = sd > 0.f ? __frcp_rn(sd) : 0.f;
-    float t[8];
+    const float2 inv2 = make_float2(inv, inv), zero2 = make_float2(0.f, 0.f);
+    float2 t[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) t[i] = __fmul_rn(v[i], inv);
-    lo = e2m1x8(t);
-    hi = 0;
+    for (int i = 0; i < 8; i++) t[i] = __fadd2_rn(__fmul2_rn(bf16x2_to_float2(w[i]), inv2), zero2);  // -0 -> +0
+    out.x = e2m1x8(t[0], t[1], t[2], t[3]);
+    out.y = e2m1x8(t[4], t[5], t[6], t[7]);
+    out.z = out.w = 0;
     return se;
   }
   // ue8m0: the smallest 2^e with bmax / 2^e <= 448 (src/kernels/blockscale.cu:111-119), from the bits
-  // of bmax (see the head of this file); bmax is a bf16 value, so its low 16 bits are zero.
-  const uint32_t b = __float_as_uint(bmax);
+  // of bmax (see the head of this file).
+  const uint32_t b = __float_as_uint(bf16x2_max_to_float(packed_max));
   const int E = int(b >> 23);  // biased exponent; 0 for zero and subnormals, whose e clamps to -127
   int e = E - 127 - 8 + ((b & 0x007fffffu) > 0x00600000u ? 1 : 0);
   e = E == 0 ? -127 : max(-127, e);
   // 2^-e: e is in [-127, 120], so -e + 127 is in [7, 254]
   const float inv = __uint_as_float(uint32_t(127 - e) << 23);
-  lo = e4m3x2(__fmul_rn(v[0], inv), __fmul_rn(v[1], inv)) | e4m3x2(__fmul_rn(v[2], inv), __fmul_rn(v[3], inv)) << 16;
-  hi = e4m3x2(__fmul_rn(v[4], inv), __fmul_rn(v[5], inv)) | e4m3x2(__fmul_rn(v[6], inv), __fmul_rn(v[7], inv)) << 16;
+  const float2 inv2 = make_float2(inv, inv);
+  uint32_t c[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) c[i] = e4m3x2(__fmul2_rn(bf16x2_to_float2(w[i]), inv2));
+  out = make_uint4(c[0] | c[1] << 16, c[2] | c[3] << 16, c[4] | c[5] << 16, c[6] | c[7] << 16);
   return uint8_t(e + 127);
 }
 
-template <int LPB>
-__device__ __forceinline__ float block_max(const float (&v)[8]) {
-  float m = 0.f;
-#pragma unroll
-  for (int i = 0; i < 8; i++) m = fmaxf(m, fabsf(v[i]));
-#pragma unroll
-  for (int o = LPB / 2; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+// Packed |.|-maximum of a thread's 16 elements, joined with the other half of the block for MXFP8.
+template <int MODE>
+__device__ __forceinline__ uint32_t block_absmax(const uint4 (&raw)[2]) {
+  uint32_t m = absmax_bf16x2(absmax_bf16x2(raw[0]), absmax_bf16x2(raw[1]));
+  if (MODE == 1) m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));
   return m;
 }
 
 // Address of the scale of (row r, scale block kb): 128 x 4 tiles of 512 bytes
 // (src/kernels/blockscale.cu:83 and :127).
-__device__ __forceinline__ int64_t sf_row_offset(int64_t r, int nkb_pad) {
-  return (r / 128) * int64_t(nkb_pad) * 128 + (r % 32) * 16 + (r % 128) / 32 * 4;
+__device__ __forceinline__ int64_t sf_row_offset(uint64_t r, int nkb_pad) {
+  return int64_t(r >> 7) * (int64_t(nkb_pad) * 128) + int64_t((r & 31) * 16 + ((r >> 5) & 3) * 4);
 }
 __device__ __forceinline__ int sf_col_offset(int kb) { return (kb >> 2) * 512 + (kb & 3); }
 
@@ -140,13 +164,20 @@ struct RowPieces {
   const unsigned char* x;
   int64_t ldx_bytes;
   int K, pieces_per_row, piece_elems;
-  __device__ void where(int64_t chunk, int64_t& row, int& k0, int& n) const {
-    row = chunk / pieces_per_row;
-    k0 = int(chunk - row * pieces_per_row) * piece_elems;
+  // chunk < 2^31 (checked by the launcher): 32-bit arithmetic, and no division in the common case of
+  // one piece per row - this runs once per chunk in every consumer thread
+  __device__ __forceinline__ void where(int64_t chunk, unsigned& row, int& k0, int& n) const {
+    const unsigned c = unsigned(chunk);
+    if (pieces_per_row == 1) {
+      row = c, k0 = 0, n = K;
+      return;
+    }
+    row = c / unsigned(pieces_per_row);
+    k0 = int(c - row * unsigned(pieces_per_row)) * piece_elems;
     n = K - k0 < piece_elems ? K - k0 : piece_elems;
   }
   __device__ void locate(int64_t chunk, Chunk& c) const {
-    int64_t row;
+    unsigned row;
     int k0, n;
     where(chunk, row, k0, n);
     c.src0 = x + row * ldx_bytes + int64_t(k0) * 2, c.src1 = nullptr, c.dst = nullptr;
@@ -158,25 +189,20 @@ struct AmaxPipeOp : RowPieces {
   static constexpr int NSRC = 1;
   float* out;
   struct State {
-    float m;
+    uint32_t m;  // two running bf16 maxima
   };
-  __device__ State init() const { return State{0.f}; }
+  __device__ State init() const { return State{0u}; }
   __device__ void consume(State& st, int64_t chunk, const unsigned char* stage, int tid, int n_cons) const {
-    int64_t row;
+    unsigned row;
     int k0, n;
     where(chunk, row, k0, n);
     const uint4* s = reinterpret_cast<const uint4*>(stage);
     const int nvec = n >> 3;
-    float m = st.m;
-    for (int i = tid; i < nvec; i += n_cons) {
-      float v[8];
-      unpack8(s[i], v);
-#pragma unroll
-      for (int j = 0; j < 8; j++) m = fmaxf(m, fabsf(v[j]));
-    }
+    uint32_t m = st.m;
+    for (int i = tid; i < nvec; i += n_cons) m = absmax_bf16x2(m, absmax_bf16x2(s[i]));
     st.m = m;
   }
-  __device__ void finish(State& st, int) const { amax_commit(st.m, out); }
+  __device__ void finish(State& st, int) const { amax_commit(bf16x2_max_to_float(st.m), out); }
 };
 
 template <int MODE>
@@ -190,35 +216,26 @@ struct QuantPipeOp : RowPieces {
   using State = Fp4Scale;
   __device__ State init() const { return MODE == 2 ? fp4_scale(amax) : Fp4Scale{1.f, 1.f}; }
   __device__ void consume(State& fs, int64_t chunk, const unsigned char* stage, int tid, int n_cons) const {
-    constexpr int U = 2;
-    int64_t row;
+    unsigned row;
     int k0, n;
     where(chunk, row, k0, n);
     const uint4* s = reinterpret_cast<const uint4*>(stage);
-    const int nvec = n >> 3, lane = tid & 31;
+    const int n16 = n >> 4, lane = tid & 31;  // n is a multiple of 32: the two halves of a block are both in range
     uint8_t* sfr = sf + sf_row_offset(row, nkb_pad);
-    uint8_t* qrow = q + (row * K + k0) / (MODE == 2 ? 2 : 1);
-    // every lane of a warp runs the same trips (the block maximum is a warp shuffle); a piece holds
-    // whole scale blocks, so the lanes of one block are on or off together
-    for (int i0 = tid - lane; i0 < nvec; i0 += U * n_cons) {
-      uint4 raw[U];
-#pragma unroll
-      for (int u = 0; u < U; u++) {
-        const int i = i0 + u * n_cons + lane;
-        raw[u] = i < nvec ? s[i] : make_uint4(0u, 0u, 0u, 0u);
-      }
-#pragma unroll
-      for (int u = 0; u < U; u++) {
-        const int i = i0 + u * n_cons + lane;
-        float v[8];
-        unpack8(raw[u], v);
-        const float bmax = block_max<LPB>(v);
-        uint32_t lo, hi;
-        const uint8_t sbyte = quant8<MODE>(v, bmax, fs, lo, hi);
-        if (i < nvec) {
-          if (MODE == 2) st_stream32(reinterpret_cast<unsigned int*>(qrow) + i, lo);
-          else st_stream(reinterpret_cast<uint2*>(qrow) + i, make_uint2(lo, hi));
-          if ((lane & (LPB - 1)) == 0) sfr[sf_col_offset((k0 + i * 8) / V)] = sbyte;
+    uint8_t* qrow = q + (int64_t(row) * K + k0) / (MODE == 2 ? 2 : 1);
+    // every lane of a warp runs the same trips (the block maximum is a warp shuffle)
+    for (int i0 = tid - lane; i0 < n16; i0 += n_cons) {
+      const int i = i0 + lane, ic = i < n16 ? i : n16 - 1;  // lanes past the end compute on a copy, store nothing
+      const uint4 raw[2] = {s[2 * ic], s[2 * ic + 1]};
+      uint4 out;
+      const uint8_t sbyte = quant16<MODE>(raw, block_absmax<MODE>(raw), fs, out);
+      if (i < n16) {
+        if (MODE == 2) {
+          st_stream(reinterpret_cast<uint2*>(qrow) + i, make_uint2(out.x, out.y));
+          sfr[sf_col_offset((k0 >> 4) + i)] = sbyte;
+        } else {
+          st_stream(reinterpret_cast<uint4*>(qrow) + i, out);
+          if ((lane & 1) == 0) sfr[sf_col_offset((k0 >> 5) + (i >> 1))] = sbyte;
         }
       }
     }
@@ -234,7 +251,7 @@ __global__ void __launch_bounds__(256) amax_kernel(const bf16* __restrict__ x, i
   constexpr int U = kRowsInFlight;
   pdl_launch_dependents();
   pdl_wait();
-  float m = 0.f;
+  uint32_t m = 0u;
   for (int64_t r = int64_t(blockIdx.x) * U; r < rows; r += int64_t(gridDim.x) * U) {
     for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
       uint4 raw[U];
@@ -242,57 +259,51 @@ __global__ void __launch_bounds__(256) amax_kernel(const bf16* __restrict__ x, i
       for (int u = 0; u < U; u++)
         raw[u] = r + u < rows ? ld_stream(reinterpret_cast<const uint4*>(x + (r + u) * ldx) + j) : make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
-      for (int u = 0; u < U; u++) {
-        float f[8];
-        unpack8(raw[u], f);
-#pragma unroll
-        for (int i = 0; i < 8; i++) m = fmaxf(m, fabsf(f[i]));
-      }
+      for (int u = 0; u < U; u++) m = absmax_bf16x2(m, absmax_bf16x2(raw[u]));
     }
   }
-  amax_commit(m, out);
+  amax_commit(bf16x2_max_to_float(m), out);
 }
 
-// MODE 1 = MXFP8, 2 = NVFP4.  Thread t of CTA column blockIdx.y owns the 8 elements starting at
-// column 8 * (blockIdx.y * blockDim.x + t) of every row it visits.
+// MODE 1 = MXFP8, 2 = NVFP4.  Thread t of CTA column blockIdx.y owns the 16 elements starting at
+// column 16 * (blockIdx.y * blockDim.x + t) of every row it visits.
 template <int MODE>
 __global__ void __launch_bounds__(256) quant_kernel(const bf16* __restrict__ x, int64_t ldx, int64_t rows, int K,
                                                      uint8_t* __restrict__ q, uint8_t* __restrict__ sf, const float* amax,
                                                      int rows_per_chunk) {
-  constexpr int V = MODE == 2 ? 16 : 32;   // elements per scale block
-  constexpr int LPB = V / 8;               // lanes per scale block
+  constexpr int V = MODE == 2 ? 16 : 32;  // elements per scale block
   constexpr int U = kRowsInFlight;
   pdl_launch_dependents();
   pdl_wait();
-  const int vec = blockIdx.y * blockDim.x + threadIdx.x;  // 8-element vector index inside the row
-  const bool col_on = vec * 8 < K;
+  const int col = blockIdx.y * blockDim.x + threadIdx.x;  // 16-element column index inside the row
+  const bool col_on = col * 16 < K;                        // K is a multiple of 32: pairs are on or off together
   const int nkb_pad = int(pad_to(K / V, 4));
-  const bool leader = (threadIdx.x & (LPB - 1)) == 0;
-  const int sf_col = sf_col_offset((vec * 8) / V);
+  const bool leader = MODE == 2 || (threadIdx.x & 1) == 0;
+  const int sf_col = sf_col_offset(col * 16 / V);
   const Fp4Scale fs = MODE == 2 ? fp4_scale(amax) : Fp4Scale{1.f, 1.f};
   const int64_t nchunks = (rows + rows_per_chunk - 1) / rows_per_chunk;
   for (int64_t c = blockIdx.x; c < nchunks; c += gridDim.x) {
     const int64_t r0 = c * rows_per_chunk;
     const int64_t r1 = r0 + rows_per_chunk < rows ? r0 + rows_per_chunk : rows;
     for (int64_t rb = r0; rb < r1; rb += U) {
-      uint4 raw[U];
+      uint4 raw[U][2];
 #pragma unroll
       for (int u = 0; u < U; u++) {
-        raw[u] = make_uint4(0u, 0u, 0u, 0u);
-        if (col_on && rb + u < r1) raw[u] = ld_stream(reinterpret_cast<const uint4*>(x + (rb + u) * ldx) + vec);
+        raw[u][0] = raw[u][1] = make_uint4(0u, 0u, 0u, 0u);
+        if (col_on && rb + u < r1) {
+          const uint4* src = reinterpret_cast<const uint4*>(x + (rb + u) * ldx) + 2 * col;
+          raw[u][0] = ld_stream(src), raw[u][1] = ld_stream(src + 1);
+        }
       }
 #pragma unroll
       for (int u = 0; u < U; u++) {
         const int64_t r = rb + u;
-        float v[8];
-        unpack8(raw[u], v);
-        const float bmax = block_max<LPB>(v);
-        uint32_t lo, hi;
-        const uint8_t sbyte = quant8<MODE>(v, bmax, fs, lo, hi);
+        uint4 out;
+        const uint8_t sbyte = quant16<MODE>(raw[u], block_absmax<MODE>(raw[u]), fs, out);
         if (col_on && r < r1) {
-          if (MODE == 2) st_stream32(reinterpret_cast<unsigned int*>(q + (r * K + int64_t(vec) * 8) / 2), lo);
-          else st_stream(reinterpret_cast<uint2*>(q + r * K + int64_t(vec) * 8), make_uint2(lo, hi));
-          if (leader) sf[sf_row_offset(r, nkb_pad) + sf_col] = sbyte;
+          if (MODE == 2) st_stream(reinterpret_cast<uint2*>(q + (r * K) / 2) + col, make_uint2(out.x, out.y));
+          else st_stream(reinterpret_cast<uint4*>(q + r * K) + col, out);
+          if (leader) sf[sf_row_offset(uint64_t(r), nkb_pad) + sf_col] = sbyte;
         }
       }
     }
@@ -325,29 +336,46 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
   if (!aligned(q, 8)) return fail(MXK_ERR_INVALID_ARG, "quantize_blockscaled: q must be 8-byte aligned");
   cudaStream_t s = as_stream(stream);
   const bf16* xb = reinterpret_cast<const bf16*>(x);
-  // padded scale rows / columns are read by the GEMM (0xff is NaN in ue8m0): clear everything first
-  cudaError_t e = cudaMemsetAsync(sf, 0, size_t(mxk_qscale_bytes(mode, rows, K)), s);
+  // Padded scale rows / columns are read by the GEMM (0xff is NaN in ue8m0) and the reference clears
+  // the whole buffer first (src/kernels/blockscale.cu:154).  Every byte of a real (row, block) is
+  // written below, so clearing what is padding gives the same bytes: nothing when rows fill their
+  // 128-row tiles and blocks their groups of 4, the last row tile when only rows are ragged, and
+  // everything when the column padding is interleaved through all tiles.
+  const int64_t nkb = K / (mode == MXK_Q_NVFP4 ? 16 : 32);
+  cudaError_t e = cudaSuccess;
+  if (nkb % 4 != 0) {
+    e = cudaMemsetAsync(sf, 0, size_t(mxk_qscale_bytes(mode, rows, K)), s);
+  } else if (rows % 128 != 0) {
+    const int64_t tile = nkb * 128;
+    e = cudaMemsetAsync(sf + rows / 128 * tile, 0, size_t(tile), s);
+  }
   if (e == cudaSuccess && mode == MXK_Q_NVFP4) e = cudaMemsetAsync(amax, 0, sizeof(float), s);
   if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "quantize_blockscaled: cudaMemsetAsync: %s", cudaGetErrorString(e));
   const int nvec = int(K / 8);
   const int V = mode == MXK_Q_NVFP4 ? 16 : 32;
-  // bulk-copy pipeline: rows cut into equal pieces of whole scale blocks, at most one chunk each
-  int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 8) * 1024;
+  // Bulk-copy pipeline: rows cut into equal pieces of whole scale blocks, at most one chunk each.
+  // Measured on B200 (8704 x 12288 and 8704 x 3072 bf16): MXFP8 runs best with 8 consumer warps on
+  // 8 KB chunks, 3 stages; NVFP4, with more arithmetic per element, with 4 warps on 32 KB chunks, 2
+  // stages.  An MXFP8 input that fits in L2 with its output goes to the register kernel, whose fixed
+  // cost is a few microseconds lower.
+  const bool fp4 = mode == MXK_Q_NVFP4;
+  int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, fp4 ? 32 : 8) * 1024;
   if (chunk_bytes > 32 * 1024) chunk_bytes = 32 * 1024;
   const int pieces = int(ceil_div(K * 2, chunk_bytes));
   const int piece_elems = int(ceil_div(ceil_div(K, pieces), 128) * 128);
-  if (tune(TUNE_QUANT_PATH, 1) == 1 && piece_elems * 2 <= chunk_bytes) {
+  const bool small = !fp4 && rows * K * 2 < (int64_t(96) << 20);
+  if (tune(TUNE_QUANT_PATH, small ? 2 : 1) == 1 && piece_elems * 2 <= chunk_bytes && rows * pieces < (int64_t(1) << 31)) {
     const int ppr = int(ceil_div(K, piece_elems));
     RowPieces rp{reinterpret_cast<const unsigned char*>(x), ldx * 2, int(K), ppr, piece_elems};
-    if (mode == MXK_Q_NVFP4) {
+    if (fp4) {
       AmaxPipeOp op;
       static_cast<RowPieces&>(op) = rp;
       op.out = amax;
-      if (int rc = run_stream_pipe("quantize_blockscaled (amax)", op, rows * ppr, piece_elems * 2, s, 4, 3)) return rc;
+      if (int rc = run_stream_pipe("quantize_blockscaled (amax)", op, rows * ppr, piece_elems * 2, s, 4, 2)) return rc;
       QuantPipeOp<2> qo;
       static_cast<RowPieces&>(qo) = rp;
       qo.q = static_cast<uint8_t*>(q), qo.sf = sf, qo.amax = amax, qo.nkb_pad = int(pad_to(K / V, 4));
-      return run_stream_pipe("quantize_blockscaled", qo, rows * ppr, piece_elems * 2, s, 8, 3);
+      return run_stream_pipe("quantize_blockscaled", qo, rows * ppr, piece_elems * 2, s, 4, 2);
     }
     QuantPipeOp<1> qo;
     static_cast<RowPieces&>(qo) = rp;
@@ -360,8 +388,9 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
     launch_pdl(amax_kernel, dim3(unsigned(grid)), dim3(256), 0, s, xb, ldx, rows, nvec, amax);
     if (int rc = after_launch("quantize_blockscaled")) return rc;
   }
-  const int threads = nvec >= 256 ? 256 : int(ceil_div(nvec, 32) * 32);
-  const unsigned gy = unsigned(ceil_div(nvec, threads));
+  const int ncol = int(K / 16);
+  const int threads = ncol >= 256 ? 256 : int(ceil_div(ncol, 32) * 32);
+  const unsigned gy = unsigned(ceil_div(ncol, threads));
   const int rpc = tune(TUNE_QUANT_ROWS_PER_CTA, 8);
   const int64_t nchunks = ceil_div(rows, rpc);
   auto go = [&](auto kern) {
