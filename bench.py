@@ -394,8 +394,43 @@ def main():
                 q_ops.append({"op": f"quantize_{mname}", "input": f"{src_name} [{rows}, {cols}]", "us": round(us, 2),
                               "bytes": int(by), "gbs": round(by / us / 1e3, 1), "frac": round(by / us / 1e3 / peak_gbs, 3)})
                 del outs
-        return {"quantize_blockscaled": q_ops,
-                "note": "bytes = bf16 read + codes + scales; nvfp4 reads the input twice (tensor amax first)"}
+        res = {"quantize_blockscaled": q_ops,
+               "note": "bytes = bf16 read + codes + scales; nvfp4 reads the input twice (tensor amax first)"}
+        if args.impl == "mxk":
+            # the MLP activation and its quantisation in one pass, against the same two calls in a row
+            am = mx.ops.ACT_GELU_TANH if w.act_mode == 0 else mx.ops.ACT_SILU_MUL
+            srcs = [b.act if w.act_mode == 0 else b.act2 for b in sets]
+            outs = [mx.ops.act_quantize_mxfp8(am, t, rows, w.F, stream=stream) for t in srcs]
+            tmp = [b.act for b in sets]
+
+            def fused(i):
+                mx.ops.act_quantize_mxfp8(am, srcs[i % n_sets], rows, w.F, outs[i % n_sets], stream)
+
+            def separate(i):
+                if w.act_mode == 0:
+                    mx.ops.gelu_tanh_inplace(tmp[i % n_sets], rows * w.F, stream)
+                else:
+                    mx.ops.silu_mul(srcs[i % n_sets], rows, w.F, tmp[i % n_sets], stream)
+                mx.ops.quantize_blockscaled(mx.ops.Q_MXFP8, tmp[i % n_sets], w.F, rows, w.F, outs[i % n_sets], stream)
+
+            pair = {}
+            for name, fn in (("one_call", fused), ("two_calls", separate)):
+                for i in range(3):
+                    fn(i)
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for i in range(K):
+                    fn(i)
+                e1.record(stream)
+                barrier()
+                pair[name] = round(e0.elapsed_time(e1) / K * 1e3, 2)
+            by = ((2 if w.act_mode == 0 else 4) + 1 + 1 / 32) * rows * w.F
+            res["act_quantize_mxfp8"] = {"act": "gelu_tanh" if w.act_mode == 0 else "silu_mul", "input": f"[{rows}, {w.F}]",
+                                         "us": pair["one_call"], "us_two_calls": pair["two_calls"], "bytes": int(by),
+                                         "gbs": round(by / pair["one_call"] / 1e3, 1),
+                                         "frac": round(by / pair["one_call"] / 1e3 / peak_gbs, 3)}
+        return res
 
     K, Wm = max(args.steps, 1), max(args.warmup, 3)
     peaks = {}

@@ -328,13 +328,26 @@ int mxk_selftest_bounded_wait(mxk_stream_t stream);
  *                GEMM needs is amax / 2688.
  * sf has mxk_qscale_bytes() bytes in cuBLASLt's VEC32_UE8M0 / VEC16_UE4M3 layout (rows padded to 128,
  * scale columns to 4, 128 x 4 tiles interleaved) and is cleared first, padding included.
- * Requirements as the reference's: K % 32 == 0, ldx % 8 == 0, x 16-byte aligned; q 8-byte aligned.
+ * Requirements as the reference's: K % 32 == 0, ldx % 8 == 0, x 16-byte aligned; q 16-byte aligned.
  * Outputs are byte-identical to the reference kernel's. */
 enum { MXK_Q_MXFP8 = 1, MXK_Q_NVFP4 = 2 };
 int64_t mxk_qdata_bytes(int mode, int64_t rows, int64_t K);
 int64_t mxk_qscale_bytes(int mode, int64_t rows, int64_t K);
 int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t rows, int64_t K, void* q, uint8_t* sf,
                              float* amax, mxk_stream_t stream);
+
+/* Activation and MXFP8 quantisation in one pass over the data, for an activation whose only reader is the
+ * next block-scaled GEMM (the MLP's hidden activation).  One call in place of two of the reference's:
+ * gelu_tanh_inplace / gelu_erf_inplace / silu_mul (src/kernels/ops.h:36-41) followed by
+ * quantize_blockscaled(MXFP8) (src/kernels/blockscale.h:30); the bf16 activation is never written, which
+ * takes the traffic from 7 bytes per element to 3.  Results are byte-identical to mxk_gelu_tanh_inplace /
+ * mxk_gelu_erf_inplace / mxk_silu_mul followed by mxk_quantize_blockscaled.
+ *   act_mode 0: gelu (tanh form) of in [rows, F];  1: silu(in[:, :F]) * in[:, F:] with in [rows, 2F];
+ *            2: gelu (erf form) of in [rows, F].
+ * F % 32 == 0, in and q 16-byte aligned.  NVFP4 has no such form: its first block cannot be scaled before
+ * the maximum of the whole activation is known. */
+int mxk_act_quantize_mxfp8(int act_mode, const mxk_bf16* in, int64_t rows, int64_t F, void* q, uint8_t* sf,
+                           mxk_stream_t stream);
 
 /* Development knob: overrides a launch-shape default (see tuning.h for the names); value 0
  * restores the default.  Results do not depend on it. */

@@ -1,34 +1,11 @@
 // silu_mul, gelu_tanh_inplace, gelu_erf_inplace, silu_inplace_f32
 // (reference: src/kernels/ops.cu:121-128, 212-233, 244-246).
+#include "act_math.cuh"
 #include "flat_map.cuh"
 #include "stream_pipe.cuh"
 
 namespace mxk {
 namespace {
-
-// 0.5 v (1 + tanh(u)), u = 0.7978845608 (v + 0.044715 v^3)  (src/kernels/ops.cu:222-224).
-// 0.5 (1 + tanh(u)) is the logistic function of 2u, so the value is v / (1 + exp(-2u)) =
-// v / (1 + 2^z) with z = -2 log2(e) u = v (B0 + B1 v^2): three multiply-adds, one ex2, one add,
-// one reciprocal, one multiply.  There is no cancellation anywhere (the negative tail divides
-// by a large number instead of adding 1 to a tanh near -1), and when 2^z overflows for very
-// negative v the reciprocal is 0 and the result the correct limit -0.  Seven issue slots per
-// element plus unpack and pack; at HBM speed the SM has to retire more than one element per
-// clock per scheduler, so every slot counts.
-__device__ __forceinline__ float gelu_tanh_f(float v) {
-  constexpr float B0 = -2.f * 1.4426950408889634f * 0.7978845608f;
-  constexpr float B1 = B0 * 0.044715f;
-  const float z = v * fmaf(v * v, B1, B0);
-  return v * rcp_approx(1.f + ex2_approx(z));
-}
-
-__device__ __forceinline__ float gelu_erf_f(float v) {
-  return 0.5f * v * (1.f + erff(v * 0.7071067811865476f));
-}
-
-// g / (1 + exp(-g))  (src/kernels/ops.cu:127): exp through ex2, the division as a reciprocal.
-__device__ __forceinline__ float silu_f(float g) {
-  return g * rcp_approx(1.f + ex2_approx(g * -1.4426950408889634f));
-}
 
 template <int KIND>  // 0 gelu tanh, 1 gelu erf
 struct GeluOp {
@@ -73,13 +50,7 @@ struct GeluPipeOp {
     c.src0 = x + off, c.src1 = nullptr, c.dst = x + off;
     c.bytes = unsigned(nbytes - off < chunk_bytes ? nbytes - off : chunk_bytes);
   }
-  __device__ uint4 apply(const uint4& a, const uint4&) const {
-    float v[8];
-    unpack8(a, v);
-#pragma unroll
-    for (int i = 0; i < 8; i++) v[i] = GeluOp<KIND>::f(v[i]);
-    return pack8(v);
-  }
+  __device__ uint4 apply(const uint4& a, const uint4&) const { return act8<KIND>(a, a); }
 };
 
 // silu(gate) * up for the streaming pipeline: a row of gu is cut into chunks_per_row column chunks.
@@ -98,14 +69,7 @@ struct SiluPipeOp {
     c.dst = out + (row * F + col) * 2;
     c.bytes = unsigned(n * 2);
   }
-  __device__ uint4 apply(const uint4& g, const uint4& u) const {
-    float a[8], b[8];
-    unpack8(g, a);
-    unpack8(u, b);
-#pragma unroll
-    for (int i = 0; i < 8; i++) a[i] = silu_f(a[i]) * b[i];
-    return pack8(a);
-  }
+  __device__ uint4 apply(const uint4& g, const uint4& u) const { return act8<ACT_SILU_MUL>(g, u); }
 };
 
 template <int KIND>

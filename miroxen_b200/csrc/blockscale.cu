@@ -32,6 +32,7 @@
 //    the one input where the ladder (no sign for -0) and the instruction (sign kept) differ.
 #include <cuda_fp8.h>
 
+#include "act_math.cuh"
 #include "common.cuh"
 #include "stream_pipe.cuh"
 #include "tuning.h"
@@ -164,6 +165,8 @@ struct RowPieces {
   const unsigned char* x;
   int64_t ldx_bytes;
   int K, pieces_per_row, piece_elems;
+  int64_t src1_off = 0;  // bytes from a piece to its second source (silu_mul's `up` half), 0 = none
+  int stage_off = 0;     // where the second source sits inside a stage
   // chunk < 2^31 (checked by the launcher): 32-bit arithmetic, and no division in the common case of
   // one piece per row - this runs once per chunk in every consumer thread
   __device__ __forceinline__ void where(int64_t chunk, unsigned& row, int& k0, int& n) const {
@@ -180,7 +183,7 @@ struct RowPieces {
     unsigned row;
     int k0, n;
     where(chunk, row, k0, n);
-    c.src0 = x + row * ldx_bytes + int64_t(k0) * 2, c.src1 = nullptr, c.dst = nullptr;
+    c.src0 = x + row * ldx_bytes + int64_t(k0) * 2, c.src1 = c.src0 + src1_off, c.dst = nullptr;
     c.bytes = unsigned(n) * 2;
   }
 };
@@ -205,9 +208,11 @@ struct AmaxPipeOp : RowPieces {
   __device__ void finish(State& st, int) const { amax_commit(bf16x2_max_to_float(st.m), out); }
 };
 
-template <int MODE>
+// ACT < 0: quantise the source as it is; otherwise apply the activation (act_math.cuh) to the source
+// first, round to bf16 as the stand-alone activation kernel does, and quantise that.
+template <int MODE, int ACT = -1>
 struct QuantPipeOp : RowPieces {
-  static constexpr int NSRC = 1;
+  static constexpr int NSRC = ACT == ACT_SILU_MUL ? 2 : 1;
   static constexpr int V = MODE == 2 ? 16 : 32, LPB = V / 8;
   uint8_t* q;
   uint8_t* sf;
@@ -226,7 +231,12 @@ struct QuantPipeOp : RowPieces {
     // every lane of a warp runs the same trips (the block maximum is a warp shuffle)
     for (int i0 = tid - lane; i0 < n16; i0 += n_cons) {
       const int i = i0 + lane, ic = i < n16 ? i : n16 - 1;  // lanes past the end compute on a copy, store nothing
-      const uint4 raw[2] = {s[2 * ic], s[2 * ic + 1]};
+      uint4 raw[2] = {s[2 * ic], s[2 * ic + 1]};
+      if (ACT >= 0) {
+        const uint4* s2 = reinterpret_cast<const uint4*>(stage + stage_off);
+        raw[0] = act8<ACT>(raw[0], NSRC == 2 ? s2[2 * ic] : raw[0]);
+        raw[1] = act8<ACT>(raw[1], NSRC == 2 ? s2[2 * ic + 1] : raw[1]);
+      }
       uint4 out;
       const uint8_t sbyte = quant16<MODE>(raw, block_absmax<MODE>(raw), fs, out);
       if (i < n16) {
@@ -313,7 +323,43 @@ __global__ void __launch_bounds__(256) quant_kernel(const bf16* __restrict__ x, 
 }  // namespace
 }  // namespace mxk
 
+// Padded scale rows / columns are read by the GEMM (0xff is NaN in ue8m0) and the reference clears
+// the whole buffer first (src/kernels/blockscale.cu:154).  Every byte of a real (row, block) is
+// written by the kernels, so clearing what is padding gives the same bytes: nothing when rows fill
+// their 128-row tiles and blocks their groups of 4, the last row tile when only rows are ragged, and
+// everything when the column padding is interleaved through all tiles.
+static int clear_scale_padding(int mode, int64_t rows, int64_t K, uint8_t* sf, cudaStream_t s) {
+  const int64_t nkb = K / (mode == MXK_Q_NVFP4 ? 16 : 32);
+  cudaError_t e = cudaSuccess;
+  if (nkb % 4 != 0) {
+    e = cudaMemsetAsync(sf, 0, size_t(mxk::pad_to(rows, 128) * mxk::pad_to(nkb, 4)), s);
+  } else if (rows % 128 != 0) {
+    const int64_t tile = nkb * 128;
+    e = cudaMemsetAsync(sf + rows / 128 * tile, 0, size_t(tile), s);
+  }
+  if (e != cudaSuccess) return mxk::fail(MXK_ERR_CUDA, "cudaMemsetAsync (scale padding): %s", cudaGetErrorString(e));
+  return MXK_OK;
+}
+
 using namespace mxk;
+
+template <int ACT>
+static int run_act_quant(const mxk_bf16* in, int64_t rows, int64_t F, void* q, uint8_t* sf, cudaStream_t s) {
+  const bool two = ACT == ACT_SILU_MUL;
+  // two sources share a stage: half the chunk each
+  int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 16) * 1024 / (two ? 2 : 1);
+  if (chunk_bytes > 32 * 1024) chunk_bytes = 32 * 1024;
+  const int pieces = int(ceil_div(F * 2, chunk_bytes));
+  const int piece_elems = int(ceil_div(ceil_div(F, pieces), 128) * 128);
+  if (piece_elems * 2 > chunk_bytes || rows * pieces >= (int64_t(1) << 31))
+    return fail(MXK_ERR_TOO_LARGE, "act_quantize_mxfp8: %lld rows of %lld do not fit the pipeline's chunking", (long long)rows, (long long)F);
+  QuantPipeOp<1, ACT> qo;
+  qo.x = reinterpret_cast<const unsigned char*>(in), qo.ldx_bytes = F * (two ? 4 : 2), qo.K = int(F);
+  qo.pieces_per_row = int(ceil_div(F, piece_elems)), qo.piece_elems = piece_elems;
+  qo.src1_off = two ? F * 2 : 0, qo.stage_off = (piece_elems * 2 + 127) & ~127;
+  qo.q = static_cast<uint8_t*>(q), qo.sf = sf, qo.amax = nullptr, qo.nkb_pad = int(pad_to(F / 32, 4));
+  return run_stream_pipe("act_quantize_mxfp8", qo, rows * qo.pieces_per_row, piece_elems * 2, s, two ? 8 : 12, 3);
+}
 
 extern "C" {
 
@@ -333,33 +379,22 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
   if (rows == 0) return MXK_OK;
   if (rows < 0 || !x || !q || !sf || (mode == MXK_Q_NVFP4 && !amax))
     return fail(MXK_ERR_INVALID_ARG, "quantize_blockscaled: null buffer or negative rows");
-  if (!aligned(q, 8)) return fail(MXK_ERR_INVALID_ARG, "quantize_blockscaled: q must be 8-byte aligned");
+  if (!aligned(q, 16)) return fail(MXK_ERR_INVALID_ARG, "quantize_blockscaled: q must be 16-byte aligned");
   cudaStream_t s = as_stream(stream);
   const bf16* xb = reinterpret_cast<const bf16*>(x);
-  // Padded scale rows / columns are read by the GEMM (0xff is NaN in ue8m0) and the reference clears
-  // the whole buffer first (src/kernels/blockscale.cu:154).  Every byte of a real (row, block) is
-  // written below, so clearing what is padding gives the same bytes: nothing when rows fill their
-  // 128-row tiles and blocks their groups of 4, the last row tile when only rows are ragged, and
-  // everything when the column padding is interleaved through all tiles.
-  const int64_t nkb = K / (mode == MXK_Q_NVFP4 ? 16 : 32);
+  if (int rc = clear_scale_padding(mode, rows, K, sf, s)) return rc;
   cudaError_t e = cudaSuccess;
-  if (nkb % 4 != 0) {
-    e = cudaMemsetAsync(sf, 0, size_t(mxk_qscale_bytes(mode, rows, K)), s);
-  } else if (rows % 128 != 0) {
-    const int64_t tile = nkb * 128;
-    e = cudaMemsetAsync(sf + rows / 128 * tile, 0, size_t(tile), s);
-  }
-  if (e == cudaSuccess && mode == MXK_Q_NVFP4) e = cudaMemsetAsync(amax, 0, sizeof(float), s);
+  if (mode == MXK_Q_NVFP4) e = cudaMemsetAsync(amax, 0, sizeof(float), s);
   if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "quantize_blockscaled: cudaMemsetAsync: %s", cudaGetErrorString(e));
   const int nvec = int(K / 8);
   const int V = mode == MXK_Q_NVFP4 ? 16 : 32;
   // Bulk-copy pipeline: rows cut into equal pieces of whole scale blocks, at most one chunk each.
-  // Measured on B200 (8704 x 12288 and 8704 x 3072 bf16): MXFP8 runs best with 8 consumer warps on
-  // 8 KB chunks, 3 stages; NVFP4, with more arithmetic per element, with 4 warps on 32 KB chunks, 2
-  // stages.  An MXFP8 input that fits in L2 with its output goes to the register kernel, whose fixed
+  // Measured on B200 (8704 x 12288, 8704 x 3072, 33272 x 5120, 33272 x 13824 bf16): MXFP8 runs best
+  // with 12 consumer warps on 16 KB chunks, 3 stages; NVFP4, with more arithmetic per element, with 4
+  // warps on 32 KB chunks, 2 stages.  An MXFP8 input that fits in L2 with its output goes to the register kernel, whose fixed
   // cost is a few microseconds lower.
   const bool fp4 = mode == MXK_Q_NVFP4;
-  int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, fp4 ? 32 : 8) * 1024;
+  int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, fp4 ? 32 : 16) * 1024;
   if (chunk_bytes > 32 * 1024) chunk_bytes = 32 * 1024;
   const int pieces = int(ceil_div(K * 2, chunk_bytes));
   const int piece_elems = int(ceil_div(ceil_div(K, pieces), 128) * 128);
@@ -380,7 +415,7 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
     QuantPipeOp<1> qo;
     static_cast<RowPieces&>(qo) = rp;
     qo.q = static_cast<uint8_t*>(q), qo.sf = sf, qo.amax = nullptr, qo.nkb_pad = int(pad_to(K / V, 4));
-    return run_stream_pipe("quantize_blockscaled", qo, rows * ppr, piece_elems * 2, s, 8, 3);
+    return run_stream_pipe("quantize_blockscaled", qo, rows * ppr, piece_elems * 2, s, 12, 3);
   }
   if (mode == MXK_Q_NVFP4) {
     int64_t grid = int64_t(sm_count()) * resident_ctas(amax_kernel, 256);
@@ -403,6 +438,21 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
   if (mode == MXK_Q_NVFP4) go(quant_kernel<2>);
   else go(quant_kernel<1>);
   return after_launch("quantize_blockscaled");
+}
+
+int mxk_act_quantize_mxfp8(int act_mode, const mxk_bf16* in, int64_t rows, int64_t F, void* q, uint8_t* sf,
+                           mxk_stream_t stream) {
+  if (act_mode < 0 || act_mode > 2) return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: act_mode %d (0 gelu tanh, 1 silu_mul, 2 gelu erf)", act_mode);
+  if (F <= 0 || F % 32 != 0 || F > (int64_t(1) << 30) || !aligned(in, 16))
+    return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: need F %% 32 == 0 and a 16-byte aligned input");
+  if (rows == 0) return MXK_OK;
+  if (rows < 0 || !in || !q || !sf) return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: null buffer or negative rows");
+  if (!aligned(q, 16)) return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: q must be 16-byte aligned");
+  cudaStream_t s = as_stream(stream);
+  if (int rc = clear_scale_padding(MXK_Q_MXFP8, rows, F, sf, s)) return rc;
+  if (act_mode == 1) return run_act_quant<ACT_SILU_MUL>(in, rows, F, q, sf, s);
+  if (act_mode == 2) return run_act_quant<ACT_GELU_ERF>(in, rows, F, q, sf, s);
+  return run_act_quant<ACT_GELU_TANH>(in, rows, F, q, sf, s);
 }
 
 }  // extern "C"

@@ -16,6 +16,7 @@ from . import _lib
 from ._lib import BlockArgs, HeadTensor, RopeRun, RowMod, check, lib
 
 ROPE_NONE, ROPE_INTERLEAVED, ROPE_HALF = 0, 1, 2
+ACT_GELU_TANH, ACT_SILU_MUL, ACT_GELU_ERF = 0, 1, 2
 Q_MXFP8, Q_NVFP4 = 1, 2  # QMode of src/kernels/blockscale.h:14 (0 = None is not a quantised mode)
 
 __all__ = [
@@ -24,7 +25,8 @@ __all__ = [
     "scatter_rows", "silu_inplace_f32", "add_bias_bf16", "add_bias_f32", "f32_to_bf16", "bf16_to_f32", "axpy_f32",
     "axpby_f32", "gated_residual_norm", "qkv_norm_rope", "HeadSpec", "dit_block_ops", "BlockArgs", "RowMod",
     "HostPipeline", "OpTimes", "dit_block_ops_host_static", "device_error", "launch_count", "reset_launch_count", "set_tuning",
-    "Q_MXFP8", "Q_NVFP4", "QMat", "qdata_bytes", "qscale_bytes", "quantize_blockscaled",
+    "Q_MXFP8", "Q_NVFP4", "QMat", "qdata_bytes", "qscale_bytes", "quantize_blockscaled", "act_quantize_mxfp8",
+    "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF",
 ]
 
 
@@ -237,6 +239,16 @@ def quantize_blockscaled(mode: int, x, ldx: int, rows: int, K: int, out: Optiona
                    torch.empty(qscale_bytes(mode, rows, K), dtype=torch.uint8, device=dev),
                    torch.empty(1, dtype=torch.float32, device=dev) if mode == Q_NVFP4 else None)
     check(lib().mxk_quantize_blockscaled(mode, _p(x), ldx, rows, K, _p(out.q), _p(out.sf), _p(out.amax), _stream(stream)))
+    return out
+
+
+def act_quantize_mxfp8(act_mode: int, in_, rows: int, F: int, out: Optional[QMat] = None, stream=None) -> QMat:
+    """The MLP activation (gelu_tanh_inplace / silu_mul / gelu_erf_inplace of src/kernels/ops.h:36-41) and its
+    MXFP8 quantisation in one pass; same bytes as the two calls, without writing the bf16 activation."""
+    if out is None:
+        out = QMat(torch.empty(qdata_bytes(Q_MXFP8, rows, F), dtype=torch.uint8, device=in_.device),
+                   torch.empty(qscale_bytes(Q_MXFP8, rows, F), dtype=torch.uint8, device=in_.device))
+    check(lib().mxk_act_quantize_mxfp8(act_mode, _p(in_), rows, F, _p(out.q), _p(out.sf), _stream(stream)))
     return out
 
 

@@ -154,3 +154,82 @@ def test_side_by_side_with_reference_kernel(mx, mode, rows, K, ldx):
     bits = orc.f32_to_bf16_bits(a)
     rq, rsf, ramax = run_reference(orc.ref_blockscale(), mode, bits, K)
     assert_same("reference kernel", mxk_quant(mx, mode, bits, K), (rq, rsf, float(ramax[0]) if mode == 2 else 0.0))
+
+
+# ---- activation + MXFP8 quantisation in one pass ----
+
+def two_calls(mx, act_mode, x_bits, rows, F):
+    """The activation kernel of this library followed by its quantiser."""
+    x = H.to_dev(torch, x_bits)
+    if act_mode == mx.ops.ACT_SILU_MUL:
+        act = torch.empty(rows, F, dtype=torch.bfloat16, device="cuda")
+        mx.ops.silu_mul(x, rows, F, act)
+    else:
+        act = x.clone()
+        (mx.ops.gelu_tanh_inplace if act_mode == mx.ops.ACT_GELU_TANH else mx.ops.gelu_erf_inplace)(act, rows * F)
+    out = mx.ops.quantize_blockscaled(mx.ops.Q_MXFP8, act, F, rows, F)
+    torch.cuda.synchronize()
+    return out.q.cpu().numpy(), out.sf.cpu().numpy(), H.bits(act)
+
+
+def one_call(mx, act_mode, x_bits, rows, F):
+    x = H.to_dev(torch, x_bits)
+    q = H.Guarded(torch, (mx.ops.qdata_bytes(1, rows, F),), torch.uint8)
+    sf = H.Guarded(torch, (mx.ops.qscale_bytes(1, rows, F),), torch.uint8)
+    sf.t.fill_(0x5A)
+    before = x.clone()
+    mx.ops.act_quantize_mxfp8(act_mode, x, rows, F, mx.ops.QMat(q.t, sf.t))
+    torch.cuda.synchronize()
+    q.check("q")
+    sf.check("sf")
+    assert torch.equal(x.view(torch.uint16), before.view(torch.uint16)), "the input must not be written"
+    return q.t.cpu().numpy(), sf.t.cpu().numpy()
+
+
+@pytest.mark.parametrize("act_mode", [0, 1, 2])
+@pytest.mark.parametrize("rows,F", [(1, 32), (5, 96), (129, 160), (64, 4096), (37, 4128), (300, 12288), (2049, 3072)])
+def test_act_quantize_equals_two_calls_and_oracle_bound(mx, act_mode, rows, F):
+    g = H.rng(rows + F + act_mode)
+    cols = 2 * F if act_mode == 1 else F
+    bits = H.normal_bf16(g, (rows, cols), 2.0)
+    q2, sf2, act_bits = two_calls(mx, act_mode, bits, rows, F)
+    q1, sf1 = one_call(mx, act_mode, bits, rows, F)
+    assert np.array_equal(sf1, sf2), f"{(sf1 != sf2).sum()} scale bytes differ"
+    assert np.array_equal(q1, q2), f"{(q1 != q2).sum()} of {q1.size} data bytes differ"
+    # and the decoded values are the oracle's activation within the format's error bound
+    if act_mode == 1:
+        ref = orc.silu_mul(bits, F)
+    else:
+        ref = (orc.gelu_tanh_inplace if act_mode == 0 else orc.gelu_erf_inplace)(bits.copy())
+    d = orc.dequantize_blockscaled(1, q1, sf1, 0.0, rows, F)
+    assert rel_rms(d, bits_to_f32(ref).reshape(rows, F)) < ELEM_ERR[1]
+
+
+@pytest.mark.parametrize("knob,value", [("stream_chunk_kb", 1), ("stream_chunk_kb", 2), ("stream_stages", 2),
+                                        ("stream_warps", 3), ("stream_ctas_per_sm", 1)])
+@pytest.mark.parametrize("act_mode", [0, 1])
+def test_act_quantize_work_split(mx, act_mode, knob, value):
+    g = H.rng(17 + value)
+    rows, F = 1500, 1056
+    bits = H.normal_bf16(g, (rows, 2 * F if act_mode == 1 else F), 1.5)
+    q2, sf2, _ = two_calls(mx, act_mode, bits, rows, F)
+    mx.ops.set_tuning(knob, value)
+    try:
+        q1, sf1 = one_call(mx, act_mode, bits, rows, F)
+    finally:
+        mx.ops.set_tuning(knob, 0)
+    assert np.array_equal(sf1, sf2) and np.array_equal(q1, q2)
+
+
+def test_act_quantize_argument_errors(mx):
+    x = torch.zeros(4, 64, dtype=torch.bfloat16, device="cuda")
+    out = mx.ops.act_quantize_mxfp8(0, x, 4, 64)
+    for kw in (dict(act_mode=3), dict(F=48), dict(act_mode=-1)):
+        a = dict(act_mode=0, F=64)
+        a.update(kw)
+        with pytest.raises(mx.MxkError):
+            mx.ops.act_quantize_mxfp8(a["act_mode"], x, 4, a["F"], out)
+    with pytest.raises(mx.MxkError):
+        mx.ops.act_quantize_mxfp8(0, x.view(-1)[1:].data_ptr(), 3, 64, out)
+    mx.ops.act_quantize_mxfp8(0, x, 0, 64, out)
+    torch.cuda.synchronize()
