@@ -430,6 +430,46 @@ def main():
                                          "us": pair["one_call"], "us_two_calls": pair["two_calls"], "bytes": int(by),
                                          "gbs": round(by / pair["one_call"] / 1e3, 1),
                                          "frac": round(by / pair["one_call"] / 1e3 / peak_gbs, 3)}
+            # the block's first norm and its quantisation in one pass, against the two calls
+            bsets = sets
+            nouts = [mx.ops.QMat(torch.empty(rows * w.dim, dtype=torch.uint8, device="cuda"),
+                                 torch.empty(mx.ops.qscale_bytes(1, rows, w.dim), dtype=torch.uint8, device="cuda")) for _ in bsets]
+
+            def mod(b, name):
+                return mx.row_mod(b.mods[name + "_t"], b.mods[name + "_p"], min(max(prefix_rows, 0), rows))
+
+            def norm_one(i):
+                b = bsets[i % n_sets]
+                if w.norm_mode == 0:
+                    mx.ops.layernorm_mod_quant_mxfp8(b.x, rows, w.dim, 1e-6, mod(b, "scale1"), mod(b, "shift1"), nouts[i % n_sets], stream)
+                else:
+                    mx.ops.rmsnorm_mod_quant_mxfp8(b.x, rows, w.dim, 1e-6, b.mods["norm1_w"], mod(b, "scale1"), mod(b, "shift1"), nouts[i % n_sets], stream)
+
+            def norm_two(i):
+                b = bsets[i % n_sets]
+                if w.norm_mode == 0:
+                    mx.ops.layernorm_mod(b.x, rows, w.dim, 1e-6, mod(b, "scale1"), mod(b, "shift1"), b.h1, stream)
+                else:
+                    mx.ops.rmsnorm_mod(b.x, rows, w.dim, 1e-6, b.mods["norm1_w"], mod(b, "scale1"), mod(b, "shift1"), b.h1, stream)
+                mx.ops.quantize_blockscaled(mx.ops.Q_MXFP8, b.h1, w.dim, rows, w.dim, nouts[i % n_sets], stream)
+
+            pair = {}
+            for name, fn in (("one_call", norm_one), ("two_calls", norm_two)):
+                for i in range(3):
+                    fn(i)
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for i in range(K):
+                    fn(i)
+                e1.record(stream)
+                barrier()
+                pair[name] = round(e0.elapsed_time(e1) / K * 1e3, 2)
+            by = (4 + 1 + 1 / 32) * rows * w.dim
+            res["norm_mod_quant_mxfp8"] = {"norm": "layernorm" if w.norm_mode == 0 else "rmsnorm", "input": f"[{rows}, {w.dim}]",
+                                           "us": pair["one_call"], "us_two_calls": pair["two_calls"], "bytes": int(by),
+                                           "gbs": round(by / pair["one_call"] / 1e3, 1),
+                                           "frac": round(by / pair["one_call"] / 1e3 / peak_gbs, 3)}
         return res
 
     K, Wm = max(args.steps, 1), max(args.warmup, 3)

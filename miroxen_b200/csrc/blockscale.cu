@@ -33,6 +33,7 @@
 #include <cuda_fp8.h>
 
 #include "act_math.cuh"
+#include "blockscale_math.cuh"
 #include "common.cuh"
 #include "stream_pipe.cuh"
 #include "tuning.h"
@@ -42,13 +43,6 @@ namespace {
 
 constexpr float kFp4Range = 6.f * 448.f;  // src/kernels/blockscale.cu:33
 constexpr int kRowsInFlight = 4;
-
-__host__ __device__ inline int64_t pad_to(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
-
-// Two floats -> two e4m3 bytes (x in the low byte), round to nearest even, saturating.
-__device__ __forceinline__ uint32_t e4m3x2(float2 v) {
-  return __nv_cvt_float2_to_fp8x2(v, __NV_SATFINITE, __NV_E4M3);
-}
 
 // Four float pairs -> eight e2m1 codes, element 0 in the lowest nibble.
 __device__ __forceinline__ uint32_t e2m1x8(float2 a, float2 b, float2 c, float2 d) {
@@ -80,24 +74,6 @@ __device__ __forceinline__ Fp4Scale fp4_scale(const float* amax) {
   return s;
 }
 
-// max(|a|, |b|) on both bf16 halves; the sign bits of the result are meaningless.
-__device__ __forceinline__ uint32_t absmax_bf16x2(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
-__device__ __forceinline__ uint32_t absmax_bf16x2(const uint4& u) {
-  return absmax_bf16x2(absmax_bf16x2(u.x, u.y), absmax_bf16x2(u.z, u.w));
-}
-// Largest magnitude of the two halves, as fp32 (a bf16 value).
-__device__ __forceinline__ float bf16x2_max_to_float(uint32_t m) {
-  m = absmax_bf16x2(m, __byte_perm(m, 0, 0x1032));
-  return __uint_as_float((m << 16) & 0x7fff0000u);
-}
-__device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
-  return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
-}
-
 // Quantises the 16 elements of one thread: raw = two vectors of 8 bf16.  MODE 1: bmax_bits is the
 // packed maximum over the thread's half block; out = 16 e4m3 bytes.  MODE 2: out.x, out.y = 16 e2m1
 // codes.  Returns the scale byte.
@@ -123,12 +99,8 @@ __device__ __forceinline__ uint8_t quant16(const uint4 (&raw)[2], uint32_t packe
   }
   // ue8m0: the smallest 2^e with bmax / 2^e <= 448 (src/kernels/blockscale.cu:111-119), from the bits
   // of bmax (see the head of this file).
-  const uint32_t b = __float_as_uint(bf16x2_max_to_float(packed_max));
-  const int E = int(b >> 23);  // biased exponent; 0 for zero and subnormals, whose e clamps to -127
-  int e = E - 127 - 8 + ((b & 0x007fffffu) > 0x00600000u ? 1 : 0);
-  e = E == 0 ? -127 : max(-127, e);
-  // 2^-e: e is in [-127, 120], so -e + 127 is in [7, 254]
-  const float inv = __uint_as_float(uint32_t(127 - e) << 23);
+  const int e = ue8m0_exponent(bf16x2_max_to_float(packed_max));
+  const float inv = pow2_neg(e);
   const float2 inv2 = make_float2(inv, inv);
   uint32_t c[8];
 #pragma unroll
@@ -144,13 +116,6 @@ __device__ __forceinline__ uint32_t block_absmax(const uint4 (&raw)[2]) {
   if (MODE == 1) m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));
   return m;
 }
-
-// Address of the scale of (row r, scale block kb): 128 x 4 tiles of 512 bytes
-// (src/kernels/blockscale.cu:83 and :127).
-__device__ __forceinline__ int64_t sf_row_offset(uint64_t r, int nkb_pad) {
-  return int64_t(r >> 7) * (int64_t(nkb_pad) * 128) + int64_t((r & 31) * 16 + ((r >> 5) & 3) * 4);
-}
-__device__ __forceinline__ int sf_col_offset(int kb) { return (kb >> 2) * 512 + (kb & 3); }
 
 __device__ __forceinline__ void amax_commit(float m, float* out) {
 #pragma unroll

@@ -12,6 +12,7 @@
 // is read from HBM exactly once into registers; mean and variance come from those registers.
 #pragma once
 
+#include "blockscale_math.cuh"
 #include "bulk_copy.cuh"
 #include "common.cuh"
 
@@ -35,6 +36,10 @@ struct NormArgs {
   int rows_per_cta;
   int64_t row_step;  // bulk-copy kernel: 1 = contiguous row range per CTA, gridDim.x = interleaved rows
   int* err;  // device error word (bounded waits report here)
+  // MXFP8 output instead of bf16 (QUANT kernels): e4m3 codes [rows, dim], interleaved ue8m0 scales
+  uint8_t* q;
+  uint8_t* sf;
+  int nkb_pad;
 };
 
 // Sum over the CTA; `red` is a 16-float scratch that must not be reused before the next
@@ -210,7 +215,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
 // barrier vote, records kErrBulkTimeout in the device's error word, drains the copies it still has in
 // flight (bounded again) and returns.
 
-template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool EXACT>
+template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool EXACT, bool QUANT = false>
 __global__ void __launch_bounds__(norm_max_threads(VPT))
     norm_rows_tma_kernel(const NormArgs a, const int stages, const int stage_bytes) {
   using raw_t = typename Raw4<TIN>::type;
@@ -367,7 +372,27 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
         o[1] = o[1] * A[k].y + B[k].y;
         o[2] = o[2] * A[k].z + B[k].z;
         o[3] = o[3] * A[k].w + B[k].w;
-        if (on[k]) st_stream(reinterpret_cast<uint2*>(orow + 4 * (k * T + tid)), pack4(o));
+        const uint2 pk = pack4(o);
+        if constexpr (QUANT) {
+          // The row rounded to bf16 exactly as above, then quantised as blockscale.cu quantises a bf16
+          // row: a scale block is 32 elements = the 4-element vectors of 8 neighbouring lanes (dim is a
+          // multiple of 32, so the lanes of a block are on or off together).
+          uint32_t m = absmax_bf16x2(pk.x, pk.y);
+          m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));
+          m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 2));
+          m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 4));
+          const int e = ue8m0_exponent(bf16x2_max_to_float(m));
+          const float inv = pow2_neg(e);
+          const float2 inv2 = make_float2(inv, inv);
+          const uint32_t codes = e4m3x2(__fmul2_rn(bf16x2_to_float2(pk.x), inv2)) |
+                                 e4m3x2(__fmul2_rn(bf16x2_to_float2(pk.y), inv2)) << 16;
+          if (on[k]) {
+            __stcs(reinterpret_cast<unsigned int*>(a.q + row * a.dim) + (k * T + tid), codes);
+            if ((tid & 7) == 0) a.sf[sf_row_offset(uint64_t(row), a.nkb_pad) + sf_col_offset((k * T + tid) >> 3)] = uint8_t(e + 127);
+          }
+        } else {
+          if (on[k]) st_stream(reinterpret_cast<uint2*>(orow + 4 * (k * T + tid)), pk);
+        }
       }
     }
   }

@@ -1,0 +1,55 @@
+// Norm + modulation + MXFP8 quantisation in one pass: layernorm_mod / rmsnorm_mod of src/kernels/ops.cu:153-170
+// followed by quantize_blockscaled(MXFP8) of src/kernels/blockscale.cu:147-164, for a normed activation
+// whose only readers are block-scaled GEMMs (the q/k/v and MLP-up projections).  The bulk-copy row
+// kernel rounds its output to bf16 in registers and quantises that instead of storing it: 5 bytes per
+// element instead of 6 + 3.
+#include "norm_dispatch.cuh"
+
+using namespace mxk;
+
+namespace {
+
+template <int MODE>
+int run_norm_quant(const char* name, const float* x, int64_t rows, int64_t dim, float eps, const float* w, MxkRowMod scale,
+                   MxkRowMod shift, void* q, uint8_t* sf, cudaStream_t s) {
+  if (rows <= 0) return MXK_OK;
+  if (int rc = check_norm_common(name, x, rows, dim, q, scale, shift)) return rc;
+  if (!sf) return fail(MXK_ERR_INVALID_ARG, "%s: null scale buffer", name);
+  if (dim % 32 != 0 || !aligned(q, 4)) return fail(MXK_ERR_INVALID_ARG, "%s: need dim %% 32 == 0 and a 4-byte aligned q", name);
+  NormArgs a{};
+  a.x = x, a.rows = rows, a.dim = int(dim), a.nvec = int(dim / 4), a.eps = eps, a.w = w, a.scale = scale, a.shift = shift;
+  a.q = static_cast<uint8_t*>(q), a.sf = sf, a.nkb_pad = int(pad_to(dim / 32, 4));
+  NormPlan p;
+  if (!norm_vector_ok<float>(a) || !plan_norm(a.nvec, a.rows, p))
+    return fail(MXK_ERR_INVALID_ARG, "%s: dim %lld or an unaligned vector is outside the one-pass kernel; call the norm and "
+                "mxk_quantize_blockscaled separately", name, (long long)dim);
+  // scale padding, as mxk_quantize_blockscaled clears it
+  const int64_t nkb = dim / 32;
+  cudaError_t e = cudaSuccess;
+  if (nkb % 4 != 0) e = cudaMemsetAsync(sf, 0, size_t(pad_to(rows, 128) * pad_to(nkb, 4)), s);
+  else if (rows % 128 != 0) e = cudaMemsetAsync(sf + rows / 128 * nkb * 128, 0, size_t(nkb * 128), s);
+  if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "%s: cudaMemsetAsync: %s", name, cudaGetErrorString(e));
+  if constexpr (MODE == 1) {
+    if (w) launch_norm<1, float, true, false, true>(p, a, true, s);
+    else launch_norm<1, float, false, false, true>(p, a, true, s);
+  } else {
+    launch_norm<0, float, false, false, true>(p, a, true, s);
+  }
+  return after_launch(name);
+}
+
+}  // namespace
+
+extern "C" {
+
+int mxk_layernorm_mod_quant_mxfp8(const float* x, int64_t rows, int64_t dim, float eps, MxkRowMod scale, MxkRowMod shift,
+                                  void* q, uint8_t* sf, mxk_stream_t stream) {
+  return run_norm_quant<0>("layernorm_mod_quant_mxfp8", x, rows, dim, eps, nullptr, scale, shift, q, sf, as_stream(stream));
+}
+
+int mxk_rmsnorm_mod_quant_mxfp8(const float* x, int64_t rows, int64_t dim, float eps, const float* w, MxkRowMod scale,
+                                MxkRowMod shift, void* q, uint8_t* sf, mxk_stream_t stream) {
+  return run_norm_quant<1>("rmsnorm_mod_quant_mxfp8", x, rows, dim, eps, w, scale, shift, q, sf, as_stream(stream));
+}
+
+}  // extern "C"

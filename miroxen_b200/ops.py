@@ -26,7 +26,7 @@ __all__ = [
     "axpby_f32", "gated_residual_norm", "qkv_norm_rope", "HeadSpec", "dit_block_ops", "BlockArgs", "RowMod",
     "HostPipeline", "OpTimes", "dit_block_ops_host_static", "device_error", "launch_count", "reset_launch_count", "set_tuning",
     "Q_MXFP8", "Q_NVFP4", "QMat", "qdata_bytes", "qscale_bytes", "quantize_blockscaled", "act_quantize_mxfp8",
-    "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF",
+    "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8",
 ]
 
 
@@ -249,6 +249,29 @@ def act_quantize_mxfp8(act_mode: int, in_, rows: int, F: int, out: Optional[QMat
         out = QMat(torch.empty(qdata_bytes(Q_MXFP8, rows, F), dtype=torch.uint8, device=in_.device),
                    torch.empty(qscale_bytes(Q_MXFP8, rows, F), dtype=torch.uint8, device=in_.device))
     check(lib().mxk_act_quantize_mxfp8(act_mode, _p(in_), rows, F, _p(out.q), _p(out.sf), _stream(stream)))
+    return out
+
+
+def _qmat_for(x, rows, dim, out):
+    if out is not None:
+        return out
+    return QMat(torch.empty(qdata_bytes(Q_MXFP8, rows, dim), dtype=torch.uint8, device=x.device),
+                torch.empty(qscale_bytes(Q_MXFP8, rows, dim), dtype=torch.uint8, device=x.device))
+
+
+def layernorm_mod_quant_mxfp8(x, rows, dim, eps, scale: RowMod, shift: RowMod, out: Optional[QMat] = None, stream=None) -> QMat:
+    """layernorm_mod (src/kernels/ops.h:22) and its MXFP8 quantisation in one pass."""
+    out = _qmat_for(x, rows, dim, out)
+    check(lib().mxk_layernorm_mod_quant_mxfp8(_p(x), rows, dim, eps, scale or _NONE, shift or _NONE, _p(out.q), _p(out.sf),
+                                              _stream(stream)))
+    return out
+
+
+def rmsnorm_mod_quant_mxfp8(x, rows, dim, eps, w, scale: RowMod, shift: RowMod, out: Optional[QMat] = None, stream=None) -> QMat:
+    """rmsnorm_mod (src/kernels/ops.h:24) and its MXFP8 quantisation in one pass."""
+    out = _qmat_for(x, rows, dim, out)
+    check(lib().mxk_rmsnorm_mod_quant_mxfp8(_p(x), rows, dim, eps, _p(w), scale or _NONE, shift or _NONE, _p(out.q), _p(out.sf),
+                                            _stream(stream)))
     return out
 
 

@@ -233,3 +233,72 @@ def test_act_quantize_argument_errors(mx):
         mx.ops.act_quantize_mxfp8(0, x.view(-1)[1:].data_ptr(), 3, 64, out)
     mx.ops.act_quantize_mxfp8(0, x, 0, 64, out)
     torch.cuda.synchronize()
+
+
+# ---- norm + modulation + MXFP8 quantisation in one pass ----
+
+@pytest.mark.parametrize("kind", ["layernorm", "rmsnorm", "rmsnorm_now"])
+@pytest.mark.parametrize("rows,dim,plen", [(1, 32, 0), (7, 96, 3), (130, 3072, 41), (300, 5120, 0), (2049, 1152, 2049),
+                                           (33, 4128, 5), (1200, 3072, 256), (64, 8192, 64)])
+def test_norm_quantize_equals_two_calls_and_oracle_bound(mx, kind, rows, dim, plen):
+    g = H.rng(rows * 3 + dim)
+    x = H.normal_f32(g, (rows, dim), 1.3, 0.2)
+    vecs = [H.normal_f32(g, dim, 0.3) for _ in range(4)]
+    w = None if kind != "rmsnorm" else H.normal_f32(g, dim, 0.1, 1.0)
+    xd, wd = H.to_dev(torch, x), (H.to_dev(torch, w) if w is not None else None)
+    vd = [H.to_dev(torch, v) for v in vecs]
+    sc, sh = mx.row_mod(vd[0], vd[1], plen), mx.row_mod(vd[2], vd[3], plen)
+    eps = 1e-6
+    bf = torch.empty(rows, dim, dtype=torch.bfloat16, device="cuda")
+    q = H.Guarded(torch, (rows * dim,), torch.uint8)
+    sf = H.Guarded(torch, (mx.ops.qscale_bytes(1, rows, dim),), torch.uint8)
+    sf.t.fill_(0x5A)
+    if kind == "layernorm":
+        mx.ops.layernorm_mod(xd, rows, dim, eps, sc, sh, bf)
+        mx.ops.layernorm_mod_quant_mxfp8(xd, rows, dim, eps, sc, sh, mx.ops.QMat(q.t, sf.t))
+        ref = orc.layernorm_mod(x, eps, orc.mod(vecs[0], vecs[1], plen), orc.mod(vecs[2], vecs[3], plen))
+    else:
+        mx.ops.rmsnorm_mod(xd, rows, dim, eps, wd, sc, sh, bf)
+        mx.ops.rmsnorm_mod_quant_mxfp8(xd, rows, dim, eps, wd, sc, sh, mx.ops.QMat(q.t, sf.t))
+        ref = orc.rmsnorm_mod(x, eps, w, orc.mod(vecs[0], vecs[1], plen), orc.mod(vecs[2], vecs[3], plen))
+    two = mx.ops.quantize_blockscaled(1, bf, dim, rows, dim)
+    torch.cuda.synchronize()
+    q.check("q")
+    sf.check("sf")
+    q1, sf1 = q.t.cpu().numpy(), sf.t.cpu().numpy()
+    assert np.array_equal(sf1, two.sf.cpu().numpy()), "scale bytes differ from the two calls"
+    assert np.array_equal(q1, two.q.cpu().numpy()), "data bytes differ from the two calls"
+    d = orc.dequantize_blockscaled(1, q1, sf1, 0.0, rows, dim)
+    assert rel_rms(d, bits_to_f32(ref).reshape(rows, dim)) < ELEM_ERR[1]
+
+
+def test_norm_quantize_many_trips_per_cta(mx):
+    """One CTA per SM, so every CTA wraps its ring of stages many times."""
+    g = H.rng(3)
+    rows, dim = 3000, 1024
+    x = H.to_dev(torch, H.normal_f32(g, (rows, dim), 2.0))
+    bf = torch.empty(rows, dim, dtype=torch.bfloat16, device="cuda")
+    none = mx.row_mod()
+    mx.ops.set_tuning("norm_ctas_per_sm", 1)
+    try:
+        mx.ops.layernorm_mod(x, rows, dim, 1e-6, none, none, bf)
+        one = mx.ops.layernorm_mod_quant_mxfp8(x, rows, dim, 1e-6, none, none)
+    finally:
+        mx.ops.set_tuning("norm_ctas_per_sm", 0)
+    two = mx.ops.quantize_blockscaled(1, bf, dim, rows, dim)
+    torch.cuda.synchronize()
+    assert torch.equal(one.q, two.q) and torch.equal(one.sf, two.sf)
+
+
+def test_norm_quantize_argument_errors(mx):
+    x = torch.zeros(4, 64, dtype=torch.float32, device="cuda")
+    none = mx.row_mod()
+    out = mx.ops.layernorm_mod_quant_mxfp8(x, 4, 64, 1e-6, none, none)
+    with pytest.raises(mx.MxkError):  # dim not a multiple of 32
+        mx.ops.layernorm_mod_quant_mxfp8(x, 4, 48, 1e-6, none, none, out)
+    with pytest.raises(mx.MxkError):  # unaligned row
+        mx.ops.layernorm_mod_quant_mxfp8(x.view(-1)[1:].data_ptr(), 3, 64, 1e-6, none, none, out)
+    with pytest.raises(mx.MxkError):
+        mx.ops.rmsnorm_mod_quant_mxfp8(x, 4, 64, 1e-6, None, none, none, mx.ops.QMat(out.q, None))
+    mx.ops.rmsnorm_mod_quant_mxfp8(x, 0, 64, 1e-6, None, none, none, out)
+    torch.cuda.synchronize()
