@@ -352,9 +352,9 @@ int mxk_act_quantize_mxfp8(int act_mode, const mxk_bf16* in, int64_t rows, int64
 /* Norm, modulation and MXFP8 quantisation in one pass, for a normed activation whose only readers are
  * block-scaled GEMMs.  One call in place of layernorm_mod / rmsnorm_mod (src/kernels/ops.h:22-25) followed by
  * quantize_blockscaled(MXFP8) (src/kernels/blockscale.h:30); arguments as mxk_layernorm_mod / mxk_rmsnorm_mod
- * with (q, sf) in place of the bf16 output.  The bf16 row is rounded in registers and never written: 5 bytes
+ * with (q, sf) in place of the bf16 output.  The bf16 row stays in shared memory and is never written: 5 bytes
  * per element instead of 9.  Byte-identical to the two calls of this library.  dim % 32 == 0, 16-byte aligned
- * vectors, q 4-byte aligned; a shape outside the one-pass kernel returns -1 and asks for the two calls. */
+ * vectors and q; a shape outside the one-pass kernel returns -1 and asks for the two calls. */
 int mxk_layernorm_mod_quant_mxfp8(const float* x, int64_t rows, int64_t dim, float eps, MxkRowMod scale,
                                   MxkRowMod shift, void* q, uint8_t* sf, mxk_stream_t stream);
 int mxk_rmsnorm_mod_quant_mxfp8(const float* x, int64_t rows, int64_t dim, float eps, const float* w, MxkRowMod scale,

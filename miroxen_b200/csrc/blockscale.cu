@@ -97,24 +97,15 @@ __device__ __forceinline__ uint8_t quant16(const uint4 (&raw)[2], uint32_t packe
     out.z = out.w = 0;
     return se;
   }
-  // ue8m0: the smallest 2^e with bmax / 2^e <= 448 (src/kernels/blockscale.cu:111-119), from the bits
-  // of bmax (see the head of this file).
-  const int e = ue8m0_exponent(bf16x2_max_to_float(packed_max));
-  const float inv = pow2_neg(e);
-  const float2 inv2 = make_float2(inv, inv);
-  uint32_t c[8];
-#pragma unroll
-  for (int i = 0; i < 8; i++) c[i] = e4m3x2(__fmul2_rn(bf16x2_to_float2(w[i]), inv2));
-  out = make_uint4(c[0] | c[1] << 16, c[2] | c[3] << 16, c[4] | c[5] << 16, c[6] | c[7] << 16);
-  return uint8_t(e + 127);
+  // ue8m0 scale and e4m3 codes (src/kernels/blockscale.cu:111-125), see blockscale_math.cuh
+  return mxfp8_quant16(raw, packed_max, out);
 }
 
 // Packed |.|-maximum of a thread's 16 elements, joined with the other half of the block for MXFP8.
 template <int MODE>
 __device__ __forceinline__ uint32_t block_absmax(const uint4 (&raw)[2]) {
-  uint32_t m = absmax_bf16x2(absmax_bf16x2(raw[0]), absmax_bf16x2(raw[1]));
-  if (MODE == 1) m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));
-  return m;
+  if (MODE == 1) return mxfp8_block_absmax(raw);
+  return absmax_bf16x2(absmax_bf16x2(raw[0]), absmax_bf16x2(raw[1]));
 }
 
 __device__ __forceinline__ void amax_commit(float m, float* out) {

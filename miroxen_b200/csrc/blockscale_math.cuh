@@ -48,6 +48,25 @@ __device__ __forceinline__ int ue8m0_exponent(float bmax) {
 // 2^-e for e in [-127, 120]: the exponent field is -e + 127, in [7, 254].
 __device__ __forceinline__ float pow2_neg(int e) { return __uint_as_float(uint32_t(127 - e) << 23); }
 
+// MXFP8 on 16 consecutive elements held by one thread (two vectors of 8 bf16), the two halves of a
+// 32-element block sitting in neighbouring lanes.
+__device__ __forceinline__ uint32_t mxfp8_block_absmax(const uint4 (&raw)[2]) {
+  const uint32_t m = absmax_bf16x2(absmax_bf16x2(raw[0]), absmax_bf16x2(raw[1]));
+  return absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));
+}
+// out = 16 e4m3 bytes; returns the ue8m0 scale byte of the block.
+__device__ __forceinline__ uint8_t mxfp8_quant16(const uint4 (&raw)[2], uint32_t packed_max, uint4& out) {
+  const uint32_t w[8] = {raw[0].x, raw[0].y, raw[0].z, raw[0].w, raw[1].x, raw[1].y, raw[1].z, raw[1].w};
+  const int e = ue8m0_exponent(bf16x2_max_to_float(packed_max));
+  const float inv = pow2_neg(e);
+  const float2 inv2 = make_float2(inv, inv);
+  uint32_t c[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) c[i] = e4m3x2(__fmul2_rn(bf16x2_to_float2(w[i]), inv2));
+  out = make_uint4(c[0] | c[1] << 16, c[2] | c[3] << 16, c[4] | c[5] << 16, c[6] | c[7] << 16);
+  return uint8_t(e + 127);
+}
+
 // Address of the scale of (row r, scale block kb): 128 x 4 tiles of 512 bytes
 // (src/kernels/blockscale.cu:83 and :127).
 __device__ __forceinline__ int64_t sf_row_offset(uint64_t r, int nkb_pad) {

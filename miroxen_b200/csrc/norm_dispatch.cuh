@@ -50,7 +50,8 @@ inline void launch_norm_inst(const NormPlan& p, NormArgs a, bool tma, cudaStream
     if (stages <= 0) stages = 2;
     if (stages < 2) stages = 2;
     if (stages > kNormMaxStages) stages = kNormMaxStages;
-    const size_t smem = size_t(stages) * stage_bytes;
+    // the quantising form keeps the bf16 row in shared memory behind the stages
+    const size_t smem = size_t(stages) * stage_bytes + (QUANT ? size_t(a.dim) * 2 : 0);
     // static shared memory (reduction scratch, barriers) counts against the 48 KB default too
     if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     const unsigned grid = norm_grid(a, tune(TUNE_NORM_CTAS_PER_SM, resident_ctas(k, p.threads, smem)));

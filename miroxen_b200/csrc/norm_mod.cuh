@@ -374,25 +374,33 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
         o[3] = o[3] * A[k].w + B[k].w;
         const uint2 pk = pack4(o);
         if constexpr (QUANT) {
-          // The row rounded to bf16 exactly as above, then quantised as blockscale.cu quantises a bf16
-          // row: a scale block is 32 elements = the 4-element vectors of 8 neighbouring lanes (dim is a
-          // multiple of 32, so the lanes of a block are on or off together).
-          uint32_t m = absmax_bf16x2(pk.x, pk.y);
-          m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 1));
-          m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 2));
-          m = absmax_bf16x2(m, __shfl_xor_sync(0xffffffffu, m, 4));
-          const int e = ue8m0_exponent(bf16x2_max_to_float(m));
-          const float inv = pow2_neg(e);
-          const float2 inv2 = make_float2(inv, inv);
-          const uint32_t codes = e4m3x2(__fmul2_rn(bf16x2_to_float2(pk.x), inv2)) |
-                                 e4m3x2(__fmul2_rn(bf16x2_to_float2(pk.y), inv2)) << 16;
-          if (on[k]) {
-            __stcs(reinterpret_cast<unsigned int*>(a.q + row * a.dim) + (k * T + tid), codes);
-            if ((tid & 7) == 0) a.sf[sf_row_offset(uint64_t(row), a.nkb_pad) + sf_col_offset((k * T + tid) >> 3)] = uint8_t(e + 127);
-          }
+          // the bf16 row goes to shared memory instead of global memory
+          if (on[k]) reinterpret_cast<uint2*>(dyn + size_t(stages) * stage_bytes)[k * T + tid] = pk;
         } else {
           if (on[k]) st_stream(reinterpret_cast<uint2*>(orow + 4 * (k * T + tid)), pk);
         }
+      }
+      if constexpr (QUANT) {
+        // Quantise the row as blockscale.cu quantises a bf16 row, 16 elements per thread (the two
+        // halves of a 32-element block in neighbouring lanes; dim is a multiple of 32).  The next
+        // row's writes to the buffer come after that row's reduction barrier, which every thread
+        // reaches only when it is done reading here.
+        __syncthreads();
+        const uint4* orow16 = reinterpret_cast<const uint4*>(dyn + size_t(stages) * stage_bytes);
+        const int n16 = a.dim >> 4, lane = tid & 31;
+        uint8_t* qrow = a.q + row * a.dim;
+        uint8_t* sfr = a.sf + sf_row_offset(uint64_t(row), a.nkb_pad);
+        for (int i0 = tid - lane; i0 < n16; i0 += T) {
+          const int i = i0 + lane, ic = i < n16 ? i : n16 - 1;
+          const uint4 raw[2] = {orow16[2 * ic], orow16[2 * ic + 1]};
+          uint4 codes;
+          const uint8_t sbyte = mxfp8_quant16(raw, mxfp8_block_absmax(raw), codes);
+          if (i < n16) {
+            st_stream(reinterpret_cast<uint4*>(qrow) + i, codes);
+            if ((lane & 1) == 0) sfr[sf_col_offset(i >> 1)] = sbyte;
+          }
+        }
+        if (nwarps == 1) __syncwarp();
       }
     }
   }

@@ -1,7 +1,7 @@
 // Norm + modulation + MXFP8 quantisation in one pass: layernorm_mod / rmsnorm_mod of src/kernels/ops.cu:153-170
 // followed by quantize_blockscaled(MXFP8) of src/kernels/blockscale.cu:147-164, for a normed activation
 // whose only readers are block-scaled GEMMs (the q/k/v and MLP-up projections).  The bulk-copy row
-// kernel rounds its output to bf16 in registers and quantises that instead of storing it: 5 bytes per
+// kernel rounds its output to bf16, parks the row in shared memory and quantises it from there instead of storing it: 5 bytes per
 // element instead of 6 + 3.
 #include "norm_dispatch.cuh"
 
@@ -15,7 +15,7 @@ int run_norm_quant(const char* name, const float* x, int64_t rows, int64_t dim, 
   if (rows <= 0) return MXK_OK;
   if (int rc = check_norm_common(name, x, rows, dim, q, scale, shift)) return rc;
   if (!sf) return fail(MXK_ERR_INVALID_ARG, "%s: null scale buffer", name);
-  if (dim % 32 != 0 || !aligned(q, 4)) return fail(MXK_ERR_INVALID_ARG, "%s: need dim %% 32 == 0 and a 4-byte aligned q", name);
+  if (dim % 32 != 0 || !aligned(q, 16)) return fail(MXK_ERR_INVALID_ARG, "%s: need dim %% 32 == 0 and a 16-byte aligned q", name);
   NormArgs a{};
   a.x = x, a.rows = rows, a.dim = int(dim), a.nvec = int(dim / 4), a.eps = eps, a.w = w, a.scale = scale, a.shift = shift;
   a.q = static_cast<uint8_t*>(q), a.sf = sf, a.nkb_pad = int(pad_to(dim / 32, 4));
