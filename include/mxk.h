@@ -360,6 +360,21 @@ int mxk_layernorm_mod_quant_mxfp8(const float* x, int64_t rows, int64_t dim, flo
 int mxk_rmsnorm_mod_quant_mxfp8(const float* x, int64_t rows, int64_t dim, float eps, const float* w, MxkRowMod scale,
                                 MxkRowMod shift, void* q, uint8_t* sf, mxk_stream_t stream);
 
+/* ---- latent layout kernels either side of the DiT ----
+ *
+ * mx::qwen_latent::encode / decode (src/kernels/qwen_latent.h:7-8): encode x [64, n] -> y [n, 64] as
+ * (x - mean[c]) / std[c]; decode x [n, 64] -> y [64, n] as x * std[c] + mean[c]; each step rounded on
+ * its own (no fused multiply-add), bit-identical to the reference.  mean, std: 64 device floats; x and y
+ * must not overlap.
+ * mx::h3_latent::video / audio (src/kernels/h3_latent.h:6-7): DiT rows -> the VAE's channel-first layout,
+ * values untouched.  video: rows [frames * h/2 * w/2, 96] -> z [24, frames, h, w] (a row holds 24 channels
+ * x 2 x 2 pixels); audio: rows [2 * samples, 32] -> z [2, 32, samples].  h and w even.
+ * Unlike the layer ops, a bad argument here is an error (-1), as in the reference. */
+int mxk_qwen_latent_encode(const float* x, float* y, int64_t n, const float* mean, const float* std, mxk_stream_t stream);
+int mxk_qwen_latent_decode(const float* x, float* y, int64_t n, const float* mean, const float* std, mxk_stream_t stream);
+int mxk_h3_latent_video(const float* rows, float* z, int64_t frames, int64_t h, int64_t w, mxk_stream_t stream);
+int mxk_h3_latent_audio(const float* rows, float* z, int64_t samples, mxk_stream_t stream);
+
 /* Development knob: overrides a launch-shape default (see tuning.h for the names); value 0
  * restores the default.  Results do not depend on it. */
 int mxk_set_tuning(const char* name, int value);

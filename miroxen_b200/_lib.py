@@ -62,6 +62,10 @@ PROTOTYPES = {
     "mxk_qscale_bytes": (_I64, [_I, _I64, _I64]),
     "mxk_quantize_blockscaled": (_I, [_I, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "mxk_act_quantize_mxfp8": (_I, [_I, _P, _I64, _I64, _P, _P, _P]),
+    "mxk_qwen_latent_encode": (_I, [_P, _P, _I64, _P, _P, _P]),
+    "mxk_qwen_latent_decode": (_I, [_P, _P, _I64, _P, _P, _P]),
+    "mxk_h3_latent_video": (_I, [_P, _P, _I64, _I64, _I64, _P]),
+    "mxk_h3_latent_audio": (_I, [_P, _P, _I64, _P]),
     "mxk_layernorm_mod_quant_mxfp8": (_I, [_P, _I64, _I64, _F, RowMod, RowMod, _P, _P, _P]),
     "mxk_rmsnorm_mod_quant_mxfp8": (_I, [_P, _I64, _I64, _F, _P, RowMod, RowMod, _P, _P, _P]),
     "mxk_layernorm_mod": (_I, [_P, _I64, _I64, _F, RowMod, RowMod, _P, _P]),

@@ -27,6 +27,7 @@ __all__ = [
     "HostPipeline", "OpTimes", "dit_block_ops_host_static", "device_error", "launch_count", "reset_launch_count", "set_tuning",
     "Q_MXFP8", "Q_NVFP4", "QMat", "qdata_bytes", "qscale_bytes", "quantize_blockscaled", "act_quantize_mxfp8",
     "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8",
+    "qwen_latent_encode", "qwen_latent_decode", "h3_latent_video", "h3_latent_audio",
 ]
 
 
@@ -273,6 +274,26 @@ def rmsnorm_mod_quant_mxfp8(x, rows, dim, eps, w, scale: RowMod, shift: RowMod, 
     check(lib().mxk_rmsnorm_mod_quant_mxfp8(_p(x), rows, dim, eps, _p(w), scale or _NONE, shift or _NONE, _p(out.q), _p(out.sf),
                                             _stream(stream)))
     return out
+
+
+def qwen_latent_encode(x, y, n, mean, std, stream=None):
+    """mx::qwen_latent::encode (src/kernels/qwen_latent.h:7): [64, n] -> [n, 64], (x - mean) / std."""
+    check(lib().mxk_qwen_latent_encode(_p(x), _p(y), n, _p(mean), _p(std), _stream(stream)))
+
+
+def qwen_latent_decode(x, y, n, mean, std, stream=None):
+    """mx::qwen_latent::decode (src/kernels/qwen_latent.h:8): [n, 64] -> [64, n], x * std + mean."""
+    check(lib().mxk_qwen_latent_decode(_p(x), _p(y), n, _p(mean), _p(std), _stream(stream)))
+
+
+def h3_latent_video(rows, z, frames, h, w, stream=None):
+    """mx::h3_latent::video (src/kernels/h3_latent.h:6)."""
+    check(lib().mxk_h3_latent_video(_p(rows), _p(z), frames, h, w, _stream(stream)))
+
+
+def h3_latent_audio(rows, z, samples, stream=None):
+    """mx::h3_latent::audio (src/kernels/h3_latent.h:7)."""
+    check(lib().mxk_h3_latent_audio(_p(rows), _p(z), samples, _stream(stream)))
 
 
 def device_error(clear: bool = True) -> int:

@@ -65,6 +65,15 @@ def ref_blockscale() -> C.CDLL:
     return _load("_ref/libmx_ref_blockscale.so")
 
 
+def have_ref_latent() -> bool:
+    return (HERE / "_ref" / "libmx_ref_latent.so").exists()
+
+
+def ref_latent() -> C.CDLL:
+    """The reference's src/kernels/qwen_latent.cu and h3_latent.cu built for sm_100a (device pointers)."""
+    return _load("_ref/libmx_ref_latent.so")
+
+
 def ref_ops() -> C.CDLL:
     """The reference's src/kernels/ops.cu built for sm_100a (device pointers; needs a GPU)."""
     return _load("_ref/libmx_ref_ops.so")
@@ -347,3 +356,43 @@ def dequantize_blockscaled(mode, q, sf, amax, rows, K):
     f.argtypes, f.restype = [C.c_int, _P, _P, _F, _I64, _I64, _P], None
     f(mode, _ptr(q), _ptr(sf), amax, rows, K, _ptr(out))
     return out
+
+
+def qwen_latent_encode(x, mean, std):
+    """x: fp32 [64, n] -> [n, 64]."""
+    x = np.ascontiguousarray(x, np.float32)
+    n = x.shape[1]
+    y = np.empty((n, 64), np.float32)
+    f = oracle().or_qwen_latent_encode
+    f.argtypes, f.restype = [_P, _P, _I64, _P, _P], None
+    f(_ptr(x), _ptr(y), n, _ptr(np.ascontiguousarray(mean, np.float32)), _ptr(np.ascontiguousarray(std, np.float32)))
+    return y
+
+
+def qwen_latent_decode(x, mean, std):
+    """x: fp32 [n, 64] -> [64, n]."""
+    x = np.ascontiguousarray(x, np.float32)
+    n = x.shape[0]
+    y = np.empty((64, n), np.float32)
+    f = oracle().or_qwen_latent_decode
+    f.argtypes, f.restype = [_P, _P, _I64, _P, _P], None
+    f(_ptr(x), _ptr(y), n, _ptr(np.ascontiguousarray(mean, np.float32)), _ptr(np.ascontiguousarray(std, np.float32)))
+    return y
+
+
+def h3_latent_video(rows, F, H, W):
+    rows = np.ascontiguousarray(rows, np.float32)
+    z = np.empty((24, F, H, W), np.float32)
+    f = oracle().or_h3_latent_video
+    f.argtypes, f.restype = [_P, _P, _I64, _I64, _I64], None
+    f(_ptr(rows), _ptr(z), F, H, W)
+    return z
+
+
+def h3_latent_audio(rows, A):
+    rows = np.ascontiguousarray(rows, np.float32)
+    z = np.empty((2, 32, A), np.float32)
+    f = oracle().or_h3_latent_audio
+    f.argtypes, f.restype = [_P, _P, _I64], None
+    f(_ptr(rows), _ptr(z), A)
+    return z

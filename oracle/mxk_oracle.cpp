@@ -546,3 +546,47 @@ void or_dequantize_blockscaled(int mode, const uint8_t* q, const uint8_t* sf, fl
 }
 
 }  // extern "C"
+
+// ---- latent layout either side of the DiT -------------------------------------------------------
+// The reference's tests hold the CPU formulas these restate: tests/qwen_latent_test.cpp:30-46 (every
+// step rounded on its own: `volatile float delta = x - mean; expected = delta / scale`, and
+// `product = x * scale; expected = product + mean`) and tests/h3_latent_test.cpp:25-36 (pure index
+// maps).  This file is compiled with -ffp-contract=off, so the two-step forms below round twice.
+extern "C" {
+
+void or_qwen_latent_encode(const float* x, float* y, int64_t n, const float* mean, const float* sd) {
+  for (int64_t p = 0; p < n; p++)
+    for (int c = 0; c < 64; c++) {
+      const float delta = x[int64_t(c) * n + p] - mean[c];
+      y[p * 64 + c] = delta / sd[c];
+    }
+}
+
+void or_qwen_latent_decode(const float* x, float* y, int64_t n, const float* mean, const float* sd) {
+  for (int c = 0; c < 64; c++)
+    for (int64_t p = 0; p < n; p++) {
+      const float product = x[p * 64 + c] * sd[c];
+      y[int64_t(c) * n + p] = product + mean[c];
+    }
+}
+
+void or_h3_latent_video(const float* rows, float* z, int64_t F, int64_t H, int64_t W) {
+  for (int64_t f = 0; f < F; f++)
+    for (int64_t y = 0; y < H / 2; y++)
+      for (int64_t x = 0; x < W / 2; x++)
+        for (int ch = 0; ch < 24; ch++)
+          for (int ph = 0; ph < 2; ph++)
+            for (int pw = 0; pw < 2; pw++) {
+              const int64_t row = (f * (H / 2) + y) * (W / 2) + x;
+              z[((ch * F + f) * H + 2 * y + ph) * W + 2 * x + pw] = rows[row * 96 + ch * 4 + ph * 2 + pw];
+            }
+}
+
+void or_h3_latent_audio(const float* rows, float* z, int64_t A) {
+  for (int ch = 0; ch < 2; ch++)
+    for (int64_t a = 0; a < A; a++)
+      for (int k = 0; k < 32; k++) z[(ch * 32 + k) * A + a] = rows[(ch * A + a) * 32 + k];
+}
+
+}  // extern "C"
+
