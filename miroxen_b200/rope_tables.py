@@ -155,6 +155,127 @@ def h3_rope_table(T, F_lat, H, W, A, anchors: Sequence[str], inv_freq, device="c
     return _expand(luts_c, luts_s, [nf, nf, nf], runs, S, device, stream)
 
 
+def _spatial_grid(dim, H, W):
+    g = np.empty(dim // 2, dtype=np.float32)
+    check(lib().mxk_h3_spatial_grid_host(dim, H, W, g.ctypes.data))
+    return g
+
+
+_PER_LATENT = (1, 4, 4, 4, 4)
+_RESCALE = 5.0 / 3.0
+
+
+def h3_ref2va_plan(T, refs, F_lat, H, W, A):
+    """Per-axis position lists and run descriptors of the reference-conditioned layout
+    (src/models/minimax_h3/layout.cpp:121-188): T text rows | one block per reference in request order
+    (a video's sound track before its frames) | 2A target audio rows | F_lat target video frames.
+
+    refs: dicts {kind: "image" | "video" | "audio", frames, h, w, audio} (latent geometry; audio =
+    latents per channel).  Times run on one clock that starts at T: an image takes one unit, an audio
+    reference its length, a video the longer of its track and its frame spans; all in double, as the
+    reference, and rounded to fp32 once.  Returns (t_list, h_list, w_list, runs, S); runs index the
+    lists as MxkRopeRun does.
+    """
+    if H % 2 or W % 2:
+        raise ValueError("latent extents must be even")
+    t_list = [float(i) for i in range(T)]
+    h_list, w_list = [np.zeros(1, np.float32)], [np.zeros(1, np.float32)]
+    grids = {}
+
+    def grid(gh, gw):
+        """(index of the grid's first h entry, first w entry, rows per frame, columns per row)"""
+        if (gh, gw) not in grids:
+            h0 = sum(a.size for a in h_list)
+            w0 = sum(a.size for a in w_list)
+            h_list.append(_spatial_grid(gh, gh, gw)), w_list.append(_spatial_grid(gw, gh, gw))
+            grids[(gh, gw)] = (h0, w0, gh // 2, gw // 2)
+        return grids[(gh, gw)]
+
+    runs = []
+    row = [T]
+    if T > 0:
+        runs.append(RopeRun(0, T, 1, 1, _i32([0, 0, 0]), _i32([1, 0, 0]), _i32([0, 0, 0]), _i32([0, 0, 0])))
+
+    def audio_rows(n, t0, g):
+        h0, w0, hh, ww = g
+        base_t = len(t_list)
+        t_list.extend(t0 + float(a) for a in range(n))
+        runs.append(RopeRun(row[0], 2, n, 1, _i32([base_t, 0, w0]), _i32([0, 0, ww - 1]), _i32([1, 0, 0]), _i32([0, 0, 0])))
+        row[0] += 2 * n
+
+    def video_rows(g, frames, t0, image):
+        h0, w0, hh, ww = g
+        base_t = len(t_list)
+        t = t0
+        for f in range(frames):
+            t_list.append(t)
+            if not image:
+                t += _RESCALE * _PER_LATENT[f % 5]
+        runs.append(RopeRun(row[0], frames, hh, ww, _i32([base_t, h0, w0]), _i32([1, 0, 0]), _i32([0, 1, 0]), _i32([0, 0, 1])))
+        row[0] += frames * hh * ww
+
+    target = grid(H, W)
+    clock = float(T)
+    for r in refs:
+        kind = r["kind"]
+        if kind == "audio":
+            if r.get("audio", 0) <= 0:
+                raise ValueError("an audio reference needs audio > 0")
+            audio_rows(r["audio"], clock, target)
+            clock += float(r["audio"])
+            continue
+        if r["h"] % 2 or r["w"] % 2:
+            raise ValueError("latent extents must be even")
+        g = grid(r["h"], r["w"])
+        if kind == "image":
+            video_rows(g, 1, clock, True)
+            clock += 1.0
+            continue
+        if kind != "video":
+            raise ValueError(f"unknown reference kind {kind!r}")
+        if r.get("audio", 0) > 0:
+            audio_rows(r["audio"], clock, g)
+        video_rows(g, r["frames"], clock, False)
+        span = 0.0
+        for f in range(r["frames"]):
+            span += _RESCALE * _PER_LATENT[f % 5]
+        clock += max(float(r.get("audio", 0)), span)
+    if A > 0:
+        audio_rows(A, clock, target)
+    if F_lat > 0:
+        video_rows(target, F_lat, clock, False)
+    return (np.asarray(t_list, dtype=np.float64).astype(np.float32), np.concatenate(h_list), np.concatenate(w_list), runs,
+            row[0])
+
+
+def positions_from_plan(t_list, h_list, w_list, runs, S) -> np.ndarray:
+    """fp32 [S, 3] positions the runs describe (host side; what mxk_rope_table_expand gathers from)."""
+    pos = np.zeros((S, 3), np.float32)
+    for r in runs:
+        i0, i1, i2 = np.meshgrid(np.arange(r.n0), np.arange(r.n1), np.arange(r.n2), indexing="ij")
+        rows = r.row0 + (i0 * r.n1 + i1) * r.n2 + i2
+        for a, lst in enumerate((t_list, h_list, w_list)):
+            idx = r.base[a] + i0 * r.step0[a] + i1 * r.step1[a] + i2 * r.step2[a]
+            pos[rows.ravel(), a] = lst[idx.ravel()]
+    return pos
+
+
+def h3_ref2va_rope_table(T, refs, F_lat, H, W, A, inv_freq, device="cuda", stream=None):
+    """cos/sin fp32 [S, 3 nf] of the reference-conditioned layout (h3_ref2va_plan)."""
+    inv_freq = np.ascontiguousarray(inv_freq, dtype=np.float32)
+    nf = inv_freq.size
+    t_list, h_list, w_list, runs, S = h3_ref2va_plan(T, refs, F_lat, H, W, A)
+    luts_c, luts_s = [], []
+    for pos in (t_list, h_list, w_list):
+        pos = np.ascontiguousarray(pos)
+        lc = np.empty((pos.size, nf), dtype=np.float32)
+        ls = np.empty((pos.size, nf), dtype=np.float32)
+        check(lib().mxk_rope_lut_f32_host(pos.ctypes.data, pos.size, inv_freq.ctypes.data, nf, lc.ctypes.data,
+                                          ls.ctypes.data))
+        luts_c.append(lc), luts_s.append(ls)
+    return _expand(luts_c, luts_s, [nf, nf, nf], runs, S, device, stream)
+
+
 def qwen_timestep_embedding(t: float, device="cuda", stream=None, on_host: bool = False):
     """fp32 [2, 256]: rows for t and for 0 (src/models/qwen_image/dit.cpp:220-230)."""
     if on_host:

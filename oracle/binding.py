@@ -283,6 +283,26 @@ def h3_positions(T, F_lat, H, W, A, anchors, use_reference=False):
     return pos
 
 
+def h3_ref2va_positions(T, refs, F_lat, H, W, A, use_reference=False):
+    """fp32 [S, 3] rotary positions of the reference-conditioned layout; refs: list of dicts
+    {kind: "image" | "video" | "audio", frames, h, w, audio}.  use_reference=True calls the reference's
+    own h3_build_ref2va_layout (oracle/_ref/libmx_ref_layout.so)."""
+    kinds = {"image": 0, "video": 1, "audio": 2}
+    n = len(refs)
+    kind = (C.c_int32 * max(n, 1))(*[kinds[r["kind"]] for r in refs])
+    arr = lambda key: (C.c_int64 * max(n, 1))(*[int(r.get(key, 0)) for r in refs])
+    fr, rh, rw, au = arr("frames"), arr("h"), arr("w"), arr("audio")
+    f = ref_layout().ref_h3_ref2va_positions if use_reference else oracle().or_h3_ref2va_positions
+    f.argtypes = [_I64, _I, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I64, _P]
+    f.restype = _I64
+    S = f(T, n, kind, fr, rh, rw, au, F_lat, H, W, A, None)
+    if S < 0:
+        raise RuntimeError("the reference rejected the layout")
+    pos = np.empty((S, 3), np.float32)
+    f(T, n, kind, fr, rh, rw, au, F_lat, H, W, A, _ptr(pos))
+    return pos
+
+
 def h3_rope_table(positions, inv_freq):
     S, nf = positions.shape[0], inv_freq.size
     cos, sin = np.empty((S, 3 * nf), np.float32), np.empty((S, 3 * nf), np.float32)

@@ -380,6 +380,68 @@ int64_t or_h3_positions(int64_t T, int64_t F_lat, int64_t H, int64_t W, int64_t 
   return S;
 }
 
+// src/models/minimax_h3/layout.cpp:121-188 (h3_build_ref2va_layout), positions only.
+// rows = T text | reference blocks in request order | 2A target audio | F_lat target video frames.
+// Reference i: kind[i] 0 image, 1 video, 2 audio; frames/h/w = latent geometry (image, video);
+// audio[i] = audio latents per channel (audio reference, or a video's sound track, whose rows come
+// before the video's rows and share its start time).  One shared clock starts at T; an image takes
+// one unit, an audio reference its length, a video the longer of its track and its frame spans.
+// positions may be null to query S.  Returns S.
+int64_t or_h3_ref2va_positions(int64_t T, int n_refs, const int32_t* kind, const int64_t* frames, const int64_t* rh,
+                               const int64_t* rw, const int64_t* audio, int64_t F_lat, int64_t H, int64_t W, int64_t A,
+                               float* positions) {
+  static const int per_latent[5] = {1, 4, 4, 4, 4};
+  const double rescale = 5.0 / 3.0;
+  std::vector<double> pos;  // t, h, w triples
+  auto push = [&](double t, double h, double w) { pos.push_back(t), pos.push_back(h), pos.push_back(w); };
+  for (int64_t i = 0; i < T; i++) push(double(i), 0, 0);
+  struct Grid {
+    std::vector<double> h, w;
+  };
+  auto grid = [&](int64_t gh, int64_t gw) {
+    const double sa = std::sqrt(double(gh * gw));
+    return Grid{spatial_grid(gh, sa), spatial_grid(gw, sa)};
+  };
+  auto video_rows = [&](const Grid& g, int64_t nf, double t0, bool image) {
+    double t = t0;
+    for (int64_t f = 0; f < nf; f++) {
+      for (double h : g.h)
+        for (double w : g.w) push(t, h, w);
+      if (!image) t += rescale * per_latent[f % 5];
+    }
+  };
+  auto audio_rows = [&](int64_t n, double t0, const Grid& g) {
+    for (int c = 0; c < 2; c++)
+      for (int64_t a = 0; a < n; a++) push(t0 + double(a), 0, c == 0 ? g.w.front() : g.w.back());
+  };
+  const Grid target = grid(H, W);
+  double clock = double(T);
+  for (int i = 0; i < n_refs; i++) {
+    if (kind[i] == 2) {
+      audio_rows(audio[i], clock, target);
+      clock += double(audio[i]);
+      continue;
+    }
+    const Grid g = grid(rh[i], rw[i]);
+    if (kind[i] == 0) {
+      video_rows(g, 1, clock, true);
+      clock += 1.0;
+      continue;
+    }
+    if (audio[i] > 0) audio_rows(audio[i], clock, g);
+    video_rows(g, frames[i], clock, false);
+    double span = 0;
+    for (int64_t f = 0; f < frames[i]; f++) span += rescale * per_latent[f % 5];
+    clock += std::max(double(audio[i]), span);
+  }
+  audio_rows(A, clock, target);
+  video_rows(target, F_lat, clock, false);
+  const int64_t S = int64_t(pos.size() / 3);
+  if (positions)
+    for (size_t i = 0; i < pos.size(); i++) positions[i] = float(pos[i]);
+  return S;
+}
+
 // src/models/minimax_h3/dit.cpp:254-262: entry [s, a*nf + j] = cosf/sinf(positions[s, a] * inv_freq[j]).
 void or_h3_rope_table(const float* positions, int64_t S, const float* inv_freq, int nf, float* hc, float* hs) {
   const int64_t half = 3 * int64_t(nf);

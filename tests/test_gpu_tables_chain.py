@@ -57,6 +57,26 @@ def test_h3_rope_table_bit_exact(mx, T, F_lat, Hh, W, A, anchors):
     assert np.array_equal(sin.cpu().numpy().view(np.uint32), rs.view(np.uint32))
 
 
+@pytest.mark.parametrize("name", ["mixed", "video_with_track", "no_text", "h3_480p_one_image"])
+def test_h3_ref2va_rope_table_bit_exact(mx, name):
+    """The reference-conditioned layout (src/models/minimax_h3/layout.cpp:121-188): table gathered on the GPU from
+    the host look-up tables == libm on the positions of the reference's own host code."""
+    import sys
+    from pathlib import Path
+    from miroxen_b200 import rope_tables
+    gold_dir = Path(__file__).resolve().parent / "golden"
+    sys.path.insert(0, str(gold_dir))
+    from make_h3_ref2va_positions import CASES
+    inv_freq = (1.0 / (10000.0 ** (np.arange(16, dtype=np.float64) * 2 / 32))).astype(np.float32)
+    cos, sin = rope_tables.h3_ref2va_rope_table(*CASES[name], inv_freq)
+    pos = np.load(gold_dir / "h3_ref2va_positions.npz")[name]
+    rc, rs = orc.h3_rope_table(pos, inv_freq)
+    torch.cuda.synchronize()
+    assert cos.shape == rc.shape
+    assert np.array_equal(cos.cpu().numpy().view(np.uint32), rc.view(np.uint32))
+    assert np.array_equal(sin.cpu().numpy().view(np.uint32), rs.view(np.uint32))
+
+
 def test_qwen_timestep_embedding_bit_exact(mx):
     from miroxen_b200 import rope_tables
     ts = [0.0, 0.5, 1.0, 0.999, 0.001, 0.123456, 0.7071] + [k / 1000.0 for k in range(0, 1000, 7)]
