@@ -42,6 +42,7 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the second chain and the per-op pass")
+    ap.add_argument("--e2e-chunk-rows", type=int, default=1024, help="rows per staged chunk of the end-to-end leg")
     ap.add_argument("--quant-only", action="store_true",
                     help="time only the block-scale quantiser on the block's activations (profiling aid; prints its own line)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
@@ -569,7 +570,7 @@ def main():
         # end to end: pinned host buffers in, results back in host memory, every step
         hb = BlockBuffers(w, rows, prefix_rows, seed=7, mods=mods, cos=cos, sin=sin, host=True)
         hb.args.fused = 1 if args.chain == "fused" else 0
-        pipe = mx.HostPipeline(1024, w.dim, w.F, w.H, w.D, w.rot, with_v=w.packed_qkv, act_mode=w.act_mode)
+        pipe = mx.HostPipeline(args.e2e_chunk_rows, w.dim, w.F, w.H, w.D, w.rot, with_v=w.packed_qkv, act_mode=w.act_mode)
         up = down = 0
         for _ in range(2):
             up, down = pipe.run(hb.args)
@@ -585,7 +586,7 @@ def main():
         line["e2e"] = {"value": round(job_bytes / dt / 1e9, 2), "unit": UNIT, "ms_per_step": round(dt * 1e3, 3),
                        "h2d_bytes_per_step": int(up) * (n_gpus if args.scaling == "weak" else 1),
                        "d2h_bytes_per_step": int(down) * (n_gpus if args.scaling == "weak" else 1), "steps": Ke,
-                       "api": "mxk_dit_block_ops_host (pinned host buffers, 1024-row chunks, 3 streams)"}
+                       "api": f"mxk_dit_block_ops_host (pinned host buffers, {args.e2e_chunk_rows}-row chunks, 3 streams)"}
         del hb
 
     if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:

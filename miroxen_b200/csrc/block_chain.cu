@@ -110,6 +110,10 @@ struct MxkOpTimes {
   int cap, used;
 };
 
+// Staging slots of the host pipeline: with three, the upload of chunk c + 2 never waits for the
+// download of chunk c (it reuses the slot of chunk c - 1, whose results left one chunk time earlier).
+constexpr int kHostSlots = 3;
+
 struct MxkHostPipeline {
   int64_t chunk_rows, dim, F, inner, half;
   int H, D, rot, with_v, act_mode;
@@ -121,7 +125,7 @@ struct MxkHostPipeline {
     mxk_bf16 *h1, *h2, *q_in, *k_in, *v_in, *q_out, *k_out, *v_out, *attn_o, *act, *act2, *mlp_o;
     float *cos, *sin;
     cudaEvent_t h2d_done, comp_done, d2h_done;
-  } slot[2];
+  } slot[kHostSlots];
 };
 
 extern "C" {
@@ -213,7 +217,7 @@ int mxk_host_pipeline_create(int64_t chunk_rows, int64_t dim, int64_t F, int H, 
   const int64_t bx = pad(R * dim * 4), bh = pad(R * dim * 2), bi = pad(R * p->inner * 2), bf = pad(R * F * 2),
                 bf2 = act_mode == 1 ? pad(R * 2 * F * 2) : 0, bt = pad(R * (p->half > 0 ? p->half : 1) * 4);
   const int64_t total = bx + 2 * bh /*h1 h2*/ + 2 * bh /*attn_o mlp_o*/ + (with_v ? 6 : 4) * bi + bf + bf2 + 2 * bt;
-  for (int i = 0; i < 2; i++) {
+  for (int i = 0; i < kHostSlots; i++) {
     MxkHostPipeline::Slot& s = p->slot[i];
     if ((e = cudaMalloc(reinterpret_cast<void**>(&s.base), size_t(total))) != cudaSuccess) return bail("cudaMalloc", e);
     char* c = s.base;
@@ -245,7 +249,7 @@ int mxk_host_pipeline_create(int64_t chunk_rows, int64_t dim, int64_t F, int H, 
 
 void mxk_host_pipeline_destroy(MxkHostPipeline* p) {
   if (!p) return;
-  for (int i = 0; i < 2; i++) {
+  for (int i = 0; i < kHostSlots; i++) {
     MxkHostPipeline::Slot& s = p->slot[i];
     if (s.base) cudaFree(s.base);
     if (s.h2d_done) cudaEventDestroy(s.h2d_done);
@@ -281,9 +285,9 @@ int mxk_dit_block_ops_host(MxkHostPipeline* p, const MxkBlockArgs* a, int64_t* h
   int64_t c = 0;
   for (int64_t r0 = 0; r0 < a->rows; r0 += p->chunk_rows, c++) {
     const int64_t n = a->rows - r0 < p->chunk_rows ? a->rows - r0 : p->chunk_rows;
-    MxkHostPipeline::Slot& s = p->slot[c & 1];
+    MxkHostPipeline::Slot& s = p->slot[c % kHostSlots];
     // upload (waits until the slot's previous results have left)
-    if (c >= 2) MXK_CU(cudaStreamWaitEvent(p->h2d, s.d2h_done, 0));
+    if (c >= kHostSlots) MXK_CU(cudaStreamWaitEvent(p->h2d, s.d2h_done, 0));
     auto in = [&](void* dst, const void* src, int64_t bytes) {
       up += bytes;
       return cudaMemcpyAsync(dst, src, size_t(bytes), cudaMemcpyHostToDevice, p->h2d);
@@ -291,6 +295,8 @@ int mxk_dit_block_ops_host(MxkHostPipeline* p, const MxkBlockArgs* a, int64_t* h
     auto in2d = [&](mxk_bf16* dst, const mxk_bf16* src, int64_t col0) {
       // gather [n, inner] out of a strided host array into a dense staging array
       up += n * inner * 2;
+      if (a->qkv_stride == inner)  // dense rows: one linear copy
+        return cudaMemcpyAsync(dst, src + r0 * inner + col0, size_t(n * inner) * 2, cudaMemcpyHostToDevice, p->h2d);
       return cudaMemcpy2DAsync(dst, size_t(inner) * 2, src + r0 * a->qkv_stride + col0, size_t(a->qkv_stride) * 2,
                                size_t(inner) * 2, size_t(n), cudaMemcpyHostToDevice, p->h2d);
     };
@@ -443,6 +449,8 @@ int mxk_dit_block_ops_host_static(const MxkBlockArgs* a, mxk_stream_t stream, in
     };
     auto in2d = [&](mxk_bf16* dst, const mxk_bf16* src, int64_t col0) {
       up += n * inner * 2;
+      if (a->qkv_stride == inner)
+        return cudaMemcpyAsync(dst, src + r0 * inner + col0, size_t(n * inner) * 2, cudaMemcpyHostToDevice, s);
       return cudaMemcpy2DAsync(dst, size_t(inner) * 2, src + r0 * a->qkv_stride + col0, size_t(a->qkv_stride) * 2,
                                size_t(inner) * 2, size_t(n), cudaMemcpyHostToDevice, s);
     };
