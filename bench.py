@@ -42,6 +42,8 @@ def parse():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the second chain and the per-op pass")
+    ap.add_argument("--shard", choices=["frames", "rows"], default="frames",
+                    help="strong scaling of a video workload: whole frames per rank (the reference's split) or equal row ranges")
     ap.add_argument("--e2e-chunk-rows", type=int, default=1024, help="rows per staged chunk of the end-to-end leg")
     ap.add_argument("--quant-only", action="store_true",
                     help="time only the block-scale quantiser on the block's activations (profiling aid; prints its own line)")
@@ -286,7 +288,7 @@ def main():
 
     # rows of this rank
     if args.scaling == "strong" and n_gpus > 1:
-        if w.frames:
+        if w.frames and args.shard == "frames":
             sh = sharding.shard_frames(w.frames, w.rows_per_frame, w.rows - w.frames * w.rows_per_frame, n_gpus, rank)
         else:
             sh = sharding.shard_rows(w.rows, n_gpus, rank)
@@ -495,7 +497,7 @@ def main():
         "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": w.name, "desc": w.desc, "rows_per_gpu": rows, "rows_total": total_rows, "dim": w.dim,
                    "heads": f"{w.H}x{w.D}", "F": w.F, "chain": args.chain, "io_dtype": "bf16 activations, fp32 residual",
-                   "bytes_per_row": w.bytes_per_row(), "parallelism": f"row-sharded x{n_gpus}, no collective in the loop",
+                   "bytes_per_row": w.bytes_per_row(), "parallelism": (f"row-sharded x{n_gpus}" + (f" ({args.shard if w.frames else 'rows'})" if args.scaling == "strong" and n_gpus > 1 else "") + ", no collective in the loop"),
                    "l2": f"{n_sets} alternating buffer sets, {sets[0].nbytes() / 1e6:.0f} MB each (> 126 MB L2)"},
         "frac_of_hbm_peak": round(value / n_gpus / peak_gbs, 4), "hbm_peak_gbs": peak_gbs, "hbm_peak_source": peak_src,
         "clocks": clocks, "gpu_launches": int(launches),

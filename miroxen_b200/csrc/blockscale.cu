@@ -123,15 +123,28 @@ struct RowPieces {
   int K, pieces_per_row, piece_elems;
   int64_t src1_off = 0;  // bytes from a piece to its second source (silu_mul's `up` half), 0 = none
   int stage_off = 0;     // where the second source sits inside a stage
-  // chunk < 2^31 (checked by the launcher): 32-bit arithmetic, and no division in the common case of
-  // one piece per row - this runs once per chunk in every consumer thread
+  // chunk / pieces_per_row for chunk < 2^31 as a multiply-high and a shift (set_pieces)
+  unsigned div_mul = 0, div_shift = 0;
+  // m = ceil(2^(31 + s) / d) with s = ceil(log2 d) fits 32 bits and gives floor(n / d) exactly for
+  // every n < 2^31 (the error term m d - 2^(31 + s) is below d <= 2^s).
+  void set_pieces(int ppr, int elems) {
+    pieces_per_row = ppr, piece_elems = elems;
+    if (ppr > 1) {
+      unsigned s = 0;
+      while ((1u << s) < unsigned(ppr)) s++;
+      const unsigned long long p = 1ull << (31 + s);
+      div_mul = unsigned((p + unsigned(ppr) - 1) / unsigned(ppr));
+      div_shift = s - 1;
+    }
+  }
+  // This runs once per chunk in every consumer thread, so: 32-bit arithmetic, no division.
   __device__ __forceinline__ void where(int64_t chunk, unsigned& row, int& k0, int& n) const {
     const unsigned c = unsigned(chunk);
     if (pieces_per_row == 1) {
       row = c, k0 = 0, n = K;
       return;
     }
-    row = c / unsigned(pieces_per_row);
+    row = __umulhi(c, div_mul) >> div_shift;
     k0 = int(c - row * unsigned(pieces_per_row)) * piece_elems;
     n = K - k0 < piece_elems ? K - k0 : piece_elems;
   }
@@ -311,7 +324,7 @@ static int run_act_quant(const mxk_bf16* in, int64_t rows, int64_t F, void* q, u
     return fail(MXK_ERR_TOO_LARGE, "act_quantize_mxfp8: %lld rows of %lld do not fit the pipeline's chunking", (long long)rows, (long long)F);
   QuantPipeOp<1, ACT> qo;
   qo.x = reinterpret_cast<const unsigned char*>(in), qo.ldx_bytes = F * (two ? 4 : 2), qo.K = int(F);
-  qo.pieces_per_row = int(ceil_div(F, piece_elems)), qo.piece_elems = piece_elems;
+  qo.set_pieces(int(ceil_div(F, piece_elems)), piece_elems);
   qo.src1_off = two ? F * 2 : 0, qo.stage_off = (piece_elems * 2 + 127) & ~127;
   qo.q = static_cast<uint8_t*>(q), qo.sf = sf, qo.amax = nullptr, qo.nkb_pad = int(pad_to(F / 32, 4));
   return run_stream_pipe("act_quantize_mxfp8", qo, rows * qo.pieces_per_row, piece_elems * 2, s, two ? 8 : 12, 3);
@@ -357,7 +370,9 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
   const bool small = !fp4 && rows * K * 2 < (int64_t(96) << 20);
   if (tune(TUNE_QUANT_PATH, small ? 2 : 1) == 1 && piece_elems * 2 <= chunk_bytes && rows * pieces < (int64_t(1) << 31)) {
     const int ppr = int(ceil_div(K, piece_elems));
-    RowPieces rp{reinterpret_cast<const unsigned char*>(x), ldx * 2, int(K), ppr, piece_elems};
+    RowPieces rp;
+    rp.x = reinterpret_cast<const unsigned char*>(x), rp.ldx_bytes = ldx * 2, rp.K = int(K);
+    rp.set_pieces(ppr, piece_elems);
     if (fp4) {
       AmaxPipeOp op;
       static_cast<RowPieces&>(op) = rp;
