@@ -229,6 +229,43 @@ def test_host_pipeline_equals_device_chain(mx, cfg):
     assert np.array_equal(td["x"].cpu().numpy(), th["x"].numpy())
 
 
+@pytest.mark.parametrize("cfg", BLOCKS[:2])
+@pytest.mark.parametrize("fused", [0, 1])
+def test_block_chain_captures_into_a_cuda_graph(mx, cfg, fused):
+    """The launchers allocate nothing and never synchronise, so a block's op sequence (with its programmatic
+    dependent launches and, in the quantiser, its memsets) can be captured once and replayed: the replay
+    writes the same bits as the eager call."""
+    rows = cfg[0]
+    n1, t1, a1 = make_block(mx, H.rng(rows + 31), *cfg)
+    n2, t2, a2 = make_block(mx, H.rng(rows + 31), *cfg)
+    a1.fused = a2.fused = fused
+    a1.chunk_rows = a2.chunk_rows = 0
+    mx.dit_block_ops(a1)          # eager; also the warm-up that resolves per-device caches
+    torch.cuda.synchronize()
+    x0 = t2["x"].clone()
+    act0 = t2["act"].clone() if cfg[6] == 0 else None
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        mx.dit_block_ops(a2)
+        qm = mx.ops.quantize_blockscaled(mx.ops.Q_NVFP4, t2["h1"], cfg[1], rows, cfg[1])
+    torch.cuda.synchronize()
+    for _ in range(2):              # replay from the same inputs twice
+        t2["x"].copy_(x0)
+        if act0 is not None:
+            t2["act"].copy_(act0)
+        graph.replay()
+        torch.cuda.synchronize()
+        for k in ("h1", "q_out", "k_out", "h2", "act"):
+            assert np.array_equal(H.bits(t1[k]), H.bits(t2[k])), k
+        assert torch.equal(t1["x"], t2["x"])
+        want = orc.quantize_blockscaled(2, H.bits(t2["h1"]))
+        assert np.array_equal(qm.q.cpu().numpy(), want[0]) and np.array_equal(qm.sf.cpu().numpy(), want[1])
+        assert float(qm.amax.item()) == want[2]
+    assert mx.device_error() == 0
+
+
 def test_bounded_wait_reports_and_context_survives(mx):
     """A wait that can never be satisfied (a barrier nothing completes) runs out of its budget, the
     kernel reports through the device error word and returns; the context keeps working."""
