@@ -43,6 +43,7 @@ namespace {
 
 constexpr float kFp4Range = 6.f * 448.f;  // src/kernels/blockscale.cu:33
 constexpr int kRowsInFlight = 4;
+constexpr int64_t kMaxQuantK = int64_t(1) << 24;  // keeps the register kernels' grid.y (K / 4096) inside 65535
 
 // Four float pairs -> eight e2m1 codes, element 0 in the lowest nibble.
 __device__ __forceinline__ uint32_t e2m1x8(float2 a, float2 b, float2 c, float2 d) {
@@ -343,8 +344,9 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
   if (mode != MXK_Q_MXFP8 && mode != MXK_Q_NVFP4)
     return fail(MXK_ERR_INVALID_ARG, "quantize_blockscaled: mode %d is not a quantised mode (1 MXFP8, 2 NVFP4)", mode);
   // the reference's own check (src/kernels/blockscale.cu:151)
-  if (K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldx < K || !aligned(x, 16) || K > (int64_t(1) << 30))
+  if (K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldx < K || !aligned(x, 16))
     return fail(MXK_ERR_INVALID_ARG, "quantize_blockscaled: need K %% 32 == 0, ldx %% 8 == 0, ldx >= K, 16-byte aligned input");
+  if (K > kMaxQuantK) return fail(MXK_ERR_TOO_LARGE, "quantize_blockscaled: K=%lld beyond %lld", (long long)K, (long long)kMaxQuantK);
   if (rows == 0) return MXK_OK;
   if (rows < 0 || !x || !q || !sf || (mode == MXK_Q_NVFP4 && !amax))
     return fail(MXK_ERR_INVALID_ARG, "quantize_blockscaled: null buffer or negative rows");
@@ -414,8 +416,9 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
 int mxk_act_quantize_mxfp8(int act_mode, const mxk_bf16* in, int64_t rows, int64_t F, void* q, uint8_t* sf,
                            mxk_stream_t stream) {
   if (act_mode < 0 || act_mode > 2) return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: act_mode %d (0 gelu tanh, 1 silu_mul, 2 gelu erf)", act_mode);
-  if (F <= 0 || F % 32 != 0 || F > (int64_t(1) << 30) || !aligned(in, 16))
+  if (F <= 0 || F % 32 != 0 || !aligned(in, 16))
     return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: need F %% 32 == 0 and a 16-byte aligned input");
+  if (F > kMaxQuantK) return fail(MXK_ERR_TOO_LARGE, "act_quantize_mxfp8: F=%lld beyond %lld", (long long)F, (long long)kMaxQuantK);
   if (rows == 0) return MXK_OK;
   if (rows < 0 || !in || !q || !sf) return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: null buffer or negative rows");
   if (!aligned(q, 16)) return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: q must be 16-byte aligned");
