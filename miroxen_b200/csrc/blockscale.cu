@@ -183,7 +183,6 @@ struct AmaxPipeOp : RowPieces {
 template <int MODE, int ACT = -1>
 struct QuantPipeOp : RowPieces {
   static constexpr int NSRC = ACT == ACT_SILU_MUL ? 2 : 1;
-  static constexpr int V = MODE == 2 ? 16 : 32, LPB = V / 8;
   uint8_t* q;
   uint8_t* sf;
   const float* amax;
