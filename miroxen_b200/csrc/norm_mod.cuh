@@ -345,6 +345,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
         float dx = v[k].x - mean, dy = v[k].y - mean, dz = v[k].z - mean, dw = v[k].w - mean;
         float q = (dx * dx + dy * dy) + (dz * dz + dw * dw);
         ss += (EXACT || MODE == 1 || on[k]) ? q : 0.f;
+        v[k] = make_float4(dx, dy, dz, dw);  // the centred row is what the epilogue scales
       }
       float total;
       if (MODE == 0) {
@@ -365,8 +366,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
       bf16* orow = a.out + row * a.dim;
 #pragma unroll
       for (int k = 0; k < VPT; k++) {
-        float o[4] = {(v[k].x - mean) * rstd, (v[k].y - mean) * rstd, (v[k].z - mean) * rstd,
-                      (v[k].w - mean) * rstd};
+        float o[4] = {v[k].x * rstd, v[k].y * rstd, v[k].z * rstd, v[k].w * rstd};
         if (HAS_W) o[0] *= W[k].x, o[1] *= W[k].y, o[2] *= W[k].z, o[3] *= W[k].w;
         o[0] = o[0] * A[k].x + B[k].x;
         o[1] = o[1] * A[k].y + B[k].y;
