@@ -487,6 +487,49 @@ def main():
                 e1.record(stream)
                 barrier()
                 pair[name] = round(e0.elapsed_time(e1) / K * 1e3, 2)
+            # bias add folded into the op that reads the GEMM output next, against add_bias_bf16 + the plain op
+            bias_f = torch.randn(2 * w.F, device="cuda") * 0.1
+            bias_d = torch.randn(w.dim, device="cuda") * 0.1
+
+            def fold(one, two, bytes_one):
+                t = {}
+                for name, fn in (("one_call", one), ("two_calls", two)):
+                    for i in range(3):
+                        fn(i)
+                    barrier()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record(stream)
+                    for i in range(K):
+                        fn(i)
+                    e1.record(stream)
+                    barrier()
+                    t[name] = round(e0.elapsed_time(e1) / K * 1e3, 2)
+                return {"us": t["one_call"], "us_two_calls": t["two_calls"], "bytes": int(bytes_one),
+                        "gbs": round(bytes_one / t["one_call"] / 1e3, 1), "frac": round(bytes_one / t["one_call"] / 1e3 / peak_gbs, 3)}
+
+            if w.act_mode == 0:
+                a_one = lambda i: mx.ops.bias_gelu_tanh_inplace(bsets[i % n_sets].act, bias_f, rows, w.F, stream)
+
+                def a_two(i):
+                    mx.ops.add_bias_bf16(bsets[i % n_sets].act, bias_f, rows, w.F, stream)
+                    mx.ops.gelu_tanh_inplace(bsets[i % n_sets].act, rows * w.F, stream)
+                act_bytes = 4 * rows * w.F
+            else:
+                a_one = lambda i: mx.ops.bias_silu_mul(bsets[i % n_sets].act2, bias_f, rows, w.F, bsets[i % n_sets].act, stream)
+
+                def a_two(i):
+                    mx.ops.add_bias_bf16(bsets[i % n_sets].act2, bias_f, rows, 2 * w.F, stream)
+                    mx.ops.silu_mul(bsets[i % n_sets].act2, rows, w.F, bsets[i % n_sets].act, stream)
+                act_bytes = 6 * rows * w.F
+            r_one = lambda i: mx.ops.gated_residual_bias(bsets[i % n_sets].x, bsets[i % n_sets].attn_o, bias_d, rows, w.dim,
+                                                         mod(bsets[i % n_sets], "gate1"), w.gate_tanh, stream)
+
+            def r_two(i):
+                b = bsets[i % n_sets]
+                mx.ops.add_bias_bf16(b.attn_o, bias_d, rows, w.dim, stream)
+                mx.ops.gated_residual(b.x, b.attn_o, rows, w.dim, mod(b, "gate1"), w.gate_tanh, stream)
+            res["bias_folding"] = {"act": dict(op="bias + " + ("gelu_tanh" if w.act_mode == 0 else "silu_mul"), **fold(a_one, a_two, act_bytes)),
+                                   "gated_residual": dict(op="bias + gated_residual", **fold(r_one, r_two, 10 * rows * w.dim))}
             by = (4 + 1 + 1 / 32) * rows * w.dim
             res["norm_mod_quant_mxfp8"] = {"norm": "layernorm" if w.norm_mode == 0 else "rmsnorm", "input": f"[{rows}, {w.dim}]",
                                            "us": pair["one_call"], "us_two_calls": pair["two_calls"], "bytes": int(by),

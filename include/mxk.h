@@ -375,6 +375,25 @@ int mxk_qwen_latent_decode(const float* x, float* y, int64_t n, const float* mea
 int mxk_h3_latent_video(const float* rows, float* z, int64_t frames, int64_t h, int64_t w, mxk_stream_t stream);
 int mxk_h3_latent_audio(const float* rows, float* z, int64_t samples, mxk_stream_t stream);
 
+/* ---- bias add folded into the op that follows it ----
+ *
+ * linear() adds a layer's bias with add_bias_bf16 right after the GEMM (src/core/weights.cpp:164-167), a
+ * read-modify-write of the whole output, and one of the ops above then reads that output again.  These take
+ * the bias instead (the caller skips its add_bias_bf16) and read the GEMM output once; (y + bias) is rounded
+ * to bf16 first, so the bits are those of mxk_add_bias_bf16 followed by the plain op.  A null bias gives the
+ * plain op.  Valid when nothing else touches the output between the bias add and the op (no LoRA branch
+ * accumulating into it).
+ *   mxk_bias_gelu_tanh_inplace: x[r, c] = gelu_tanh(bf16(x[r, c] + bias[c])), x bf16 [rows, F], bias fp32 [F].
+ *   mxk_bias_silu_mul: out[r, c] = silu(bf16(gu[r, c] + bias[c])) * bf16(gu[r, F + c] + bias[F + c]),
+ *                      gu bf16 [rows, 2F], bias fp32 [2F].
+ *   mxk_gated_residual_bias: x[r, :] += act(gate) * bf16(y[r, :] + bias), arguments as mxk_gated_residual.
+ * F % 8 == 0 (dim % 8 == 0, dim <= 8192) and 16-byte aligned buffers; other shapes return -1 and ask for the
+ * two calls. */
+int mxk_bias_gelu_tanh_inplace(mxk_bf16* x, const float* bias, int64_t rows, int64_t F, mxk_stream_t stream);
+int mxk_bias_silu_mul(const mxk_bf16* gu, const float* bias, int64_t rows, int64_t F, mxk_bf16* out, mxk_stream_t stream);
+int mxk_gated_residual_bias(float* x, const mxk_bf16* y, const float* bias, int64_t rows, int64_t dim, MxkRowMod gate,
+                            int gate_tanh, mxk_stream_t stream);
+
 /* Development knob: overrides a launch-shape default (see tuning.h for the names); value 0
  * restores the default.  Results do not depend on it. */
 int mxk_set_tuning(const char* name, int value);

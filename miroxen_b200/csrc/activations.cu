@@ -72,6 +72,64 @@ struct SiluPipeOp {
   __device__ uint4 apply(const uint4& g, const uint4& u) const { return act8<ACT_SILU_MUL>(g, u); }
 };
 
+// 8 bf16 plus 8 fp32 bias values, rounded back to bf16: what add_bias_bf16 leaves in memory
+// (src/kernels/ops.cu:249-262), so the activation sees the same bits as after the separate call.
+__device__ __forceinline__ uint4 add_bias8(const uint4& raw, const float* bias) {
+  float v[8];
+  unpack8(raw, v);
+  const float4 b0 = *reinterpret_cast<const float4*>(bias), b1 = *reinterpret_cast<const float4*>(bias + 4);
+  v[0] += b0.x, v[1] += b0.y, v[2] += b0.z, v[3] += b0.w, v[4] += b1.x, v[5] += b1.y, v[6] += b1.z, v[7] += b1.w;
+  return pack8(v);
+}
+
+// Bias add and activation in one pass: out[r, c] = act(bf16(in[r, c] + bias[c])) (GELU, in place), or
+// silu(bf16(gu[r, c] + bias[c])) * bf16(gu[r, F + c] + bias[F + c]).  Chunk = a piece of one row, so
+// the column of every vector is known; the bias vector is read through L1/L2.
+template <int ACT>
+struct BiasActPipeOp : RowPieces {
+  static constexpr int NSRC = ACT == ACT_SILU_MUL ? 2 : 1;
+  const float* bias;
+  unsigned char* out;
+  struct State {};
+  __device__ State init() const { return State{}; }
+  __device__ void consume(State&, int64_t chunk, const unsigned char* stage, int tid, int n_cons) const {
+    unsigned row;
+    int k0, n;
+    where(chunk, row, k0, n);
+    const uint4* s0 = reinterpret_cast<const uint4*>(stage);
+    const uint4* s1 = reinterpret_cast<const uint4*>(stage + stage_off);
+    uint4* dst = reinterpret_cast<uint4*>(out + (int64_t(row) * K + k0) * 2);
+    const int nvec = n >> 3;
+    for (int i = tid; i < nvec; i += n_cons) {
+      const uint4 g = add_bias8(s0[i], bias + k0 + 8 * i);
+      const uint4 u = NSRC == 2 ? add_bias8(s1[i], bias + K + k0 + 8 * i) : g;
+      st_stream(dst + i, act8<ACT>(g, u));
+    }
+  }
+  __device__ void finish(State&, int) const {}
+};
+
+template <int ACT>
+int run_bias_act(const char* name, const mxk_bf16* in, const float* bias, int64_t rows, int64_t F, mxk_bf16* out,
+                 cudaStream_t s) {
+  const bool two = ACT == ACT_SILU_MUL;
+  if (F <= 0 || F % 8 != 0 || F > (int64_t(1) << 24) || !aligned(in, 16) || !aligned(out, 16) || !aligned(bias, 16))
+    return fail(MXK_ERR_INVALID_ARG, "%s: needs F %% 8 == 0, F <= 2^24 and 16-byte aligned buffers; otherwise call "
+                "mxk_add_bias_bf16 and the activation separately", name);
+  int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 8) * 1024 / (two ? 2 : 1);
+  if (chunk_bytes > 32 * 1024) chunk_bytes = 32 * 1024;
+  const int pieces = int(ceil_div(F * 2, chunk_bytes));
+  const int piece_elems = int(ceil_div(ceil_div(F, pieces), 128) * 128);
+  if (piece_elems * 2 > chunk_bytes || rows * pieces >= (int64_t(1) << 31))
+    return fail(MXK_ERR_TOO_LARGE, "%s: %lld rows of %lld do not fit the pipeline's chunking", name, (long long)rows, (long long)F);
+  BiasActPipeOp<ACT> op;
+  op.x = reinterpret_cast<const unsigned char*>(in), op.ldx_bytes = F * (two ? 4 : 2), op.K = int(F);
+  op.set_pieces(int(ceil_div(F, piece_elems)), piece_elems);
+  op.src1_off = two ? F * 2 : 0, op.stage_off = (piece_elems * 2 + 127) & ~127;
+  op.bias = bias, op.out = reinterpret_cast<unsigned char*>(out);
+  return run_stream_pipe(name, op, rows * op.pieces_per_row, piece_elems * 2, s, two ? 4 : 8, two ? 2 : 3);
+}
+
 template <int KIND>
 int run_gelu(const char* name, mxk_bf16* x, int64_t n, cudaStream_t s) {
   bf16* xb = reinterpret_cast<bf16*>(x);
@@ -148,6 +206,20 @@ __global__ void __launch_bounds__(256)
 using namespace mxk;
 
 extern "C" {
+
+int mxk_bias_gelu_tanh_inplace(mxk_bf16* x, const float* bias, int64_t rows, int64_t F, mxk_stream_t stream) {
+  if (rows <= 0 || F <= 0) return MXK_OK;
+  if (!x) return fail(MXK_ERR_INVALID_ARG, "bias_gelu_tanh_inplace: null x");
+  if (!bias) return mxk_gelu_tanh_inplace(x, rows * F, stream);
+  return run_bias_act<ACT_GELU_TANH>("bias_gelu_tanh_inplace", x, bias, rows, F, x, as_stream(stream));
+}
+
+int mxk_bias_silu_mul(const mxk_bf16* gu, const float* bias, int64_t rows, int64_t F, mxk_bf16* out, mxk_stream_t stream) {
+  if (rows <= 0 || F <= 0) return MXK_OK;
+  if (!gu || !out) return fail(MXK_ERR_INVALID_ARG, "bias_silu_mul: null gu or out");
+  if (!bias) return mxk_silu_mul(gu, rows, F, out, stream);
+  return run_bias_act<ACT_SILU_MUL>("bias_silu_mul", gu, bias, rows, F, out, as_stream(stream));
+}
 
 int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk_stream_t stream) {
   if (rows <= 0 || F <= 0) return MXK_OK;

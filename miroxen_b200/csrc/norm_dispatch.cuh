@@ -37,11 +37,11 @@ inline unsigned norm_grid(NormArgs& a, int per_sm) {
 
 constexpr int kNormMaxStages = 8;
 
-template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool EXACT, bool QUANT = false>
+template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool EXACT, bool QUANT = false, bool YBIAS = false>
 inline void launch_norm_inst(const NormPlan& p, NormArgs a, bool tma, cudaStream_t s) {
   if (tma) {
     a.err = device_error_word();
-    auto k = norm_rows_tma_kernel<MODE, TIN, VPT, HAS_W, FUSE_RES, EXACT, QUANT>;
+    auto k = norm_rows_tma_kernel<MODE, TIN, VPT, HAS_W, FUSE_RES, EXACT, QUANT, YBIAS>;
     const int xb = (a.dim * int(sizeof(TIN)) + 127) & ~127;
     const int stage_bytes = xb + (FUSE_RES ? ((a.dim * 2 + 127) & ~127) : 0);
     int stages = tune(TUNE_NORM_STAGES, 0);
@@ -57,30 +57,30 @@ inline void launch_norm_inst(const NormPlan& p, NormArgs a, bool tma, cudaStream
     const unsigned grid = norm_grid(a, tune(TUNE_NORM_CTAS_PER_SM, resident_ctas(k, p.threads, smem)));
     a.row_step = tune(TUNE_NORM_INTERLEAVE, 1) == 1 ? int64_t(grid) : 1;
     launch_pdl(k, dim3(grid), dim3(p.threads), smem, s, a, stages, stage_bytes);
-  } else if constexpr (!QUANT) {  // the quantising form exists for the bulk-copy kernel only
+  } else if constexpr (!QUANT && !YBIAS) {  // the quantising and bias forms exist for the bulk-copy kernel only
     auto k = norm_rows_kernel<MODE, TIN, VPT, HAS_W, FUSE_RES, EXACT>;
     const unsigned grid = norm_grid(a, tune(TUNE_NORM_CTAS_PER_SM, resident_ctas(k, p.threads)));
     launch_pdl(k, dim3(grid), dim3(p.threads), 0, s, a);
   }
 }
 
-template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool QUANT = false>
+template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool QUANT = false, bool YBIAS = false>
 inline void launch_norm_vpt(const NormPlan& p, const NormArgs& a, bool tma, cudaStream_t s) {
-  if (p.exact) launch_norm_inst<MODE, TIN, VPT, HAS_W, FUSE_RES, true, QUANT>(p, a, tma, s);
-  else launch_norm_inst<MODE, TIN, VPT, HAS_W, FUSE_RES, false, QUANT>(p, a, tma, s);
+  if (p.exact) launch_norm_inst<MODE, TIN, VPT, HAS_W, FUSE_RES, true, QUANT, YBIAS>(p, a, tma, s);
+  else launch_norm_inst<MODE, TIN, VPT, HAS_W, FUSE_RES, false, QUANT, YBIAS>(p, a, tma, s);
 }
 
-template <int MODE, class TIN, bool HAS_W, bool FUSE_RES, bool QUANT = false>
+template <int MODE, class TIN, bool HAS_W, bool FUSE_RES, bool QUANT = false, bool YBIAS = false>
 inline void launch_norm(const NormPlan& p, const NormArgs& a, bool tma, cudaStream_t s) {
   switch (p.vpt) {
-    case 1: launch_norm_vpt<MODE, TIN, 1, HAS_W, FUSE_RES, QUANT>(p, a, tma, s); break;
-    case 2: launch_norm_vpt<MODE, TIN, 2, HAS_W, FUSE_RES, QUANT>(p, a, tma, s); break;
-    case 3: launch_norm_vpt<MODE, TIN, 3, HAS_W, FUSE_RES, QUANT>(p, a, tma, s); break;
-    case 4: launch_norm_vpt<MODE, TIN, 4, HAS_W, FUSE_RES, QUANT>(p, a, tma, s); break;
-    case 5: launch_norm_vpt<MODE, TIN, 5, HAS_W, FUSE_RES, QUANT>(p, a, tma, s); break;
-    case 6: launch_norm_vpt<MODE, TIN, 6, HAS_W, FUSE_RES, QUANT>(p, a, tma, s); break;
-    case 7: launch_norm_vpt<MODE, TIN, 7, HAS_W, FUSE_RES, QUANT>(p, a, tma, s); break;
-    default: launch_norm_vpt<MODE, TIN, 8, HAS_W, FUSE_RES, QUANT>(p, a, tma, s); break;
+    case 1: launch_norm_vpt<MODE, TIN, 1, HAS_W, FUSE_RES, QUANT, YBIAS>(p, a, tma, s); break;
+    case 2: launch_norm_vpt<MODE, TIN, 2, HAS_W, FUSE_RES, QUANT, YBIAS>(p, a, tma, s); break;
+    case 3: launch_norm_vpt<MODE, TIN, 3, HAS_W, FUSE_RES, QUANT, YBIAS>(p, a, tma, s); break;
+    case 4: launch_norm_vpt<MODE, TIN, 4, HAS_W, FUSE_RES, QUANT, YBIAS>(p, a, tma, s); break;
+    case 5: launch_norm_vpt<MODE, TIN, 5, HAS_W, FUSE_RES, QUANT, YBIAS>(p, a, tma, s); break;
+    case 6: launch_norm_vpt<MODE, TIN, 6, HAS_W, FUSE_RES, QUANT, YBIAS>(p, a, tma, s); break;
+    case 7: launch_norm_vpt<MODE, TIN, 7, HAS_W, FUSE_RES, QUANT, YBIAS>(p, a, tma, s); break;
+    default: launch_norm_vpt<MODE, TIN, 8, HAS_W, FUSE_RES, QUANT, YBIAS>(p, a, tma, s); break;
   }
 }
 

@@ -35,6 +35,7 @@ struct NormArgs {
   bf16* out;
   int rows_per_cta;
   int64_t row_step;  // bulk-copy kernel: 1 = contiguous row range per CTA, gridDim.x = interleaved rows
+  const float* ybias;  // YBIAS kernels: fp32 [dim] added to y (and rounded to bf16) before the residual update
   int* err;  // device error word (bounded waits report here)
   // MXFP8 output instead of bf16 (QUANT kernels): e4m3 codes [rows, dim], interleaved ue8m0 scales
   uint8_t* q;
@@ -215,7 +216,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
 // barrier vote, records kErrBulkTimeout in the device's error word, drains the copies it still has in
 // flight (bounded again) and returns.
 
-template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool EXACT, bool QUANT = false>
+template <int MODE, class TIN, int VPT, bool HAS_W, bool FUSE_RES, bool EXACT, bool QUANT = false, bool YBIAS = false>
 __global__ void __launch_bounds__(norm_max_threads(VPT))
     norm_rows_tma_kernel(const NormArgs a, const int stages, const int stage_bytes) {
   using raw_t = typename Raw4<TIN>::type;
@@ -256,12 +257,14 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
 #pragma unroll
   for (int k = 0; k < VPT; k++) on[k] = EXACT || (k * T + tid < a.nvec);
 
-  float4 A[VPT], B[VPT], W[HAS_W ? VPT : 1], G[FUSE_RES ? VPT : 1];
+  float4 A[VPT], B[VPT], W[HAS_W ? VPT : 1], G[FUSE_RES ? VPT : 1], YB[YBIAS ? VPT : 1];
   int cur_set = -1;
 #pragma unroll
   for (int k = 0; k < VPT; k++) {
     if (HAS_W) W[k] = on[k] ? *reinterpret_cast<const float4*>(a.w + 4 * (k * T + tid))
                             : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (YBIAS) YB[k] = on[k] ? *reinterpret_cast<const float4*>(a.ybias + 4 * (k * T + tid))
+                             : make_float4(0.f, 0.f, 0.f, 0.f);
   }
 
   int st = 0;
@@ -313,6 +316,11 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
       for (int k = 0; k < VPT; k++) {
         float4 yv = make_float4(0.f, 0.f, 0.f, 0.f);
         if (on[k] && arrived) yv = widen(reinterpret_cast<const uint2*>(sx + yoff)[k * T + tid]);
+        if (YBIAS) {
+          // y + bias rounded to bf16, as add_bias_bf16 leaves it (src/kernels/ops.cu:249-262)
+          const float t[4] = {yv.x + YB[k].x, yv.y + YB[k].y, yv.z + YB[k].z, yv.w + YB[k].w};
+          yv = widen(pack4(t));
+        }
         v[k].x = fmaf(yv.x, G[k].x, v[k].x);
         v[k].y = fmaf(yv.y, G[k].y, v[k].y);
         v[k].z = fmaf(yv.z, G[k].z, v[k].z);

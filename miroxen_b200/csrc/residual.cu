@@ -166,6 +166,26 @@ int mxk_gated_residual(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, M
   return after_launch("gated_residual");
 }
 
+int mxk_gated_residual_bias(float* x, const mxk_bf16* y, const float* bias, int64_t rows, int64_t dim, MxkRowMod gate,
+                            int gate_tanh, mxk_stream_t stream) {
+  if (!bias) return mxk_gated_residual(x, y, rows, dim, gate, gate_tanh, stream);
+  if (rows <= 0) return MXK_OK;
+  if (!x || !y) return fail(MXK_ERR_INVALID_ARG, "gated_residual_bias: null x or y");
+  if (gate.target && !gate.prefix && gate.prefix_len > 0)
+    return fail(MXK_ERR_INVALID_ARG, "gated_residual_bias: prefix_len > 0 with a null prefix vector");
+  const bool gate_ok = (!gate.target || aligned(gate.target, 16)) && (!gate.prefix || aligned(gate.prefix, 16));
+  NormArgs a{};
+  a.x = x, a.xw = x, a.y = reinterpret_cast<const bf16*>(y), a.ybias = bias, a.gate = gate, a.gate_tanh = gate_tanh;
+  a.rows = rows, a.dim = int(dim), a.nvec = int(dim / 4);
+  NormPlan p;
+  if (dim <= 0 || dim % 8 != 0 || dim > 8192 || !aligned(x, 16) || !aligned(y, 16) || !aligned(bias, 16) || !gate_ok ||
+      !plan_norm(a.nvec, rows, p, 256))
+    return fail(MXK_ERR_INVALID_ARG, "gated_residual_bias: dim %lld or an unaligned vector is outside the one-pass kernel; "
+                "call mxk_add_bias_bf16 and mxk_gated_residual", (long long)dim);
+  launch_norm<2, float, false, true, false, true>(p, a, true, as_stream(stream));
+  return after_launch("gated_residual_bias");
+}
+
 int mxk_gated_residual_norm(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, MxkRowMod gate,
                             int gate_tanh, int norm_mode, float eps, const float* w,
                             MxkRowMod scale, MxkRowMod shift, mxk_bf16* out, mxk_stream_t stream) {

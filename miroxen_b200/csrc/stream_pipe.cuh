@@ -34,6 +34,48 @@ struct Chunk {
   unsigned bytes;  // per source and of the destination; multiple of 16
 };
 
+// Chunking of a [rows, K] bf16 matrix for ops that need to know the column of what they process: a
+// chunk is one piece (pieces_per_row of them, whole multiples of 128 elements) of one row.
+struct RowPieces {
+  const unsigned char* x;
+  int64_t ldx_bytes;
+  int K, pieces_per_row, piece_elems;
+  int64_t src1_off = 0;  // bytes from a piece to its second source (silu_mul's `up` half), 0 = none
+  int stage_off = 0;     // where the second source sits inside a stage
+  // chunk / pieces_per_row for chunk < 2^31 as a multiply-high and a shift (set_pieces)
+  unsigned div_mul = 0, div_shift = 0;
+  // m = ceil(2^(31 + s) / d) with s = ceil(log2 d) fits 32 bits and gives floor(n / d) exactly for
+  // every n < 2^31 (the error term m d - 2^(31 + s) is below d <= 2^s).
+  void set_pieces(int ppr, int elems) {
+    pieces_per_row = ppr, piece_elems = elems;
+    if (ppr > 1) {
+      unsigned s = 0;
+      while ((1u << s) < unsigned(ppr)) s++;
+      const unsigned long long p = 1ull << (31 + s);
+      div_mul = unsigned((p + unsigned(ppr) - 1) / unsigned(ppr));
+      div_shift = s - 1;
+    }
+  }
+  // This runs once per chunk in every consumer thread, so: 32-bit arithmetic, no division.
+  __device__ __forceinline__ void where(int64_t chunk, unsigned& row, int& k0, int& n) const {
+    const unsigned c = unsigned(chunk);
+    if (pieces_per_row == 1) {
+      row = c, k0 = 0, n = K;
+      return;
+    }
+    row = __umulhi(c, div_mul) >> div_shift;
+    k0 = int(c - row * unsigned(pieces_per_row)) * piece_elems;
+    n = K - k0 < piece_elems ? K - k0 : piece_elems;
+  }
+  __device__ void locate(int64_t chunk, Chunk& c) const {
+    unsigned row;
+    int k0, n;
+    where(chunk, row, k0, n);
+    c.src0 = x + row * ldx_bytes + int64_t(k0) * 2, c.src1 = c.src0 + src1_off, c.dst = nullptr;
+    c.bytes = unsigned(n) * 2;
+  }
+};
+
 template <class Op, class = void>
 struct consumes_itself : std::false_type {};
 template <class Op>

@@ -28,6 +28,7 @@ __all__ = [
     "Q_MXFP8", "Q_NVFP4", "QMat", "qdata_bytes", "qscale_bytes", "quantize_blockscaled", "act_quantize_mxfp8",
     "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8",
     "qwen_latent_encode", "qwen_latent_decode", "h3_latent_video", "h3_latent_audio",
+    "bias_gelu_tanh_inplace", "bias_silu_mul", "gated_residual_bias",
 ]
 
 
@@ -274,6 +275,21 @@ def rmsnorm_mod_quant_mxfp8(x, rows, dim, eps, w, scale: RowMod, shift: RowMod, 
     check(lib().mxk_rmsnorm_mod_quant_mxfp8(_p(x), rows, dim, eps, _p(w), scale or _NONE, shift or _NONE, _p(out.q), _p(out.sf),
                                             _stream(stream)))
     return out
+
+
+def bias_gelu_tanh_inplace(x, bias, rows, F, stream=None):
+    """add_bias_bf16 (src/kernels/ops.h:53) + gelu_tanh_inplace (ops.h:46) in one pass over x [rows, F]."""
+    check(lib().mxk_bias_gelu_tanh_inplace(_p(x), _p(bias), rows, F, _stream(stream)))
+
+
+def bias_silu_mul(gu, bias, rows, F, out, stream=None):
+    """add_bias_bf16 on gu [rows, 2F] + silu_mul (ops.h:44) in one pass."""
+    check(lib().mxk_bias_silu_mul(_p(gu), _p(bias), rows, F, _p(out), _stream(stream)))
+
+
+def gated_residual_bias(x, y, bias, rows, dim, gate: RowMod, gate_tanh, stream=None):
+    """add_bias_bf16 on y + gated_residual (ops.h:27) in one pass."""
+    check(lib().mxk_gated_residual_bias(_p(x), _p(y), _p(bias), rows, dim, gate or _NONE, int(gate_tanh), _stream(stream)))
 
 
 def qwen_latent_encode(x, y, n, mean, std, stream=None):
