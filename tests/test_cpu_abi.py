@@ -102,7 +102,7 @@ def test_host_builders_match_oracle(L):
 
 
 def test_cpp_shim_compiles_and_links(tmp_path, L):
-    """include/mx_ops.h (the reference's namespace mx signatures over the C ABI) builds with g++ against
+    """include/mx_ops.h and include/mx_latent.h (the reference's namespace mx signatures over the C ABI) build with g++ against
     libmxk and reports a bad argument as std::runtime_error, like the reference's MX_CHECK."""
     import shutil
     if not shutil.which("g++") or not Path("/usr/local/cuda/include/cuda_runtime.h").exists():
@@ -112,7 +112,19 @@ def test_cpp_shim_compiles_and_links(tmp_path, L):
 #include <cstdio>
 #include <cstring>
 #include "mx_ops.h"
+#include "mx_latent.h"
 int main() {
+  try {  // the reference's own negative test (tests/h3_latent_test.cpp:69-71)
+    mx::h3_latent::video(nullptr, nullptr, 1, 3, 2, nullptr);
+    return 3;
+  } catch (const std::runtime_error& e) {
+    if (!std::strstr(e.what(), "h3_latent_video")) return 4;
+  }
+  try {
+    mx::qwen_latent::encode(nullptr, nullptr, 0, nullptr, nullptr, nullptr);
+    return 5;
+  } catch (const std::runtime_error&) {
+  }
   mx::layernorm_mod(nullptr, 0, 3072, 1e-6f, mx::RowMod{}, mx::RowMod{}, nullptr, nullptr);   // rows == 0: no-op
   mx::gated_residual(nullptr, nullptr, -1, 3072, mx::RowMod{}, 1, nullptr);
   try {
