@@ -71,6 +71,7 @@ PROTOTYPES = {
     "mxk_h3_latent_audio": (_I, [_P, _P, _I64, _P]),
     "mxk_layernorm_mod_quant_mxfp8": (_I, [_P, _I64, _I64, _F, RowMod, RowMod, _P, _P, _P]),
     "mxk_rmsnorm_mod_quant_mxfp8": (_I, [_P, _I64, _I64, _F, _P, RowMod, RowMod, _P, _P, _P]),
+    "mxk_gated_residual_norm_quant_mxfp8": (_I, [_P, _P, _I64, _I64, RowMod, _I, _I, _F, _P, RowMod, RowMod, _P, _P, _P]),
     "mxk_layernorm_mod": (_I, [_P, _I64, _I64, _F, RowMod, RowMod, _P, _P]),
     "mxk_rmsnorm_mod": (_I, [_P, _I64, _I64, _F, _P, RowMod, RowMod, _P, _P]),
     "mxk_rmsnorm_bf16": (_I, [_P, _I64, _I64, _F, _P, _P, _P]),

@@ -26,7 +26,7 @@ __all__ = [
     "axpby_f32", "gated_residual_norm", "qkv_norm_rope", "HeadSpec", "dit_block_ops", "BlockArgs", "RowMod",
     "HostPipeline", "OpTimes", "dit_block_ops_host_static", "device_error", "launch_count", "reset_launch_count", "set_tuning",
     "Q_MXFP8", "Q_NVFP4", "QMat", "qdata_bytes", "qscale_bytes", "quantize_blockscaled", "act_quantize_mxfp8",
-    "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8",
+    "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8", "gated_residual_norm_quant_mxfp8",
     "qwen_latent_encode", "qwen_latent_decode", "h3_latent_video", "h3_latent_audio",
     "bias_gelu_tanh_inplace", "bias_silu_mul", "gated_residual_bias",
 ]
@@ -310,6 +310,15 @@ def h3_latent_video(rows, z, frames, h, w, stream=None):
 def h3_latent_audio(rows, z, samples, stream=None):
     """mx::h3_latent::audio (src/kernels/h3_latent.h:7)."""
     check(lib().mxk_h3_latent_audio(_p(rows), _p(z), samples, _stream(stream)))
+
+
+def gated_residual_norm_quant_mxfp8(x, y, rows, dim, gate: RowMod, gate_tanh, norm_mode, eps, w, scale: RowMod, shift: RowMod,
+                                    out: Optional[QMat] = None, stream=None) -> QMat:
+    """gated_residual, the norm and its MXFP8 quantisation in one pass (x updated in place)."""
+    out = _qmat_for(x, rows, dim, out)
+    check(lib().mxk_gated_residual_norm_quant_mxfp8(_p(x), _p(y), rows, dim, gate or _NONE, int(gate_tanh), int(norm_mode), eps,
+                                                    _p(w), scale or _NONE, shift or _NONE, _p(out.q), _p(out.sf), _stream(stream)))
+    return out
 
 
 def device_error(clear: bool = True) -> int:

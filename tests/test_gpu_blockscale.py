@@ -302,3 +302,28 @@ def test_norm_quantize_argument_errors(mx):
         mx.ops.rmsnorm_mod_quant_mxfp8(x, 4, 64, 1e-6, None, none, none, mx.ops.QMat(out.q, None))
     mx.ops.rmsnorm_mod_quant_mxfp8(x, 0, 64, 1e-6, None, none, none, out)
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("norm_mode", [0, 1])
+@pytest.mark.parametrize("rows,dim,plen,tanh", [(1, 32, 0, 1), (7, 96, 3, 0), (130, 3072, 41, 1), (300, 5120, 0, 0), (1200, 3072, 256, 1),
+                                                (64, 8192, 64, 0)])
+def test_residual_norm_quantize_equals_the_two_calls(mx, norm_mode, rows, dim, plen, tanh):
+    g = H.rng(rows * 5 + dim + norm_mode)
+    x, ybits = H.normal_f32(g, (rows, dim), 1.3), H.normal_bf16(g, (rows, dim), 1.0)
+    vecs = [H.to_dev(torch, H.normal_f32(g, dim, 0.3)) for _ in range(6)]
+    w = H.to_dev(torch, H.normal_f32(g, dim, 0.1, 1.0)) if norm_mode == 1 else None
+    gate, sc, sh = mx.row_mod(vecs[0], vecs[1], plen), mx.row_mod(vecs[2], vecs[3], plen), mx.row_mod(vecs[4], vecs[5], plen)
+    x2, y = H.to_dev(torch, x), H.to_dev(torch, ybits)
+    bf = torch.empty(rows, dim, dtype=torch.bfloat16, device="cuda")
+    mx.ops.gated_residual_norm(x2, y, rows, dim, gate, tanh, norm_mode, 1e-6, w, sc, sh, bf)
+    two = mx.ops.quantize_blockscaled(1, bf, dim, rows, dim)
+    x1 = H.to_dev(torch, x)
+    q = H.Guarded(torch, (rows * dim,), torch.uint8)
+    sf = H.Guarded(torch, (mx.ops.qscale_bytes(1, rows, dim),), torch.uint8)
+    sf.t.fill_(0x5A)
+    mx.ops.gated_residual_norm_quant_mxfp8(x1, y, rows, dim, gate, tanh, norm_mode, 1e-6, w, sc, sh, mx.ops.QMat(q.t, sf.t))
+    torch.cuda.synchronize()
+    q.check("q")
+    sf.check("sf")
+    assert torch.equal(x1, x2), "residual stream differs from the two calls"
+    assert torch.equal(sf.t, two.sf) and torch.equal(q.t, two.q)
