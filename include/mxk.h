@@ -344,9 +344,11 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
  * mxk_gelu_erf_inplace / mxk_silu_mul followed by mxk_quantize_blockscaled.
  *   act_mode 0: gelu (tanh form) of in [rows, F];  1: silu(in[:, :F]) * in[:, F:] with in [rows, 2F];
  *            2: gelu (erf form) of in [rows, F].
- * F % 32 == 0, in and q 16-byte aligned.  NVFP4 has no such form: its first block cannot be scaled before
+ * bias (nullable): fp32 [F] ([2F] for act_mode 1) that linear() would have added with add_bias_bf16 right after the
+ * GEMM (src/core/weights.cpp:164-167); in + bias is rounded to bf16 first, so the bits are those of the three calls.
+ * F % 32 == 0, in, bias and q 16-byte aligned.  NVFP4 has no such form: its first block cannot be scaled before
  * the maximum of the whole activation is known. */
-int mxk_act_quantize_mxfp8(int act_mode, const mxk_bf16* in, int64_t rows, int64_t F, void* q, uint8_t* sf,
+int mxk_act_quantize_mxfp8(int act_mode, const mxk_bf16* in, const float* bias, int64_t rows, int64_t F, void* q, uint8_t* sf,
                            mxk_stream_t stream);
 
 /* Norm, modulation and MXFP8 quantisation in one pass, for a normed activation whose only readers are

@@ -30,6 +30,16 @@ __device__ __forceinline__ float silu_f(float g) {
   return g * rcp_approx(1.f + ex2_approx(g * -1.4426950408889634f));
 }
 
+// 8 bf16 plus 8 fp32 bias values, rounded back to bf16: what add_bias_bf16 leaves in memory
+// (src/kernels/ops.cu:249-262), so the activation sees the same bits as after the separate call.
+__device__ __forceinline__ uint4 add_bias8(const uint4& raw, const float* bias) {
+  float v[8];
+  unpack8(raw, v);
+  const float4 b0 = *reinterpret_cast<const float4*>(bias), b1 = *reinterpret_cast<const float4*>(bias + 4);
+  v[0] += b0.x, v[1] += b0.y, v[2] += b0.z, v[3] += b0.w, v[4] += b1.x, v[5] += b1.y, v[6] += b1.z, v[7] += b1.w;
+  return pack8(v);
+}
+
 // Eight elements at a time on packed bf16.  ACT 0: GELU (tanh form) of a; 1: GELU (erf form) of a;
 // 2: silu(a) * b.  The result is rounded to bf16 exactly as the stand-alone kernels round it.
 enum { ACT_GELU_TANH = 0, ACT_GELU_ERF = 1, ACT_SILU_MUL = 2 };

@@ -72,16 +72,6 @@ struct SiluPipeOp {
   __device__ uint4 apply(const uint4& g, const uint4& u) const { return act8<ACT_SILU_MUL>(g, u); }
 };
 
-// 8 bf16 plus 8 fp32 bias values, rounded back to bf16: what add_bias_bf16 leaves in memory
-// (src/kernels/ops.cu:249-262), so the activation sees the same bits as after the separate call.
-__device__ __forceinline__ uint4 add_bias8(const uint4& raw, const float* bias) {
-  float v[8];
-  unpack8(raw, v);
-  const float4 b0 = *reinterpret_cast<const float4*>(bias), b1 = *reinterpret_cast<const float4*>(bias + 4);
-  v[0] += b0.x, v[1] += b0.y, v[2] += b0.z, v[3] += b0.w, v[4] += b1.x, v[5] += b1.y, v[6] += b1.z, v[7] += b1.w;
-  return pack8(v);
-}
-
 // Bias add and activation in one pass: out[r, c] = act(bf16(in[r, c] + bias[c])) (GELU, in place), or
 // silu(bf16(gu[r, c] + bias[c])) * bf16(gu[r, F + c] + bias[F + c]).  Chunk = a piece of one row, so
 // the column of every vector is known; the bias vector is read through L1/L2.

@@ -147,6 +147,7 @@ struct QuantPipeOp : RowPieces {
   uint8_t* sf;
   const float* amax;
   int nkb_pad;
+  const float* bias = nullptr;  // ACT >= 0: fp32 [K] (or [2K], gate then up) added and rounded to bf16 first
   using State = Fp4Scale;
   __device__ State init() const { return MODE == 2 ? fp4_scale(amax) : Fp4Scale{1.f, 1.f}; }
   __device__ void consume(State& fs, int64_t chunk, const unsigned char* stage, int tid, int n_cons) const {
@@ -163,8 +164,15 @@ struct QuantPipeOp : RowPieces {
       uint4 raw[2] = {s[2 * ic], s[2 * ic + 1]};
       if (ACT >= 0) {
         const uint4* s2 = reinterpret_cast<const uint4*>(stage + stage_off);
-        raw[0] = act8<ACT>(raw[0], NSRC == 2 ? s2[2 * ic] : raw[0]);
-        raw[1] = act8<ACT>(raw[1], NSRC == 2 ? s2[2 * ic + 1] : raw[1]);
+        uint4 up[2] = {raw[0], raw[1]};
+        if (NSRC == 2) up[0] = s2[2 * ic], up[1] = s2[2 * ic + 1];
+        if (bias) {
+          const float* bp = bias + k0 + 16 * ic;
+          raw[0] = add_bias8(raw[0], bp), raw[1] = add_bias8(raw[1], bp + 8);
+          if (NSRC == 2) up[0] = add_bias8(up[0], bp + K), up[1] = add_bias8(up[1], bp + K + 8);
+        }
+        raw[0] = act8<ACT>(raw[0], up[0]);
+        raw[1] = act8<ACT>(raw[1], up[1]);
       }
       uint4 out;
       const uint8_t sbyte = quant16<MODE>(raw, block_absmax<MODE>(raw), fs, out);
@@ -273,7 +281,7 @@ static int clear_scale_padding(int mode, int64_t rows, int64_t K, uint8_t* sf, c
 using namespace mxk;
 
 template <int ACT>
-static int run_act_quant(const mxk_bf16* in, int64_t rows, int64_t F, void* q, uint8_t* sf, cudaStream_t s) {
+static int run_act_quant(const mxk_bf16* in, const float* bias, int64_t rows, int64_t F, void* q, uint8_t* sf, cudaStream_t s) {
   const bool two = ACT == ACT_SILU_MUL;
   // two sources share a stage: half the chunk each
   int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 16) * 1024 / (two ? 2 : 1);
@@ -286,7 +294,7 @@ static int run_act_quant(const mxk_bf16* in, int64_t rows, int64_t F, void* q, u
   qo.x = reinterpret_cast<const unsigned char*>(in), qo.ldx_bytes = F * (two ? 4 : 2), qo.K = int(F);
   qo.set_pieces(int(ceil_div(F, piece_elems)), piece_elems);
   qo.src1_off = two ? F * 2 : 0, qo.stage_off = (piece_elems * 2 + 127) & ~127;
-  qo.q = static_cast<uint8_t*>(q), qo.sf = sf, qo.amax = nullptr, qo.nkb_pad = int(pad_to(F / 32, 4));
+  qo.q = static_cast<uint8_t*>(q), qo.sf = sf, qo.amax = nullptr, qo.nkb_pad = int(pad_to(F / 32, 4)), qo.bias = bias;
   return run_stream_pipe("act_quantize_mxfp8", qo, rows * qo.pieces_per_row, piece_elems * 2, s, two ? 8 : 12, 3);
 }
 
@@ -372,20 +380,20 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
   return after_launch("quantize_blockscaled");
 }
 
-int mxk_act_quantize_mxfp8(int act_mode, const mxk_bf16* in, int64_t rows, int64_t F, void* q, uint8_t* sf,
+int mxk_act_quantize_mxfp8(int act_mode, const mxk_bf16* in, const float* bias, int64_t rows, int64_t F, void* q, uint8_t* sf,
                            mxk_stream_t stream) {
   if (act_mode < 0 || act_mode > 2) return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: act_mode %d (0 gelu tanh, 1 silu_mul, 2 gelu erf)", act_mode);
-  if (F <= 0 || F % 32 != 0 || !aligned(in, 16))
-    return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: need F %% 32 == 0 and a 16-byte aligned input");
+  if (F <= 0 || F % 32 != 0 || !aligned(in, 16) || !aligned(bias, 16))
+    return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: need F %% 32 == 0 and 16-byte aligned input and bias");
   if (F > kMaxQuantK) return fail(MXK_ERR_TOO_LARGE, "act_quantize_mxfp8: F=%lld beyond %lld", (long long)F, (long long)kMaxQuantK);
   if (rows == 0) return MXK_OK;
   if (rows < 0 || !in || !q || !sf) return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: null buffer or negative rows");
   if (!aligned(q, 16)) return fail(MXK_ERR_INVALID_ARG, "act_quantize_mxfp8: q must be 16-byte aligned");
   cudaStream_t s = as_stream(stream);
   if (int rc = clear_scale_padding(MXK_Q_MXFP8, rows, F, sf, s)) return rc;
-  if (act_mode == 1) return run_act_quant<ACT_SILU_MUL>(in, rows, F, q, sf, s);
-  if (act_mode == 2) return run_act_quant<ACT_GELU_ERF>(in, rows, F, q, sf, s);
-  return run_act_quant<ACT_GELU_TANH>(in, rows, F, q, sf, s);
+  if (act_mode == 1) return run_act_quant<ACT_SILU_MUL>(in, bias, rows, F, q, sf, s);
+  if (act_mode == 2) return run_act_quant<ACT_GELU_ERF>(in, bias, rows, F, q, sf, s);
+  return run_act_quant<ACT_GELU_TANH>(in, bias, rows, F, q, sf, s);
 }
 
 }  // extern "C"

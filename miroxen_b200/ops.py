@@ -244,13 +244,13 @@ def quantize_blockscaled(mode: int, x, ldx: int, rows: int, K: int, out: Optiona
     return out
 
 
-def act_quantize_mxfp8(act_mode: int, in_, rows: int, F: int, out: Optional[QMat] = None, stream=None) -> QMat:
+def act_quantize_mxfp8(act_mode: int, in_, rows: int, F: int, out: Optional[QMat] = None, stream=None, bias=None) -> QMat:
     """The MLP activation (gelu_tanh_inplace / silu_mul / gelu_erf_inplace of src/kernels/ops.h:36-41) and its
     MXFP8 quantisation in one pass; same bytes as the two calls, without writing the bf16 activation."""
     if out is None:
         out = QMat(torch.empty(qdata_bytes(Q_MXFP8, rows, F), dtype=torch.uint8, device=in_.device),
                    torch.empty(qscale_bytes(Q_MXFP8, rows, F), dtype=torch.uint8, device=in_.device))
-    check(lib().mxk_act_quantize_mxfp8(act_mode, _p(in_), rows, F, _p(out.q), _p(out.sf), _stream(stream)))
+    check(lib().mxk_act_quantize_mxfp8(act_mode, _p(in_), _p(bias), rows, F, _p(out.q), _p(out.sf), _stream(stream)))
     return out
 
 

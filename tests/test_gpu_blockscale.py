@@ -327,3 +327,24 @@ def test_residual_norm_quantize_equals_the_two_calls(mx, norm_mode, rows, dim, p
     sf.check("sf")
     assert torch.equal(x1, x2), "residual stream differs from the two calls"
     assert torch.equal(sf.t, two.sf) and torch.equal(q.t, two.q)
+
+
+@pytest.mark.parametrize("act_mode", [0, 1])
+@pytest.mark.parametrize("rows,F", [(5, 96), (129, 160), (37, 4128), (300, 12288)])
+def test_bias_act_quantize_equals_three_calls(mx, act_mode, rows, F):
+    g = H.rng(rows + F + 7 * act_mode)
+    cols = 2 * F if act_mode == 1 else F
+    bits, bias = H.normal_bf16(g, (rows, cols), 2.0), H.normal_f32(g, cols, 0.5)
+    bd = H.to_dev(torch, bias)
+    x = H.to_dev(torch, bits)
+    one = mx.ops.act_quantize_mxfp8(act_mode, x, rows, F, bias=bd)
+    mx.ops.add_bias_bf16(x, bd, rows, cols)
+    if act_mode == 1:
+        act = torch.empty(rows, F, dtype=torch.bfloat16, device="cuda")
+        mx.ops.silu_mul(x, rows, F, act)
+    else:
+        act = x
+        mx.ops.gelu_tanh_inplace(act, rows * F)
+    three = mx.ops.quantize_blockscaled(1, act, F, rows, F)
+    torch.cuda.synchronize()
+    assert torch.equal(one.sf, three.sf) and torch.equal(one.q, three.q)
