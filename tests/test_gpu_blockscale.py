@@ -348,3 +348,21 @@ def test_bias_act_quantize_equals_three_calls(mx, act_mode, rows, F):
     three = mx.ops.quantize_blockscaled(1, act, F, rows, F)
     torch.cuda.synchronize()
     assert torch.equal(one.sf, three.sf) and torch.equal(one.q, three.q)
+
+
+def test_mxfp8_row_shards_on_tile_boundaries_equal_the_whole(mx):
+    """Rows are independent and a scale tile holds 128 rows, so shards cut at multiples of 128 rows write
+    disjoint parts of the same (q, sf): what a row-sharded run does with one shard per GPU."""
+    g = H.rng(77)
+    rows, K = 640, 1056
+    bits = H.normal_bf16(g, (rows, K), 1.5)
+    x = H.to_dev(torch, bits)
+    whole = mx.ops.quantize_blockscaled(1, x, K, rows, K)
+    q = torch.zeros_like(whole.q)
+    sf = torch.zeros_like(whole.sf)
+    tile = mx.ops.qscale_bytes(1, 128, K)
+    for r0, n in ((0, 256), (256, 128), (384, 256)):
+        part = mx.ops.QMat(q[r0 * K:(r0 + n) * K], sf[r0 // 128 * tile:(r0 + n) // 128 * tile])
+        mx.ops.quantize_blockscaled(1, x[r0:r0 + n], K, n, K, part)
+    torch.cuda.synchronize()
+    assert torch.equal(q, whole.q) and torch.equal(sf, whole.sf)
