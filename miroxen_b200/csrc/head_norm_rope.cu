@@ -211,7 +211,7 @@ struct LaneRole {
 // All `ntok` tokens of one tensor inside a stage.  NORM: per-head RMSNorm; MODE as MXK_ROPE_*.
 // src points at the thread's 8 channels of token 0 (pass 0) in shared memory, dst at the same
 // place of the output; cr / sr at the lane's first table entry of token 0.
-template <int LPH, bool NORM, int MODE>
+template <int LPH, bool NORM, int MODE, int PASSES>
 __device__ __forceinline__ void rope_tokens(const unsigned char* src, int tok_bytes, const float* cr, const float* sr,
                                             int half, int ntok, unsigned char* dst, int out_tok_bytes,
                                             const float* wsm_row, float inv_d, float eps, int passes, int heads_per_pass,
@@ -239,8 +239,11 @@ __device__ __forceinline__ void rope_tokens(const unsigned char* src, int tok_by
     }
     const unsigned char* sp = src;
     unsigned char* dp = dst;
-    for (int pass = 0; pass < passes; pass++) {
-      const bool on = r.hp < (pass + 1 < passes ? heads_per_pass : H - pass * heads_per_pass);
+    // PASSES > 0: the pass count is a compile-time constant and every pass is full (H = PASSES *
+    // heads_per_pass), so the loop unrolls into independent chains and needs no predicate.
+#pragma unroll
+    for (int pass = 0; pass < (PASSES > 0 ? PASSES : passes); pass++) {
+      const bool on = PASSES > 0 || r.hp < (pass + 1 < passes ? heads_per_pass : H - pass * heads_per_pass);
       uint4 raw = make_uint4(0u, 0u, 0u, 0u);
       if (on) raw = *reinterpret_cast<const uint4*>(sp);
       float v[8];
@@ -320,7 +323,7 @@ __device__ __forceinline__ bool rope_produce(const RopeArgs& a, unsigned char* d
   return true;
 }
 
-template <int LPH>
+template <int LPH, int PASSES = 0>
 __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ __align__(8) unsigned long long full[8], empty[8];
@@ -399,7 +402,7 @@ __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
           const bool t_rope = t.mode != MXK_ROPE_NONE && t.rot > 0;
           const float* wr = &wsm[ti][8 * l];
 #define MXK_ROPE_CALL(NORM, MODE)                                                                          \
-  rope_tokens<LPH, NORM, MODE>(src, sg.token_bytes, cr, sr, half, ntok, dst, tok_out_bytes, wr, inv_d, a.eps, \
+  rope_tokens<LPH, NORM, MODE, PASSES>(src, sg.token_bytes, cr, sr, half, ntok, dst, tok_out_bytes, wr, inv_d, a.eps, \
                                a.passes, a.heads_per_pass, a.H, r)
           if (t.norm_w) {
             if (!t_rope) MXK_ROPE_CALL(true, MXK_ROPE_NONE);
@@ -561,9 +564,9 @@ bool pipe_plan(RopeArgs& a) {
   return size_t(stages) * a.stage_bytes <= 200 * 1024;
 }
 
-template <int LPH>
+template <int LPH, int PASSES = 0>
 int launch_pipe(const char* name, RopeArgs a, cudaStream_t stream) {
-  auto k = head_rope_pipe_kernel<LPH>;
+  auto k = head_rope_pipe_kernel<LPH, PASSES>;
   const int threads = int(ceil_div(int64_t(LPH) * a.heads_per_pass, 32) * 32) + 32;  // consumers + producer warp
   const size_t smem = size_t(a.stages) * a.stage_bytes;
   if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -583,7 +586,21 @@ int run(const char* name, RopeArgs a, cudaStream_t stream) {
     switch (a.D / 8) {
       case 4: return launch_pipe<4>(name, a, stream);
       case 8: return launch_pipe<8>(name, a, stream);
-      case 16: return launch_pipe<16>(name, a, stream);
+      case 16: {
+        // D = 128, the model shapes: when every pass is full and every consumer thread has a head, the
+        // pass loop is unrolled at compile time (24, 32, 40, 56 heads at 8 heads per pass)
+        const bool exact = a.H == a.passes * a.heads_per_pass && (16 * a.heads_per_pass) % 32 == 0;
+        if (exact && tune(TUNE_ROPE_UNROLL, 1) == 1) {
+          switch (a.passes) {
+            case 3: return launch_pipe<16, 3>(name, a, stream);
+            case 4: return launch_pipe<16, 4>(name, a, stream);
+            case 5: return launch_pipe<16, 5>(name, a, stream);
+            case 7: return launch_pipe<16, 7>(name, a, stream);
+            default: break;
+          }
+        }
+        return launch_pipe<16>(name, a, stream);
+      }
       default: return launch_pipe<32>(name, a, stream);
     }
   }

@@ -32,6 +32,7 @@ enum TuneKey {
   TUNE_PIPE_INTERLEAVE,    // same choice for the head and streaming pipelines (1 interleaved, 2 contiguous)
   TUNE_QUANT_ROWS_PER_CTA, // rows per work item of the block-scale quantiser
   TUNE_QUANT_PATH,         // 1 bulk-copy streaming pipeline for the quantiser, 2 register kernels
+  TUNE_ROPE_UNROLL,        // 1: head pipeline with the pass loop unrolled where the shape allows (default), 2: runtime loop
   TUNE_COUNT
 };
 
