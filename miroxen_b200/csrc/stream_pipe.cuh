@@ -162,6 +162,13 @@ __global__ void __launch_bounds__(544) stream_pipe_kernel(const Op op, const int
       const uint4* s1 = reinterpret_cast<const uint4*>(dyn + size_t(st) * stage_bytes + src_bytes);
       uint4* d = reinterpret_cast<uint4*>(c.dst);
       const int nvec = int(c.bytes >> 4);
+      if (nvec == 2 * n_cons) {
+        // a full chunk at the default shapes: two vectors per thread, no loop and no bounds checks
+        const uint4 a0 = s0[tid], a1 = s0[tid + n_cons];
+        const uint4 b0 = Op::NSRC == 2 ? s1[tid] : a0, b1 = Op::NSRC == 2 ? s1[tid + n_cons] : a1;
+        st_stream(d + tid, op.apply(a0, b0));
+        st_stream(d + tid + n_cons, op.apply(a1, b1));
+      } else
       for (int v = tid; v < nvec; v += 4 * n_cons) {
         uint4 a[4], b[4];
 #pragma unroll
