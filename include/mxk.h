@@ -73,6 +73,18 @@ int mxk_rmsnorm_mod(const float* x, int64_t rows, int64_t dim, float eps, const 
 int mxk_rmsnorm_bf16(const mxk_bf16* x, int64_t rows, int64_t dim, float eps, const float* w,
                      mxk_bf16* out, mxk_stream_t stream);
 
+/* No counterpart in the reference (its launchers have one kernel per op).  Reports which kernel
+ * family a norm call with these pointer values and sizes would take: 0 = one CTA per row (any
+ * size / alignment), 1 = register row kernel (8/16-byte vector accesses), 2 = bulk-copy row kernel
+ * (rows copied to shared memory with cp.async.bulk, which needs every row of x, and of y in the
+ * fused forms, to start on a 16-byte boundary).  op: 0 layernorm_mod, 1 rmsnorm_mod,
+ * 2 rmsnorm_bf16, 3 / 4 gated_residual_norm with LayerNorm / RMSNorm, 5 / 6 the same two with
+ * MXFP8 output (`out` stands for q; these return 2 or MXK_ERR_INVALID_ARG, as the entry point
+ * would).  Pure host arithmetic: nothing is dereferenced and no CUDA call is made, so it works
+ * without a GPU. */
+int mxk_norm_path_probe(int op, const void* x, const void* y, const void* out, const float* w, MxkRowMod scale,
+                        MxkRowMod shift, MxkRowMod gate, int64_t rows, int64_t dim);
+
 /* ---- residual --------------------------------------------------------------------------- */
 
 /* src/kernels/ops.h:27 gated_residual: x += act(gate) * y with act = tanh when gate_tanh != 0,

@@ -75,6 +75,7 @@ PROTOTYPES = {
     "mxk_layernorm_mod": (_I, [_P, _I64, _I64, _F, RowMod, RowMod, _P, _P]),
     "mxk_rmsnorm_mod": (_I, [_P, _I64, _I64, _F, _P, RowMod, RowMod, _P, _P]),
     "mxk_rmsnorm_bf16": (_I, [_P, _I64, _I64, _F, _P, _P, _P]),
+    "mxk_norm_path_probe": (_I, [_I, _P, _P, _P, _P, RowMod, RowMod, RowMod, _I64, _I64]),
     "mxk_gated_residual": (_I, [_P, _P, _I64, _I64, RowMod, _I, _P]),
     "mxk_add_inplace_bf16": (_I, [_P, _P, _I64, _P]),
     "mxk_head_norm_rope": (_I, [_P, _I64, _I64, _I64, _I, _I, _P, _F, _P, _P, _I, _I, _P, _P]),

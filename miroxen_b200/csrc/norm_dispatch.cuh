@@ -84,7 +84,7 @@ inline void launch_norm(const NormPlan& p, const NormArgs& a, bool tma, cudaStre
   }
 }
 
-// True when every pointer the vector kernel dereferences with 8/16-byte accesses is aligned.
+// True when every pointer the register row kernel dereferences with 8/16-byte accesses is aligned.
 template <class TIN>
 inline bool norm_vector_ok(const NormArgs& a) {
   if (a.dim % 4) return false;
@@ -94,15 +94,37 @@ inline bool norm_vector_ok(const NormArgs& a) {
          ok(a.gate.target, 16) && ok(a.gate.prefix, 16);
 }
 
-// Runs one norm launch (vector kernel when shapes and alignment allow, generic otherwise).
+// What the bulk-copy row kernel needs on top of norm_vector_ok(): every row it copies with
+// cp.async.bulk must start on a 16-byte boundary and be a multiple of 16 bytes long.  Callers pass
+// offset pointers (a view that starts a few elements into a buffer), so the base address is checked
+// as well as the row pitch: a bf16 x or y that is only 8-byte aligned takes the register kernel.
+template <class TIN>
+inline bool norm_bulk_ok(const NormArgs& a, bool fuse_res) {
+  auto ok16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
+  if ((int64_t(a.dim) * int64_t(sizeof(TIN))) % 16 != 0 || !ok16(a.x)) return false;
+  if (fuse_res && (a.dim % 8 != 0 || !ok16(a.y) || !ok16(a.xw))) return false;
+  return a.rows >= 2;
+}
+
+// Kernel family a norm launch takes.  Pure host arithmetic on pointer values and sizes (nothing is
+// dereferenced), so the choice can be checked without a GPU (mxk_norm_path_probe).
+enum NormPath { kNormPathGeneric = 0, kNormPathVector = 1, kNormPathBulk = 2 };
+
+template <int MODE, class TIN, bool FUSE_RES>
+inline NormPath choose_norm_path(const NormArgs& a, NormPlan& p) {
+  // LayerNorm with an affine weight has no caller in the reference; it takes the generic kernel.
+  if ((MODE == 0 && a.w) || !norm_vector_ok<TIN>(a) || !plan_norm(a.nvec, a.rows, p)) return kNormPathGeneric;
+  if (tune(TUNE_NORM_PATH, 1) == 1 && norm_bulk_ok<TIN>(a, FUSE_RES)) return kNormPathBulk;
+  return kNormPathVector;
+}
+
+// Runs one norm launch (bulk-copy or register row kernel when shapes and alignment allow, generic otherwise).
 template <int MODE, class TIN, bool FUSE_RES>
 inline int run_norm(const char* name, NormArgs a, cudaStream_t s) {
   NormPlan p;
-  // LayerNorm with an affine weight has no caller in the reference; it takes the generic kernel.
-  if (!(MODE == 0 && a.w) && norm_vector_ok<TIN>(a) && plan_norm(a.nvec, a.rows, p)) {
-    // The bulk-copy pipeline needs 16-byte rows: dim % 4 for fp32 rows (given), dim % 8 for bf16 rows.
-    const bool rows16 = (sizeof(TIN) == 4 || a.dim % 8 == 0) && (!FUSE_RES || a.dim % 8 == 0);
-    const bool tma = rows16 && tune(TUNE_NORM_PATH, 1) == 1 && a.rows >= 2;
+  const NormPath path = choose_norm_path<MODE, TIN, FUSE_RES>(a, p);
+  if (path != kNormPathGeneric) {
+    const bool tma = path == kNormPathBulk;
     if constexpr (MODE == 1) {
       if (a.w) launch_norm<MODE, TIN, true, FUSE_RES>(p, a, tma, s);
       else launch_norm<MODE, TIN, false, FUSE_RES>(p, a, tma, s);
@@ -125,6 +147,14 @@ inline int run_norm(const char* name, NormArgs a, cudaStream_t s) {
     if (rc) return rc;
   }
   return MXK_OK;
+}
+
+// The norm + MXFP8 one-pass forms run on the bulk-copy row kernel only; true when this call can take it.
+template <bool FUSE_RES>
+inline bool norm_quant_ok(const NormArgs& a, NormPlan& p) {
+  NormArgs b = a;
+  b.rows = a.rows < 2 ? 2 : a.rows;  // a single row runs through the same kernel
+  return norm_vector_ok<float>(a) && norm_bulk_ok<float>(b, FUSE_RES) && plan_norm(a.nvec, a.rows, p);
 }
 
 inline int check_norm_common(const char* name, const void* x, int64_t rows, int64_t dim,

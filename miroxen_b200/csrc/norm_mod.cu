@@ -46,4 +46,28 @@ int mxk_rmsnorm_bf16(const mxk_bf16* x, int64_t rows, int64_t dim, float eps, co
                                   as_stream(stream));
 }
 
+int mxk_norm_path_probe(int op, const void* x, const void* y, const void* out, const float* w, MxkRowMod scale,
+                        MxkRowMod shift, MxkRowMod gate, int64_t rows, int64_t dim) {
+  if (rows <= 0 || dim <= 0 || dim > (int64_t(1) << 30)) return MXK_ERR_INVALID_ARG;
+  NormArgs a = make_args(x, rows, dim, 0.f, w, scale, shift, static_cast<mxk_bf16*>(const_cast<void*>(out)));
+  NormPlan p;
+  const bool fused = op >= 3;
+  if (fused) a.xw = static_cast<float*>(const_cast<void*>(x)), a.y = static_cast<const bf16*>(y), a.gate = gate;
+  switch (op) {
+    case 0: a.w = nullptr; return choose_norm_path<0, float, false>(a, p);
+    case 1: return choose_norm_path<1, float, false>(a, p);
+    case 2: return choose_norm_path<1, bf16, false>(a, p);
+    case 3: a.w = nullptr; return choose_norm_path<0, float, true>(a, p);
+    case 4: return choose_norm_path<1, float, true>(a, p);
+    case 5:
+    case 6:
+      // the one-pass MXFP8 forms: `out` stands for the code buffer q
+      a.out = nullptr;
+      if (dim % 32 != 0 || !aligned(out, 16)) return MXK_ERR_INVALID_ARG;
+      if (op == 5) a.w = nullptr;
+      return norm_quant_ok<true>(a, p) ? int(kNormPathBulk) : MXK_ERR_INVALID_ARG;
+    default: return MXK_ERR_INVALID_ARG;
+  }
+}
+
 }  // extern "C"

@@ -28,7 +28,8 @@ int run_norm_quant(const char* name, const float* x, int64_t rows, int64_t dim, 
   a.q = static_cast<uint8_t*>(q), a.sf = sf, a.nkb_pad = int(pad_to(dim / 32, 4));
   if (FUSE_RES) a.xw = xw, a.y = reinterpret_cast<const bf16*>(y), a.gate = gate, a.gate_tanh = gate_tanh;
   NormPlan p;
-  if (!norm_vector_ok<float>(a) || !plan_norm(a.nvec, a.rows, p))
+  // The one-pass form exists for the bulk-copy row kernel only, whose copies need x (and y) rows on 16-byte boundaries.
+  if (!norm_quant_ok<FUSE_RES>(a, p))
     return fail(MXK_ERR_INVALID_ARG, "%s: dim %lld or an unaligned vector is outside the one-pass kernel; call the norm and "
                 "mxk_quantize_blockscaled separately", name, (long long)dim);
   // scale padding, as mxk_quantize_blockscaled clears it

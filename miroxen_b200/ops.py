@@ -29,6 +29,7 @@ __all__ = [
     "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8", "gated_residual_norm_quant_mxfp8",
     "qwen_latent_encode", "qwen_latent_decode", "h3_latent_video", "h3_latent_audio",
     "bias_gelu_tanh_inplace", "bias_silu_mul", "gated_residual_bias",
+    "norm_path_probe", "NORM_PATH_GENERIC", "NORM_PATH_VECTOR", "NORM_PATH_BULK",
 ]
 
 
@@ -68,6 +69,15 @@ def rmsnorm_mod(x, rows, dim, eps, w, scale: RowMod, shift: RowMod, out, stream=
 
 def rmsnorm_bf16(x, rows, dim, eps, w, out, stream=None):
     check(lib().mxk_rmsnorm_bf16(_p(x), rows, dim, eps, _p(w), _p(out), _stream(stream)))
+
+
+NORM_PATH_GENERIC, NORM_PATH_VECTOR, NORM_PATH_BULK = 0, 1, 2
+
+
+def norm_path_probe(op, x, y, out, w, rows, dim, scale: RowMod = None, shift: RowMod = None, gate: RowMod = None) -> int:
+    """Kernel family a norm call with these pointers and sizes takes (host arithmetic only; see mxk.h)."""
+    return lib().mxk_norm_path_probe(int(op), _p(x), _p(y), _p(out), _p(w), scale or _NONE, shift or _NONE, gate or _NONE,
+                                     rows, dim)
 
 
 def gated_residual(x, y, rows, dim, gate: RowMod, gate_tanh, stream=None):

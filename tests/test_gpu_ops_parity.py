@@ -121,6 +121,87 @@ def test_norm_unaligned_pointers(mx):
     assert float(obuf[0]) == 0.0
 
 
+def _offset_view(flat, off, n):
+    """`n` elements of a flat device tensor starting `off` elements in (an offset pointer, as the
+    reference's callers pass: src/models/minimax_h3/dit_sp.cpp:91,153-163)."""
+    return flat[off:off + n]
+
+
+@pytest.mark.parametrize("off", [4, 8, 12])
+def test_rmsnorm_bf16_input_offset_by_eight_bytes(mx, off):
+    """A bf16 x that starts 4 (or 12) elements into its buffer is 8- but not 16-byte aligned: it must
+    leave the bulk-copy kernel (whose copies need 16) and still match the oracle."""
+    g = H.rng(40 + off)
+    rows, dim = 37, 3584
+    x = H.normal_bf16(g, (rows, dim), 1.5)
+    w = H.normal_f32(g, dim, 0.1, 1.0)
+    ref = orc.rmsnorm_bf16(x, 1e-6, w)
+    xbuf = torch.zeros(rows * dim + 16, dtype=torch.bfloat16, device="cuda")
+    xv = _offset_view(xbuf, off, rows * dim)
+    xv.copy_(H.to_dev(torch, x).reshape(-1))
+    out = H.Guarded(torch, (rows, dim), torch.bfloat16)
+    wd = H.to_dev(torch, w)
+    path = mx.norm_path_probe(2, xv, None, out.t, wd, rows, dim)
+    assert xv.data_ptr() % 16 == (off * 2) % 16
+    if xv.data_ptr() % 16:
+        assert path == mx.NORM_PATH_VECTOR
+    mx.rmsnorm_bf16(xv, rows, dim, 1e-6, wd, out.t)
+    torch.cuda.synchronize()
+    out.check("rmsnorm_bf16 offset x")
+    H.assert_bf16_close(H.bits(out.t), ref, f"rmsnorm_bf16 x offset {off}")
+
+
+@pytest.mark.parametrize("norm_mode", [0, 1])
+@pytest.mark.parametrize("off", [4, 8])
+def test_gated_residual_norm_residual_row_offset_by_eight_bytes(mx, norm_mode, off):
+    """The fused residual + norm with y starting 4 elements into its buffer: the register kernel's
+    64-bit loads take it; the result equals the oracle and x equals the two-call form bit for bit."""
+    g = H.rng(50 + off + norm_mode)
+    rows, dim = 41, 3072
+    x = H.normal_f32(g, (rows, dim))
+    y = H.normal_bf16(g, (rows, dim))
+    gate = H.normal_f32(g, dim, 0.7)
+    sc, sh = H.normal_f32(g, dim, 0.3), H.normal_f32(g, dim, 0.3)
+    w = H.normal_f32(g, dim, 0.1, 1.0) if norm_mode == 1 else None
+    xr = orc.gated_residual(x.copy(), y, orc.mod(gate), 1)
+    ref = (orc.layernorm_mod(xr, 1e-6, orc.mod(sc), orc.mod(sh)) if norm_mode == 0
+           else orc.rmsnorm_mod(xr, 1e-6, w, orc.mod(sc), orc.mod(sh)))
+    keep = []
+    dg, dsc, dsh = dev_mod(mx, keep, gate), dev_mod(mx, keep, sc), dev_mod(mx, keep, sh)
+    wd = H.to_dev(torch, w) if w is not None else None
+    ybuf = torch.zeros(rows * dim + 16, dtype=torch.bfloat16, device="cuda")
+    yv = _offset_view(ybuf, off, rows * dim)
+    yv.copy_(H.to_dev(torch, y).reshape(-1))
+    xf = H.Guarded(torch, (rows, dim), torch.float32, fill=torch.from_numpy(x))
+    of = H.Guarded(torch, (rows, dim), torch.bfloat16)
+    path = mx.norm_path_probe(3 + norm_mode, xf.t, yv, of.t, wd, rows, dim, dsc, dsh, dg)
+    if yv.data_ptr() % 16:
+        assert path == mx.NORM_PATH_VECTOR
+    mx.gated_residual_norm(xf.t, yv, rows, dim, dg, 1, norm_mode, 1e-6, wd, dsc, dsh, of.t)
+    x2 = H.to_dev(torch, x)
+    mx.gated_residual(x2, yv, rows, dim, dg, 1)
+    torch.cuda.synchronize()
+    xf.check("fused x"), of.check("fused out")
+    H.assert_f32_close(xf.t.cpu().numpy(), xr, "fused residual x, offset y")
+    H.assert_bf16_close(H.bits(of.t), ref, "fused norm out, offset y")
+    assert torch.equal(xf.t, x2)
+
+
+def test_gated_residual_norm_quant_refuses_a_residual_row_offset_by_eight_bytes(mx):
+    """The one-pass MXFP8 form exists for the bulk-copy kernel only: an 8-byte aligned y is refused
+    with a status (the caller then makes the two calls), nothing is launched."""
+    rows, dim = 16, 3072
+    x = torch.zeros((rows, dim), dtype=torch.float32, device="cuda")
+    ybuf = torch.zeros(rows * dim + 16, dtype=torch.bfloat16, device="cuda")
+    launches = mx.launch_count()
+    with pytest.raises(mx.MxkError, match="outside the one-pass kernel"):
+        mx.gated_residual_norm_quant_mxfp8(x, _offset_view(ybuf, 4, rows * dim), rows, dim, None, 0, 0, 1e-6, None, None, None)
+    assert mx.launch_count() == launches
+    # the same call with y offset by a multiple of 16 bytes runs
+    mx.gated_residual_norm_quant_mxfp8(x, _offset_view(ybuf, 8, rows * dim), rows, dim, None, 0, 0, 1e-6, None, None, None)
+    torch.cuda.synchronize()
+
+
 @pytest.mark.parametrize("rows,dim", [(8, 3072), (37, 5376), (19, 100), (7, 99), (1, 4096), (260, 3072)])
 @pytest.mark.parametrize("mode", ["tanh_prefix", "identity", "none"])
 def test_gated_residual(mx, rows, dim, mode):
