@@ -284,15 +284,22 @@ int mxk_op_times_read(MxkOpTimes* t, float* ms_host, int cap);
  * of one chunk overlapping the kernels of another on three internal streams owned by the handle.
  * Host buffers should be pinned for the copies to overlap. */
 typedef struct MxkHostPipeline MxkHostPipeline;
-/* Allocates two sets of device staging buffers for chunks of chunk_rows rows (this is the one
- * place the library allocates device memory; the handle owns it). with_v / act_mode mirror the args. */
+/* Allocates MXK_HOST_PIPELINE_SLOTS (three) sets of device staging buffers for chunks of chunk_rows
+ * rows, three streams and nine events (this is the one place the library allocates device memory; the
+ * handle owns it).  Device bytes per set: chunk_rows x (4 dim + 4 x 2 dim + (4, or 6 with_v) x 2 H D +
+ * 2 F (+ 4 F when act_mode == 1) + 2 x 4 max(rot / 2, 1)), each array rounded up to 256 bytes; a caller that
+ * sizes an arena budgets three times that.  with_v / act_mode mirror the args. */
+#define MXK_HOST_PIPELINE_SLOTS 3
 int mxk_host_pipeline_create(int64_t chunk_rows, int64_t dim, int64_t F, int H, int D, int rot,
                              int with_v, int act_mode, MxkHostPipeline** out);
 void mxk_host_pipeline_destroy(MxkHostPipeline* p);
 /* `a` holds HOST pointers for x, h1, h2, q/k/v_in, q/k/v_out, attn_o, act, act2, mlp_o, cos, sin
  * and DEVICE pointers for the modulation vectors and norm weights; q/k/v_in are read as separate
  * [rows, H*D] arrays (qkv_stride and col0 as given apply to the host arrays).  Blocks until the
- * results are back in host memory.  h2d_bytes / d2h_bytes (may be NULL) receive the bytes copied. */
+ * results are back in host memory.  h2d_bytes / d2h_bytes (may be NULL) receive the bytes copied.
+ * Before returning it reads the device error word (see mxk_device_error): if a kernel's bounded wait
+ * ran out during the call the status is MXK_ERR_CUDA and the host results are incomplete.  Callers of
+ * the device-buffer entry points, which never synchronise, poll mxk_device_error themselves. */
 int mxk_dit_block_ops_host(MxkHostPipeline* p, const MxkBlockArgs* a, int64_t* h2d_bytes,
                            int64_t* d2h_bytes);
 
@@ -308,7 +315,13 @@ int mxk_dit_block_ops_host(MxkHostPipeline* p, const MxkBlockArgs* a, int64_t* h
  *  - Limit: 64 rows of staging must fit the array (for a 3072-wide block one row stages about 85 KB);
  *    wider blocks return MXK_ERR_TOO_LARGE.  The number of rows is not limited.
  *  - The first call on each device looks the array's address up (cudaGetSymbolAddress, with that
- *    device current); make that first call before any stream capture begins.
+ *    device current) and keeps it for the life of the process; make that first call before any
+ *    stream capture begins.  The kept address does not survive a cudaDeviceReset of that device:
+ *    after a reset the library must be reloaded before this entry point is used again.
+ *  - The stream must belong to the current device (the array that is used is the current device's);
+ *    a stream of another device is refused with MXK_ERR_INVALID_ARG before any copy is issued.
+ *  - Like mxk_dit_block_ops_host it reads the device error word before returning and reports a
+ *    kernel's timed-out wait as MXK_ERR_CUDA.
  *  - All calls on a device share the one array.  It keeps the previous call's bytes, which is harmless:
  *    every byte a chunk's kernels read is first written by that chunk's own copies or kernels, so
  *    nothing has to start at zero.  Two calls whose work overlaps on the GPU (different streams or

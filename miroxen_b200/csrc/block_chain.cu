@@ -31,6 +31,23 @@ int check_block(const MxkBlockArgs* a) {
   return MXK_OK;
 }
 
+// Reads the device error word behind everything already queued on `s` and waits for it.  The host-buffer
+// entry points hand results back in host memory, so a kernel that gave up on a bounded wait (and left
+// part of its output unwritten) must turn into a status here: nobody else would look.  The word is left
+// set; mxk_device_error() reads and clears it.
+int device_error_status(const char* name, cudaStream_t s) {
+  int word = 0;
+  int* p = device_error_word();
+  if (!p) return fail(MXK_ERR_CUDA, "%s: no error word on this device", name);
+  cudaError_t e = cudaMemcpyAsync(&word, p, sizeof(int), cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "%s: reading the device error word: %s", name, cudaGetErrorString(e));
+  if (word != 0)
+    return fail(MXK_ERR_CUDA, "%s: a kernel's bounded wait ran out (device error word = %d); the results in host memory "
+                "are incomplete", name, word);
+  return MXK_OK;
+}
+
 #define MXK_TRY(expr)            \
   do {                           \
     if (int rc_ = (expr)) return rc_; \
@@ -112,7 +129,7 @@ struct MxkOpTimes {
 
 // Staging slots of the host pipeline: with three, the upload of chunk c + 2 never waits for the
 // download of chunk c (it reuses the slot of chunk c - 1, whose results left one chunk time earlier).
-constexpr int kHostSlots = 3;
+constexpr int kHostSlots = MXK_HOST_PIPELINE_SLOTS;
 
 struct MxkHostPipeline {
   int64_t chunk_rows, dim, F, inner, half;
@@ -350,7 +367,8 @@ int mxk_dit_block_ops_host(MxkHostPipeline* p, const MxkBlockArgs* a, int64_t* h
 #undef MXK_CU
   if (h2d_bytes) *h2d_bytes = up;
   if (d2h_bytes) *d2h_bytes = down;
-  return MXK_OK;
+  // the last download was ordered after every chunk's kernels, so the word is final by now
+  return device_error_status("dit_block_ops_host", p->d2h);
 }
 
 
@@ -410,9 +428,21 @@ int mxk_dit_block_ops_host_static(const MxkBlockArgs* a, mxk_stream_t stream, in
                 "dit_block_ops_host_static: one row stages %lld bytes; 64 rows do not fit the %lld-byte static "
                 "staging array (use mxk_dit_block_ops_host, whose pipeline allocates its own)",
                 (long long)per_row, (long long)kStaticStageBytes);
+  cudaStream_t s = as_stream(stream);
+  // The array's address is looked up for the CURRENT device: a stream of another device would make the
+  // copies below land in (or fail against) the wrong GPU's array half-way through the block.
+  if (reinterpret_cast<uintptr_t>(s) > 2) {  // 0, 1 and 2 are the default-stream handles of the current device
+    int cur = -1, sdev = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cudaStreamGetDevice(s, &sdev) == cudaSuccess) {
+      if (cur != sdev)
+        return fail(MXK_ERR_INVALID_ARG, "dit_block_ops_host_static: the stream belongs to device %d but device %d is "
+                    "current; make the stream's device current before the call", sdev, cur);
+    } else {
+      cudaGetLastError();  // an unsupported query is not an error of this call
+    }
+  }
   unsigned char* base = nullptr;
   if (int rc = static_stage_base(&base)) return rc;
-  cudaStream_t s = as_stream(stream);
 
   unsigned char* c = base;
   auto take = [&](int64_t row_bytes) { unsigned char* r = c; c += row_bytes * chunk; return r; };
@@ -496,11 +526,11 @@ int mxk_dit_block_ops_host_static(const MxkBlockArgs* a, mxk_stream_t stream, in
     MXK_CU(outc(a->act + r0 * F, sact, n * F * 2));
     MXK_CU(outc(a->x + r0 * dim, sx, n * dim * 4));
   }
-  MXK_CU(cudaStreamSynchronize(s));
 #undef MXK_CU
   if (h2d_bytes) *h2d_bytes = up;
   if (d2h_bytes) *d2h_bytes = down;
-  return MXK_OK;
+  // one more 4-byte copy behind the last download (no allocation), then the wait for everything
+  return device_error_status("dit_block_ops_host_static", s);
 }
 
 }  // extern "C"

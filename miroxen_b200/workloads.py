@@ -89,6 +89,27 @@ WORKLOADS = {
 }
 
 
+# image grid (tokens), text tokens and batch of the Qwen-Image-shaped workloads; rows are ordered
+# [img0 | img1 | ... | txt0 | txt1 | ...] so that one prefix boundary separates image and text modulation
+QWEN_GRIDS = {"qwen1024": (64, 64, 256, 2), "qwen512": (32, 32, 128, 1), "qwen2048": (128, 128, 512, 1)}
+
+
+def rope_tables_for(w: "Workload", device="cuda"):
+    """(cos, sin) fp32 [w.rows, rot/2] for the workload's row order, or (None, None) when the workload has no
+    closed-form layout here (BlockBuffers then draws random angles).  Qwen-shaped workloads get the MSRoPE table
+    of src/models/qwen_image/dit.cpp:151-185 for [image | text], repeated per batch element."""
+    grid = QWEN_GRIDS.get(w.name)
+    if not grid:
+        return None, None
+    from . import rope_tables
+    ih, iw, nt, batch = grid
+    c1, s1 = rope_tables.qwen_rope_table([("image", ih, iw), ("text", nt)], device=device)
+    n_img = ih * iw
+    cos = torch.cat([c1[:n_img]] * batch + [c1[n_img:]] * batch).contiguous()
+    sin = torch.cat([s1[:n_img]] * batch + [s1[n_img:]] * batch).contiguous()
+    return cos, sin
+
+
 def with_rows(w: Workload, rows: int, prefix_rows: int) -> Workload:
     return replace(w, rows=rows, prefix_rows=prefix_rows)
 
@@ -164,6 +185,29 @@ class BlockBuffers:
         a.attn_o, a.act, a.mlp_o = self.attn_o.data_ptr(), self.act.data_ptr(), self.mlp_o.data_ptr()
         a.act2 = self.act2.data_ptr() if self.act2 is not None else None
         self.args = a
+
+    def shard_args(self, row0: int, rows: int) -> BlockArgs:
+        """BlockArgs for rows [row0, row0 + rows) of these buffers: every pointer is offset to the range's first row
+        and each prefix boundary is moved by row0, which is what a rank that owns the range launches
+        (the reference hands its two cards `x + r0*D` and friends the same way, src/models/minimax_h3/dit_sp.cpp:91-110)."""
+        a, w = self.args, self.w
+        b = BlockArgs()
+        for name, _ in BlockArgs._fields_:
+            setattr(b, name, getattr(a, name))
+        b.rows = rows
+        inner, half = w.inner, w.rot // 2
+        per_row = {"x": 4 * w.dim, "h1": 2 * w.dim, "h2": 2 * w.dim, "attn_o": 2 * w.dim, "mlp_o": 2 * w.dim,
+                   "act": 2 * w.F, "act2": 4 * w.F, "q_out": 2 * inner, "k_out": 2 * inner, "v_out": 2 * inner,
+                   "q_in": 2 * a.qkv_stride, "k_in": 2 * a.qkv_stride, "v_in": 2 * a.qkv_stride,
+                   "cos": 4 * half, "sin": 4 * half}
+        for name, nbytes in per_row.items():
+            base = getattr(a, name)
+            if base:
+                setattr(b, name, base + row0 * nbytes)
+        for k in ("shift1", "scale1", "gate1", "shift2", "scale2", "gate2"):
+            m = getattr(a, k)
+            setattr(b, k, type(m)(m.target, m.prefix, m.prefix_len - row0))
+        return b
 
     def nbytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in vars(self).values() if isinstance(t, torch.Tensor))

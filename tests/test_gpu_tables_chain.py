@@ -280,3 +280,28 @@ def test_bounded_wait_reports_and_context_survives(mx):
     mx.axpy_f32(x, y, 0.5, 1024)
     torch.cuda.synchronize()
     assert float(x.sum()) == 2048.0
+
+
+def test_host_entry_points_report_a_timed_out_wait_as_a_status(mx):
+    """The host-buffer entry points return results in host memory, so they read the device error word
+    themselves: with the word set (here by the harmless bounded-wait self-test) both return
+    MXK_ERR_CUDA instead of 0; after the word is cleared the same calls succeed."""
+    from miroxen_b200 import _lib
+    cfg = BLOCKS[0]
+    _, _, a = make_block(mx, H.rng(11), *cfg, host=True)
+    pipe = mx.HostPipeline(64, cfg[1], cfg[4], cfg[2], cfg[3], cfg[7], with_v=cfg[9], act_mode=cfg[6])
+    try:
+        assert mx.device_error() == 0
+        _lib.check(mx.lib().mxk_selftest_bounded_wait(None))
+        torch.cuda.synchronize()
+        with pytest.raises(mx.MxkError, match="bounded wait ran out"):
+            pipe.run(a)
+        with pytest.raises(mx.MxkError, match="bounded wait ran out"):
+            mx.dit_block_ops_host_static(a)
+        assert mx.device_error(clear=True) == 1  # the entry points leave the word for the caller to clear
+        up, down = pipe.run(a)
+        assert up > 0 and down > 0
+        mx.dit_block_ops_host_static(a)
+    finally:
+        pipe.close()
+        mx.device_error(clear=True)
