@@ -4,16 +4,20 @@ of synthetic token rows).
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload qwen1024] [--chain dropin|fused]
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...     (N > 1)
-    python bench.py --impl reference ...      the CPU restatement of the reference on the host cores
+    python bench.py --impl reference ...      the reference's own CUDA kernels (oracle/_ref) on the same buffers
+    python bench.py --impl reference-cpu ...  the CPU restatement of the reference on the host cores
 
 Prints ONE JSON line (rank 0).  `value` is whole-job GB/s of algorithmic bytes (the per-row byte
 count of the unfused op list x rows / device time) with inputs resident in HBM; `e2e` is the same
 block through mxk_dit_block_ops_host with pinned HOST buffers, copies inside the timed region.
+With N > 1 the token rows of ONE workload are sharded over the ranks (strong scaling, no collective
+in the timed loop); `--scaling weak` runs N replicas instead.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
 import sys
@@ -26,6 +30,8 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "fused-layer HBM GB/s"
 UNIT = "GB/s"
+L2_BYTES = 126e6
+MIN_TIMED_MS = 120.0  # the K-step window is repeated until this much device time has been sampled
 
 
 def parse():
@@ -33,19 +39,23 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="mxk", choices=["mxk", "reference", "reference-cuda"])
+    ap.add_argument("--impl", default="mxk", choices=["mxk", "reference", "reference-cuda", "reference-cpu"])
     ap.add_argument("--workload", default="qwen1024")
     ap.add_argument("--chain", default="dropin", choices=["dropin", "fused"],
                     help="dropin: one launch per reference call; fused: gated_residual+norm and q/k(/v) rope fused")
-    ap.add_argument("--scaling", default="weak", choices=["weak", "strong"],
-                    help="weak: every rank runs the whole workload's rows; strong: the rows are sharded")
+    ap.add_argument("--scaling", default=None, choices=["weak", "strong"],
+                    help="strong (default for N > 1): the workload's rows are sharded over the ranks; "
+                         "weak: every rank runs the whole workload's rows")
+    ap.add_argument("--repeats", type=int, default=0, help="K-step windows timed (default: >= 5, enough for ~120 ms)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-extras", action="store_true", help="skip the second chain and the per-op pass")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the per-op pass, the second chain, the reference kernels and the extra strong-scaling records")
     ap.add_argument("--graph", action="store_true",
                     help="capture each buffer set's block chain into a CUDA graph once and time replays (small shapes)")
-    ap.add_argument("--shard", choices=["frames", "rows"], default="frames",
-                    help="strong scaling of a video workload: whole frames per rank (the reference's split) or equal row ranges")
+    ap.add_argument("--shard", choices=["frames", "rows"], default=None,
+                    help="strong scaling of a video workload: whole frames per rank (the reference's split) or equal "
+                         "row ranges (default: rows for the main line; the video record reports both)")
     ap.add_argument("--e2e-chunk-rows", type=int, default=1024, help="rows per staged chunk of the end-to-end leg")
     ap.add_argument("--quant-only", action="store_true",
                     help="time only the block-scale quantiser on the block's activations (profiling aid; prints its own line)")
@@ -109,8 +119,8 @@ class ClockSampler:
     def summary(self):
         if not self.samples:
             return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
-        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(self.samples),
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_mhz_min": int(min(self.samples)),
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples),
                 "power_w_max": round(max(self.power), 1) if self.power else None}
 
 
@@ -181,38 +191,53 @@ def host_threads():
         return os.cpu_count() or 1
 
 
-def run_reference_cpu(args, W):
-    """--impl reference: the reference has no CPU implementation of these ops (its kernels are CUDA
-    only), so the timed CPU arm is the oracle port on all host threads, on a bounded row sample."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+def cpu_baseline(w, rows, reps):
+    threads = host_threads()
+    sec = cpu_block(w, rows, min(w.prefix_rows, rows * w.prefix_rows // max(w.rows, 1)), threads, reps)
+    return {"value": round(w.bytes_per_row() * rows / sec / 1e9, 3), "unit": UNIT, "cores": threads, "kind": "port",
+            "sample": f"{rows} of {w.rows} rows, every op of the block, median of {reps} passes",
+            "ms_per_block_scaled": round(sec * 1e3 * w.rows / rows, 2),
+            "what": "CPU restatement of the reference's CUDA kernels (the reference has no CPU implementation of these ops)"}
+
+
+def job_config(w, chain, n_gpus, scaling, shard):
+    """The `config` object: a function of the job alone, so that both arms print the same one."""
+    split = "replicas" if scaling == "weak" or n_gpus == 1 else (f"token rows sharded by {shard}")
+    return {"workload": w.name, "desc": w.desc, "rows": w.rows, "dim": w.dim, "heads": f"{w.H}x{w.D}", "F": w.F, "chain": chain,
+            "io_dtype": "bf16 activations, fp32 residual and arithmetic", "bytes_per_row": w.bytes_per_row(),
+            "parallelism": f"{n_gpus} GPU(s), {split}, no collective in the timed loop",
+            "l2": "alternating buffer sets, together > 3x the 126 MB L2"}
+
+
+def run_reference_cpu(args, W, why=None):
+    """The CPU restatement of the reference kernels on all host threads, on a bounded row sample."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
     w = W[args.workload]
-    threads = host_threads()
     rows = args.cpu_rows or min(w.rows, 1088)
-    prefix = min(w.prefix_rows, rows * w.prefix_rows // max(w.rows, 1))
-    for _ in range(max(args.warmup - 1, 0)):
-        pass  # cpu_block warms itself with one untimed pass
-    sec = cpu_block(w, rows, prefix, threads, max(args.steps, 1))
-    gbs = w.bytes_per_row() * rows / sec / 1e9
+    cb = cpu_baseline(w, rows, max(min(args.steps, 20), 1))
+    scaling = args.scaling or ("strong" if args.gpus > 1 else "weak")
     line = {
-        "impl": "reference", "metric": METRIC, "value": round(gbs, 3), "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3 * w.rows / rows, 3),
-        "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "desc": w.desc, "rows": w.rows, "chain": "dropin",
-                   "note": "ms_per_step is the sample's time scaled to the workload's rows"},
-        "cpu_baseline": {"value": round(gbs, 3), "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{rows} of {w.rows} rows, every op of the block, median of {max(args.steps, 1)} passes"},
-        "e2e": {"value": round(gbs, 3), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": cb["ms_per_block_scaled"],
+        "higher_is_better": True, "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": job_config(w, "dropin", args.gpus, scaling, args.shard or "rows"),
+        "reference_kind": "cpu port of the reference's CUDA kernels (oracle/liboracle_fast.so)",
+        "note": "ms_per_step is the sample's time scaled to the workload's rows",
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if why:
+        line["fallback"] = why
     print(json.dumps(line), flush=True)
 
 
-# ---- reference CUDA kernels (extra arm) ----------------------------------------------------------
+# ---- reference CUDA kernels ----------------------------------------------------------------------
 
-def ref_cuda_chain(w, buf, stream_ptr):
-    """One block pass with the REFERENCE's kernels (src/kernels/ops.cu rebuilt for sm_100a)."""
+def ref_cuda_chain(w, buf, stream_ptr, mark=None):
+    """One block pass with the REFERENCE's kernels (src/kernels/ops.cu rebuilt for sm_100a) on the
+    buffers of `buf`; `mark()` (optional) is called before the first launch and after each launch."""
     import ctypes as C
     from oracle import binding as orc
     L = orc.ref_ops()
@@ -228,6 +253,7 @@ def ref_cuda_chain(w, buf, stream_ptr):
     L.ref_gelu_tanh_inplace.argtypes = [P, I64, P]
     L.ref_silu_mul.argtypes = [P, I64, I64, P, P]
     rows, d, Fd = a.rows, a.dim, a.F
+    tick = mark or (lambda: None)
 
     def norm(sc, sh, wgt, out):
         if w.norm_mode == 0:
@@ -235,435 +261,683 @@ def ref_cuda_chain(w, buf, stream_ptr):
         return L.ref_rmsnorm_mod(a.x, rows, d, a.eps, wgt, conv(sc), conv(sh), out, stream_ptr)
 
     def go():
+        tick()
         rc = norm(a.scale1, a.shift1, a.norm1_w, a.h1)
+        tick()
         rc |= L.ref_head_norm_rope(a.q_in, rows, a.qkv_stride, a.q_col0, a.H, a.D, a.norm_q, a.eps, a.cos, a.sin, a.rot,
                                    a.rope_mode, a.q_out, stream_ptr)
+        tick()
         rc |= L.ref_head_norm_rope(a.k_in, rows, a.qkv_stride, a.k_col0, a.H, a.D, a.norm_k, a.eps, a.cos, a.sin, a.rot,
                                    a.rope_mode, a.k_out, stream_ptr)
+        tick()
         if w.packed_qkv:
             rc |= L.ref_head_norm_rope(a.v_in, rows, a.qkv_stride, a.v_col0, a.H, a.D, None, 0.0, None, None, 0, 0,
                                        a.v_out, stream_ptr)
+            tick()
         rc |= L.ref_gated_residual(a.x, a.attn_o, rows, d, conv(a.gate1), a.gate_tanh, stream_ptr)
+        tick()
         rc |= norm(a.scale2, a.shift2, a.norm2_w, a.h2)
+        tick()
         if w.act_mode == 0:
             rc |= L.ref_gelu_tanh_inplace(a.act, rows * Fd, stream_ptr)
         else:
             rc |= L.ref_silu_mul(a.act2, rows, Fd, a.act, stream_ptr)
+        tick()
         rc |= L.ref_gated_residual(a.x, a.mlp_o, rows, d, conv(a.gate2), a.gate_tanh, stream_ptr)
+        tick()
         if rc:
             raise RuntimeError("reference kernel launch failed: " + L.ref_last_error().decode())
     return go
 
 
-# ---- GPU arm ------------------------------------------------------------------------------------
+def dropin_op_names(w):
+    return ["norm_mod"] + ["head_norm_rope"] * (3 if w.packed_qkv else 2) + ["gated_residual", "norm_mod", "act", "gated_residual"]
+
+
+def op_rows(w, names, us_list, rows, peak_gbs):
+    ob = w.op_bytes(rows)
+    act_name = "gelu_tanh_inplace" if w.act_mode == 0 else "silu_mul"
+    ops = []
+    for nme, us in zip(names, us_list):
+        key = act_name if nme == "act" else nme
+        # the token's cos/sin row is charged to each head_norm_rope call that reads it
+        by = ob[key] if key != "head_norm_rope" else ob[key] + 2 * (w.rot // 2) * 4 * rows
+        ops.append({"op": key, "us": round(us, 2), "bytes": by, "gbs": round(by / us / 1e3, 1),
+                    "frac": round(by / us / 1e3 / peak_gbs, 3)})
+    return ops
+
+
+# ---- GPU arms -----------------------------------------------------------------------------------
+
+class Env:
+    """Process-wide handles of a GPU run."""
+
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        import miroxen_b200 as mx
+        self.torch, self.dist, self.mx, self.args = torch, dist, mx, args
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local = int(os.environ.get("LOCAL_RANK", "0"))
+        self.distributed = False
+        pk = ROOT / "MEASURED_PEAKS.json"
+        peaks = json.loads(pk.read_text()) if pk.exists() else {}
+        self.peak_gbs, self.peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+
+    def start(self, distributed):
+        torch = self.torch
+        if not torch.cuda.is_available():
+            raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
+        torch.cuda.set_device(self.local)
+        if distributed and self.world > 1:
+            self.dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
+            self.distributed = True
+        self.mx.lib()
+        for kv in self.args.tune:
+            k, v = kv.split("=")
+            self.mx.set_tuning(k, int(v))
+        self.stream = torch.cuda.current_stream()
+        self.sp = self.stream.cuda_stream or None
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.distributed:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, v):
+        if self.distributed:
+            t = self.torch.tensor([v], dtype=self.torch.float64, device="cuda")
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+            return float(t.item())
+        return v
+
+    def sum_over_ranks(self, v):
+        if self.distributed:
+            t = self.torch.tensor([v], dtype=self.torch.float64, device="cuda")
+            self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+            return float(t.item())
+        return v
+
+    def event_ms(self, fn, n):
+        """Device time of n calls of fn(i), CUDA events on the launching stream."""
+        torch = self.torch
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(self.stream)
+        for i in range(n):
+            fn(i)
+        e1.record(self.stream)
+        e1.synchronize()
+        return e0.elapsed_time(e1)
+
+
+class Job:
+    """This rank's rows of one workload: alternating buffer sets and the step function."""
+
+    def __init__(self, env, w, rows, row0, mods=None, chain="dropin", impl="mxk"):
+        from miroxen_b200.workloads import BlockBuffers, make_mods, rope_tables_for
+        torch = env.torch
+        self.env, self.w, self.rows, self.row0, self.impl = env, w, rows, row0, impl
+        self.prefix_rows = w.prefix_rows - row0
+        if mods is None:
+            # made on every rank from the same seed, then broadcast from rank 0 once (set-up, untimed)
+            mods = make_mods(w, seed=1000, device="cuda")
+            if env.distributed:
+                from miroxen_b200 import sharding
+                sharding.broadcast_modulation(list(mods.values()), src=0)
+        self.mods = mods
+        cos, sin = rope_tables_for(w)
+        if cos is not None:
+            cos, sin = cos[row0:row0 + rows].contiguous(), sin[row0:row0 + rows].contiguous()
+        self.cos, self.sin = cos, sin
+        one = BlockBuffers(w, rows, self.prefix_rows, seed=0, mods=mods, cos=cos, sin=sin)
+        # enough sets that a set is long gone from the 126 MB L2 when its turn comes again
+        self.n_sets = max(2, math.ceil(3.2 * L2_BYTES / max(one.nbytes(), 1)))
+        self.sets = [one] + [BlockBuffers(w, rows, self.prefix_rows, seed=s, mods=mods, cos=cos, sin=sin)
+                             for s in range(1, self.n_sets)]
+        self.set_chain(chain)
+        self.graphs, self.per_replay = None, 0
+        if impl != "mxk":
+            self.runners = [ref_cuda_chain(w, b, env.sp) for b in self.sets]
+
+    def set_chain(self, chain):
+        self.chain = chain
+        for b in self.sets:
+            b.args.fused = 1 if chain == "fused" else 0
+
+    def capture_graphs(self):
+        env, torch, mx = self.env, self.env.torch, self.env.mx
+        for b in self.sets:
+            mx.dit_block_ops(b.args, env.stream)  # eager warm-up: resolves the per-device caches
+        torch.cuda.synchronize()
+        cap = torch.cuda.Stream()
+        cap.wait_stream(env.stream)
+        self.graphs = []
+        for b in self.sets:
+            g = torch.cuda.CUDAGraph()
+            mx.reset_launch_count()
+            with torch.cuda.graph(g, stream=cap):
+                mx.dit_block_ops(b.args)
+            self.per_replay = mx.launch_count()
+            self.graphs.append(g)
+        torch.cuda.synchronize()
+
+    def step(self, i):
+        if self.impl != "mxk":
+            self.runners[i % self.n_sets]()
+        elif self.graphs:
+            self.graphs[i % self.n_sets].replay()
+        else:
+            self.env.mx.dit_block_ops(self.sets[i % self.n_sets].args, self.env.stream)
+
+    def set_bytes(self):
+        return self.sets[0].nbytes()
+
+    def timed(self, K, warm, repeats=0, clocks=False):
+        """`repeats` windows of exactly K steps each (barrier + synchronize either side of every window,
+        max over ranks per window).  Returns (median ms per step, stats, launches per window, clock summary)."""
+        env = self.env
+        for i in range(warm):
+            self.step(i)
+        env.barrier()
+        first = env.max_over_ranks(env.event_ms(self.step, K))
+        env.barrier()
+        R = repeats or int(min(60, max(5, math.ceil(MIN_TIMED_MS / max(first, 1e-3)))))
+        if env.distributed:  # every rank must run the same number of windows
+            R = int(env.max_over_ranks(float(R)))
+        windows, launches = [], 0
+        sampler = ClockSampler(env.local) if clocks else None
+        if sampler:
+            sampler.__enter__()
+        try:
+            for _ in range(R):
+                env.mx.reset_launch_count()
+                ms = env.event_ms(self.step, K)
+                launches = env.mx.launch_count() if not self.graphs else self.per_replay * K
+                env.barrier()
+                windows.append(env.max_over_ranks(ms) / K)
+        finally:
+            if sampler:
+                sampler.__exit__()
+        med = statistics.median(windows)
+        stats = {"repeats": R, "ms_per_step_min": round(min(windows), 4), "ms_per_step_max": round(max(windows), 4),
+                 "timed_ms_total": round(sum(windows) * K, 1)}
+        return med, stats, launches, (sampler.summary() if sampler else None)
+
+    def per_op(self, K, fused):
+        """Per-op device times inside a timed pass (events between the launches)."""
+        env, mx = self.env, self.env.mx
+        w = self.w
+        keep_chain = self.chain
+        ot = mx.OpTimes()
+        saved = []
+        for b in self.sets:
+            b.args.fused = fused
+            saved.append(b.args.chunk_rows)
+            b.args.chunk_rows = 0
+        acc = None
+        for i in range(3):
+            ot.run(self.sets[i % self.n_sets].args, env.stream)
+        env.barrier()
+        for i in range(K):
+            ot.run(self.sets[i % self.n_sets].args, env.stream)
+            t = ot.read()
+            acc = t if acc is None else [a + b for a, b in zip(acc, t)]
+        ot.close()
+        for b, c in zip(self.sets, saved):
+            b.args.chunk_rows = c
+        self.set_chain(keep_chain)
+        names = ["norm_mod", "qkv_norm_rope", "gated_residual_norm", "act", "gated_residual"] if fused else dropin_op_names(w)
+        ops = op_rows(w, names, [t / K * 1e3 for t in acc], self.rows, env.peak_gbs)
+        return {"us_per_block": round(sum(o["us"] for o in ops), 1), "ops": ops}
+
+    def close(self):
+        self.sets, self.graphs = [], None
+        if self.impl != "mxk":
+            self.runners = []
+        self.env.torch.cuda.empty_cache()
+
+
+def shard_of(w, n, rank, by):
+    from miroxen_b200 import sharding
+    if by == "frames" and w.frames:
+        return sharding.shard_frames(w.frames, w.rows_per_frame, w.rows - w.frames * w.rows_per_frame, n, rank)
+    return sharding.shard_rows(w.rows, n, rank)
+
+
+def quant_rows(env, job, K, impl):
+    """The step that follows these ops on the reference's fp8 / fp4 path: the activation block-scale
+    quantiser, timed on this block's norm output [rows, dim] and MLP activation [rows, F]."""
+    torch, mx = env.torch, env.mx
+    w, rows, sets, n_sets, stream, sp, peak_gbs = job.w, job.rows, job.sets, job.n_sets, env.stream, env.sp, env.peak_gbs
+    prefix_rows = job.prefix_rows
+
+    def time_us(fn):
+        for i in range(3):
+            fn(i)
+        env.barrier()
+        return env.event_ms(fn, K) / K * 1e3
+
+    if impl != "mxk":
+        from oracle import binding as orc
+        if not orc.have_ref_blockscale():
+            return {"unavailable": "oracle/_ref/libmx_ref_blockscale.so not built"}
+        import ctypes as C
+        L = orc.ref_blockscale()
+        L.ref_quantize_blockscaled.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
+                                               C.c_void_p, C.c_void_p, C.c_void_p]
+
+        def quant(mode, t, cols, out):
+            if L.ref_quantize_blockscaled(mode, t.data_ptr(), cols, rows, cols, out.q.data_ptr(), out.sf.data_ptr(),
+                                          out.amax.data_ptr() if out.amax is not None else None, sp):
+                raise RuntimeError("reference quantize_blockscaled failed")
+    else:
+        def quant(mode, t, cols, out):
+            mx.ops.quantize_blockscaled(mode, t, cols, rows, cols, out, stream)
+    q_ops = []
+    for mode, mname, per_el in ((mx.ops.Q_MXFP8, "mxfp8", 2 + 1 + 1 / 32), (mx.ops.Q_NVFP4, "nvfp4", 2 + 2 + 0.5 + 1 / 16)):
+        for src_name, cols in (("h1", w.dim), ("act", w.F)):
+            srcs = [getattr(b, src_name) for b in sets]
+            outs = [mx.ops.QMat(torch.empty(mx.ops.qdata_bytes(mode, rows, cols), dtype=torch.uint8, device="cuda"),
+                                torch.empty(mx.ops.qscale_bytes(mode, rows, cols), dtype=torch.uint8, device="cuda"),
+                                torch.empty(1, dtype=torch.float32, device="cuda") if mode == mx.ops.Q_NVFP4 else None)
+                    for _ in srcs]
+            us = time_us(lambda i: quant(mode, srcs[i % n_sets], cols, outs[i % n_sets]))
+            by = per_el * rows * cols
+            q_ops.append({"op": f"quantize_{mname}", "input": f"{src_name} [{rows}, {cols}]", "us": round(us, 2),
+                          "bytes": int(by), "gbs": round(by / us / 1e3, 1), "frac": round(by / us / 1e3 / peak_gbs, 3)})
+            del outs
+    res = {"quantize_blockscaled": q_ops,
+           "note": "bytes = bf16 read + codes + scales; nvfp4 reads the input twice (tensor amax first)"}
+    if impl != "mxk":
+        return res
+
+    def pair_us(one, two):
+        return round(time_us(one), 2), round(time_us(two), 2)
+
+    def mod(b, name):
+        return mx.row_mod(b.mods[name + "_t"], b.mods[name + "_p"], min(max(prefix_rows, 0), rows))
+
+    # the MLP activation and its quantisation in one pass, against the same two calls in a row
+    am = mx.ops.ACT_GELU_TANH if w.act_mode == 0 else mx.ops.ACT_SILU_MUL
+    srcs = [b.act if w.act_mode == 0 else b.act2 for b in sets]
+    outs = [mx.ops.act_quantize_mxfp8(am, t, rows, w.F, stream=stream) for t in srcs]
+    tmp = [b.act for b in sets]
+
+    def act_two(i):
+        if w.act_mode == 0:
+            mx.ops.gelu_tanh_inplace(tmp[i % n_sets], rows * w.F, stream)
+        else:
+            mx.ops.silu_mul(srcs[i % n_sets], rows, w.F, tmp[i % n_sets], stream)
+        mx.ops.quantize_blockscaled(mx.ops.Q_MXFP8, tmp[i % n_sets], w.F, rows, w.F, outs[i % n_sets], stream)
+
+    one, two = pair_us(lambda i: mx.ops.act_quantize_mxfp8(am, srcs[i % n_sets], rows, w.F, outs[i % n_sets], stream), act_two)
+    by = ((2 if w.act_mode == 0 else 4) + 1 + 1 / 32) * rows * w.F
+    res["act_quantize_mxfp8"] = {"act": "gelu_tanh" if w.act_mode == 0 else "silu_mul", "input": f"[{rows}, {w.F}]",
+                                 "us": one, "us_two_calls": two, "bytes": int(by), "gbs": round(by / one / 1e3, 1),
+                                 "frac": round(by / one / 1e3 / peak_gbs, 3)}
+    del outs
+    # the block's first norm and its quantisation in one pass, against the two calls
+    nouts = [mx.ops.QMat(torch.empty(rows * w.dim, dtype=torch.uint8, device="cuda"),
+                         torch.empty(mx.ops.qscale_bytes(1, rows, w.dim), dtype=torch.uint8, device="cuda")) for _ in sets]
+
+    def norm_one(i):
+        b = sets[i % n_sets]
+        if w.norm_mode == 0:
+            mx.ops.layernorm_mod_quant_mxfp8(b.x, rows, w.dim, 1e-6, mod(b, "scale1"), mod(b, "shift1"), nouts[i % n_sets], stream)
+        else:
+            mx.ops.rmsnorm_mod_quant_mxfp8(b.x, rows, w.dim, 1e-6, b.mods["norm1_w"], mod(b, "scale1"), mod(b, "shift1"), nouts[i % n_sets], stream)
+
+    def norm_two(i):
+        b = sets[i % n_sets]
+        if w.norm_mode == 0:
+            mx.ops.layernorm_mod(b.x, rows, w.dim, 1e-6, mod(b, "scale1"), mod(b, "shift1"), b.h1, stream)
+        else:
+            mx.ops.rmsnorm_mod(b.x, rows, w.dim, 1e-6, b.mods["norm1_w"], mod(b, "scale1"), mod(b, "shift1"), b.h1, stream)
+        mx.ops.quantize_blockscaled(mx.ops.Q_MXFP8, b.h1, w.dim, rows, w.dim, nouts[i % n_sets], stream)
+
+    one, two = pair_us(norm_one, norm_two)
+    by = (4 + 1 + 1 / 32) * rows * w.dim
+    res["norm_mod_quant_mxfp8"] = {"norm": "layernorm" if w.norm_mode == 0 else "rmsnorm", "input": f"[{rows}, {w.dim}]",
+                                   "us": one, "us_two_calls": two, "bytes": int(by), "gbs": round(by / one / 1e3, 1),
+                                   "frac": round(by / one / 1e3 / peak_gbs, 3)}
+    # bias add folded into the op that reads the GEMM output next, against add_bias_bf16 + the plain op
+    bias_f = torch.randn(2 * w.F, device="cuda") * 0.1
+    bias_d = torch.randn(w.dim, device="cuda") * 0.1
+
+    def fold(one_fn, two_fn, bytes_one):
+        a, b2 = pair_us(one_fn, two_fn)
+        return {"us": a, "us_two_calls": b2, "bytes": int(bytes_one), "gbs": round(bytes_one / a / 1e3, 1),
+                "frac": round(bytes_one / a / 1e3 / peak_gbs, 3)}
+
+    if w.act_mode == 0:
+        a_one = lambda i: mx.ops.bias_gelu_tanh_inplace(sets[i % n_sets].act, bias_f, rows, w.F, stream)
+
+        def a_two(i):
+            mx.ops.add_bias_bf16(sets[i % n_sets].act, bias_f, rows, w.F, stream)
+            mx.ops.gelu_tanh_inplace(sets[i % n_sets].act, rows * w.F, stream)
+        act_bytes = 4 * rows * w.F
+    else:
+        a_one = lambda i: mx.ops.bias_silu_mul(sets[i % n_sets].act2, bias_f, rows, w.F, sets[i % n_sets].act, stream)
+
+        def a_two(i):
+            mx.ops.add_bias_bf16(sets[i % n_sets].act2, bias_f, rows, 2 * w.F, stream)
+            mx.ops.silu_mul(sets[i % n_sets].act2, rows, w.F, sets[i % n_sets].act, stream)
+        act_bytes = 6 * rows * w.F
+    r_one = lambda i: mx.ops.gated_residual_bias(sets[i % n_sets].x, sets[i % n_sets].attn_o, bias_d, rows, w.dim,
+                                                 mod(sets[i % n_sets], "gate1"), w.gate_tanh, stream)
+
+    def r_two(i):
+        b = sets[i % n_sets]
+        mx.ops.add_bias_bf16(b.attn_o, bias_d, rows, w.dim, stream)
+        mx.ops.gated_residual(b.x, b.attn_o, rows, w.dim, mod(b, "gate1"), w.gate_tanh, stream)
+    res["bias_folding"] = {"act": dict(op="bias + " + ("gelu_tanh" if w.act_mode == 0 else "silu_mul"), **fold(a_one, a_two, act_bytes)),
+                           "gated_residual": dict(op="bias + gated_residual", **fold(r_one, r_two, 10 * rows * w.dim))}
+    return res
+
+
+def reference_cuda_record(env, job, K):
+    """The reference's own kernels (src/kernels/ops.cu and blockscale.cu rebuilt for sm_100a) on this job's
+    buffers with the same event method: block time, per op, and its quantiser."""
+    from oracle import binding as orc
+    if not orc.have_ref_ops():
+        return {"unavailable": "oracle/_ref/libmx_ref_ops.so not built (needs the reference tree at build time)"}
+    torch, w = env.torch, job.w
+    runners = [ref_cuda_chain(w, b, env.sp) for b in job.sets]
+    step = lambda i: runners[i % job.n_sets]()
+    for i in range(3):
+        step(i)
+    env.barrier()
+    windows = [env.event_ms(step, K) / K for _ in range(3)]
+    ms = statistics.median(windows)
+    # per op: events between its launches
+    evs = []
+
+    def mark():
+        e = torch.cuda.Event(enable_timing=True)
+        e.record(env.stream)
+        evs.append(e)
+    marked = [ref_cuda_chain(w, b, env.sp, mark) for b in job.sets]
+    names = dropin_op_names(w)
+    acc = [0.0] * len(names)
+    n_pass = min(K, 10)
+    for i in range(n_pass):
+        evs.clear()
+        marked[i % job.n_sets]()
+        torch.cuda.synchronize()
+        for j in range(len(names)):
+            acc[j] += evs[j].elapsed_time(evs[j + 1])
+    ops = op_rows(w, names, [t / n_pass * 1e3 for t in acc], job.rows, env.peak_gbs)
+    by = w.bytes_per_row() * job.rows
+    rec = {"what": "the reference's src/kernels/ops.cu rebuilt for sm_100a, same device buffers, same event timing",
+           "us_per_block": round(ms * 1e3, 1), "gbs": round(by / (ms * 1e-3) / 1e9, 1),
+           "frac_of_hbm_peak": round(by / (ms * 1e-3) / 1e9 / env.peak_gbs, 4), "launches_per_block": len(names), "per_op": ops}
+    q = quant_rows(env, job, K, "reference-cuda")
+    rec["quantize_blockscaled"] = q.get("quantize_blockscaled", q)
+    return rec
+
+
+def e2e_mxk(env, w, rows, row0, mods, chain, cos, sin, K, total_bytes):
+    """End to end through the public host-buffer call: pinned host buffers in, results back in host
+    memory, every step; wall clock between synchronizes, max over ranks."""
+    from miroxen_b200.workloads import BlockBuffers
+    args, mx, torch = env.args, env.mx, env.torch
+    hb = BlockBuffers(w, rows, w.prefix_rows - row0, seed=7, mods=mods, cos=cos, sin=sin, host=True)
+    hb.args.fused = 1 if chain == "fused" else 0
+    pipe = mx.HostPipeline(args.e2e_chunk_rows, w.dim, w.F, w.H, w.D, w.rot, with_v=w.packed_qkv, act_mode=w.act_mode)
+    up = down = 0
+    for _ in range(2):
+        up, down = pipe.run(hb.args)
+    env.barrier()
+    Ke = max(3, min(K, 10))
+    t0 = time.perf_counter()
+    for _ in range(Ke):
+        pipe.run(hb.args)
+    torch.cuda.synchronize()
+    dt = env.max_over_ranks((time.perf_counter() - t0) / Ke)
+    env.barrier()
+    pipe.close()
+    up_all, down_all = env.sum_over_ranks(float(up)), env.sum_over_ranks(float(down))
+    return {"value": round(total_bytes / dt / 1e9, 2), "unit": UNIT, "ms_per_step": round(dt * 1e3, 3),
+            "h2d_bytes_per_step": int(up_all), "d2h_bytes_per_step": int(down_all), "steps": Ke,
+            "bytes_note": "summed over the ranks' copies",
+            "api": f"mxk_dit_block_ops_host (pinned host buffers, {args.e2e_chunk_rows}-row chunks, 3 streams per GPU)"}
+
+
+def e2e_reference(env, job, K):
+    """The reference's kernels fed from pinned host buffers the plain way: upload every input, run
+    its launchers, download every output, on one stream (its API has no host-buffer entry point)."""
+    from miroxen_b200.workloads import BlockBuffers
+    torch, w = env.torch, job.w
+    hb = BlockBuffers(w, job.rows, job.prefix_rows, seed=7, mods=job.mods, cos=job.cos, sin=job.sin, host=True)
+    db = job.sets[0]
+    ins = ["x", "attn_o", "mlp_o", "cos", "sin"] + (["qkv"] if w.packed_qkv else ["q_in", "k_in"]) + (["act"] if w.act_mode == 0 else ["act2"])
+    outs = ["h1", "q_out", "k_out", "h2", "act", "x"] + (["v_out"] if w.packed_qkv else [])
+    run = ref_cuda_chain(w, db, env.sp)
+    up = sum(getattr(hb, k).numel() * getattr(hb, k).element_size() for k in ins)
+    down = sum(getattr(hb, k).numel() * getattr(hb, k).element_size() for k in outs)
+
+    def step():
+        for k in ins:
+            getattr(db, k).copy_(getattr(hb, k), non_blocking=True)
+        run()
+        for k in outs:
+            getattr(hb, k).copy_(getattr(db, k), non_blocking=True)
+        torch.cuda.synchronize()
+    for _ in range(2):
+        step()
+    Ke = max(3, min(K, 10))
+    t0 = time.perf_counter()
+    for _ in range(Ke):
+        step()
+    dt = (time.perf_counter() - t0) / Ke
+    return {"value": round(w.bytes_per_row() * job.rows / dt / 1e9, 2), "unit": UNIT, "ms_per_step": round(dt * 1e3, 3),
+            "h2d_bytes_per_step": int(up), "d2h_bytes_per_step": int(down), "steps": Ke,
+            "api": "pinned host buffers -> cudaMemcpyAsync -> the reference's launchers -> cudaMemcpyAsync, one stream"}
+
+
+def run_reference_cuda(args, W):
+    """--impl reference: the reference's own implementation of this path is CUDA (src/kernels/ops.cu), so
+    this arm runs those kernels, rebuilt unmodified for sm_100a (oracle/_ref), on one GPU over the whole
+    workload; the CPU restatement is reported beside it as `cpu_baseline`."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import binding as orc
+    if not orc.have_ref_ops():
+        if args.impl == "reference-cuda":
+            print(json.dumps({"impl": "reference", "unavailable": "oracle/_ref/libmx_ref_ops.so not built (needs the reference tree at build time)"}), flush=True)
+            return
+        return run_reference_cpu(args, W, why="oracle/_ref/libmx_ref_ops.so (the reference's CUDA kernels) is absent: "
+                                              "the CPU restatement was timed instead")
+    env = Env(args)
+    env.start(distributed=False)
+    w = W[args.workload]
+    K, Wm = max(args.steps, 1), max(args.warmup, 3)
+    job = Job(env, w, w.rows, 0, chain="dropin", impl="reference-cuda")
+    ms, stats, _, clocks = job.timed(K, Wm, args.repeats, clocks=True)
+    by = w.bytes_per_row() * w.rows
+    scaling = args.scaling or ("strong" if args.gpus > 1 else "weak")
+    n_launch = len(dropin_op_names(w))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(by / (ms * 1e-3) / 1e9, 1), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": K, "warmup": Wm, "ms_per_step": round(ms, 4), "us_per_block": round(ms * 1e3, 1), "higher_is_better": True,
+        "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": job_config(w, "dropin", args.gpus, scaling, args.shard or "rows"),
+        "reference_kind": "the reference's CUDA kernels (src/kernels/ops.cu, unmodified, rebuilt for sm_100a), one GPU, "
+                          "the whole workload" + ("; the other ranks of this launch do no work" if args.gpus > 1 else ""),
+        "timing": stats, "frac_of_hbm_peak": round(by / (ms * 1e-3) / 1e9 / env.peak_gbs, 4), "hbm_peak_gbs": env.peak_gbs,
+        "hbm_peak_source": env.peak_src, "clocks": clocks, "gpu_launches": n_launch * K,
+    }
+    if not args.no_extras:
+        rec = reference_cuda_record(env, job, min(K, 20))
+        line["per_op"] = {"dropin": {"us_per_block": round(sum(o["us"] for o in rec["per_op"]), 1), "ops": rec["per_op"]}}
+        line["next_rows"] = {"quantize_blockscaled": rec["quantize_blockscaled"]}
+    if not args.no_e2e:
+        line["e2e"] = e2e_reference(env, job, K)
+    job.close()
+    if not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(w, args.cpu_rows or min(w.rows, 1088), 3)
+    print(json.dumps(line), flush=True)
+
+
+def strong_record(env, w, K, splits):
+    """Strong scaling of one workload inside this run: the whole workload on one GPU (every rank runs it,
+    max over ranks), then each split of its rows over the ranks.  Times are ms per block, max over ranks."""
+    world, rank = env.world, env.rank
+    rec = {"workload": w.name, "rows": w.rows, "n_gpus": world, "chains": {}}
+    whole = Job(env, w, w.rows, 0)
+    base = {}
+    for chain in ("dropin", "fused"):
+        whole.set_chain(chain)
+        base[chain], _, _, _ = whole.timed(K, 3, repeats=3)
+    mods = whole.mods
+    whole.close()
+    for by in splits:
+        sh = shard_of(w, world, rank, by)
+        job = Job(env, w, sh.rows, sh.row0, mods=mods)
+        rows_max = int(env.max_over_ranks(float(sh.rows)))
+        entry = {"rows_per_gpu_max": rows_max, "ceiling": round(w.rows / rows_max, 2)}
+        for chain in ("dropin", "fused"):
+            job.set_chain(chain)
+            ms, _, _, _ = job.timed(K, 3, repeats=5)
+            entry[chain] = {"ms_per_block": round(ms, 4), "ms_per_block_1gpu": round(base[chain], 4),
+                            "speedup": round(base[chain] / ms, 2),
+                            "gbs": round(w.bytes_per_row() * w.rows / (ms * 1e-3) / 1e9, 1)}
+        rec["chains"][by] = entry
+        job.close()
+    rec["note"] = ("speedup = this run's 1-GPU ms_per_block / the sharded ms_per_block; `ceiling` = rows / the largest shard "
+                   "(a by-frame split of 21 frames over 8 GPUs is 3,3,3,3,3,2,2,2 frames: at most 7.11x)")
+    return rec
+
 
 def main():
     args = parse()
     from miroxen_b200.workloads import WORKLOADS as W
     if args.workload not in W:
         raise SystemExit(f"unknown workload {args.workload}; one of {sorted(W)}")
-    if args.impl == "reference":
+    if args.impl == "reference-cpu":
         return run_reference_cpu(args, W)
+    if args.impl in ("reference", "reference-cuda"):
+        return run_reference_cuda(args, W)
 
-    import torch
-    import torch.distributed as dist
-    import miroxen_b200 as mx
-    from miroxen_b200 import rope_tables, sharding
-    from miroxen_b200.workloads import BlockBuffers, make_mods
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    if args.impl == "reference-cuda" and rank != 0:
-        return
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
-    torch.cuda.set_device(local)
-    if world > 1 and args.impl == "mxk":
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    mx.lib()
-    for kv in args.tune:
-        k, v = kv.split("=")
-        mx.set_tuning(k, int(v))
+    env = Env(args)
+    env.start(distributed=True)
+    mx, torch = env.mx, env.torch
+    world, rank = env.world, env.rank
     w = W[args.workload]
-    n_gpus = world if args.impl == "mxk" else 1
+    n_gpus = world
+    scaling = args.scaling or ("strong" if n_gpus > 1 else "weak")
+    shard_by = args.shard or "rows"
+    K, Wm = max(args.steps, 1), max(args.warmup, 3)
 
     # rows of this rank
-    if args.scaling == "strong" and n_gpus > 1:
-        if w.frames and args.shard == "frames":
-            sh = sharding.shard_frames(w.frames, w.rows_per_frame, w.rows - w.frames * w.rows_per_frame, n_gpus, rank)
-        else:
-            sh = sharding.shard_rows(w.rows, n_gpus, rank)
+    if scaling == "strong" and n_gpus > 1:
+        sh = shard_of(w, n_gpus, rank, shard_by)
         rows, row0 = sh.rows, sh.row0
     else:
         rows, row0 = w.rows, 0
-    prefix_rows = w.prefix_rows - row0
-    total_rows = w.rows * (n_gpus if args.scaling == "weak" else 1)
-
-    # modulation vectors: made on rank 0, broadcast once (set-up, untimed); no collective afterwards
-    mods = make_mods(w, seed=1000, device="cuda")
-    if world > 1 and args.impl == "mxk":
-        sharding.broadcast_modulation(list(mods.values()), src=0)
-
-    # rotary tables for the job's row order, sliced to this rank's rows
-    cos = sin = None
-    if w.name.startswith("qwen") and not w.packed_qkv:
-        n_img = {"qwen1024": (64, 64, 256, 2), "qwen512": (32, 32, 128, 1), "qwen2048": (128, 128, 512, 1),
-                 "qwen21_true": None}.get(w.name)
-        if n_img:
-            ih, iw, nt, batch = n_img
-            c1, s1 = rope_tables.qwen_rope_table([("image", ih, iw), ("text", nt)])
-            order = [c1[:ih * iw]] * batch + [c1[ih * iw:]] * batch
-            order_s = [s1[:ih * iw]] * batch + [s1[ih * iw:]] * batch
-            cos, sin = torch.cat(order)[row0:row0 + rows].contiguous(), torch.cat(order_s)[row0:row0 + rows].contiguous()
-
-    n_sets = 2  # two buffer sets, used alternately; every step streams far more than the 126 MB L2
-    sets = [BlockBuffers(w, rows, prefix_rows, seed=s, mods=mods, cos=cos, sin=sin) for s in range(n_sets)]
-    for b in sets:
-        b.args.fused = 1 if args.chain == "fused" else 0
-    stream = torch.cuda.current_stream()
-    sp = stream.cuda_stream or None
-
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1 and args.impl == "mxk":
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def max_over_ranks(v):
-        if world > 1 and args.impl == "mxk":
-            t = torch.tensor([v], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item())
-        return v
-
-    if args.impl == "reference-cuda":
-        runners = [ref_cuda_chain(w, b, sp) for b in sets]
-        step = lambda i: runners[i % n_sets]()
-    elif args.graph:
-        # one graph per buffer set, captured after an eager warm-up call (which resolves the per-device caches)
-        graphs, per_replay = [], 0
-        for b in sets:
-            mx.dit_block_ops(b.args, stream)
-        torch.cuda.synchronize()
-        cap = torch.cuda.Stream()
-        cap.wait_stream(stream)
-        for b in sets:
-            g = torch.cuda.CUDAGraph()
-            mx.reset_launch_count()
-            with torch.cuda.graph(g, stream=cap):
-                mx.dit_block_ops(b.args)
-            per_replay = mx.launch_count()
-            graphs.append(g)
-        torch.cuda.synchronize()
-        step = lambda i: graphs[i % n_sets].replay()
-    else:
-        step = lambda i: mx.dit_block_ops(sets[i % n_sets].args, stream)
-
-    def timed(step_fn, K, Wm):
-        for i in range(Wm):
-            step_fn(i)
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        mx.reset_launch_count()
-        with ClockSampler(local) as cs:
-            e0.record(stream)
-            for i in range(K):
-                step_fn(i)
-            e1.record(stream)
-            barrier()
-        launches = mx.launch_count() if not (args.graph and args.impl == "mxk") else per_replay * K
-        return max_over_ranks(e0.elapsed_time(e1)) / K, launches, cs.summary()
-
-    def quant_rows():
-        """The step that follows these ops on the reference's fp8 / fp4 path: the activation block-scale
-        quantiser, timed on this block's norm output [rows, dim] and MLP activation [rows, F]."""
-        if args.impl == "reference-cuda":
-            from oracle import binding as orc
-            if not orc.have_ref_blockscale():
-                return {"unavailable": "oracle/_ref/libmx_ref_blockscale.so not built"}
-            import ctypes as C
-            L = orc.ref_blockscale()
-            L.ref_quantize_blockscaled.argtypes = [C.c_int, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p,
-                                                   C.c_void_p, C.c_void_p, C.c_void_p]
-
-            def quant(mode, t, cols, out):
-                if L.ref_quantize_blockscaled(mode, t.data_ptr(), cols, rows, cols, out.q.data_ptr(), out.sf.data_ptr(),
-                                              out.amax.data_ptr() if out.amax is not None else None, sp):
-                    raise RuntimeError("reference quantize_blockscaled failed")
-        else:
-            def quant(mode, t, cols, out):
-                mx.ops.quantize_blockscaled(mode, t, cols, rows, cols, out, stream)
-        q_ops = []
-        for mode, mname, per_el in ((mx.ops.Q_MXFP8, "mxfp8", 2 + 1 + 1 / 32), (mx.ops.Q_NVFP4, "nvfp4", 2 + 2 + 0.5 + 1 / 16)):
-            for src_name, cols in (("h1", w.dim), ("act", w.F)):
-                srcs = [getattr(b, src_name) for b in sets]
-                outs = [mx.ops.QMat(torch.empty(mx.ops.qdata_bytes(mode, rows, cols), dtype=torch.uint8, device="cuda"),
-                                    torch.empty(mx.ops.qscale_bytes(mode, rows, cols), dtype=torch.uint8, device="cuda"),
-                                    torch.empty(1, dtype=torch.float32, device="cuda") if mode == mx.ops.Q_NVFP4 else None)
-                        for _ in srcs]
-                for i in range(3):
-                    quant(mode, srcs[i % n_sets], cols, outs[i % n_sets])
-                barrier()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                for i in range(K):
-                    quant(mode, srcs[i % n_sets], cols, outs[i % n_sets])
-                e1.record(stream)
-                barrier()
-                us = e0.elapsed_time(e1) / K * 1e3
-                by = per_el * rows * cols
-                q_ops.append({"op": f"quantize_{mname}", "input": f"{src_name} [{rows}, {cols}]", "us": round(us, 2),
-                              "bytes": int(by), "gbs": round(by / us / 1e3, 1), "frac": round(by / us / 1e3 / peak_gbs, 3)})
-                del outs
-        res = {"quantize_blockscaled": q_ops,
-               "note": "bytes = bf16 read + codes + scales; nvfp4 reads the input twice (tensor amax first)"}
-        if args.impl == "mxk":
-            # the MLP activation and its quantisation in one pass, against the same two calls in a row
-            am = mx.ops.ACT_GELU_TANH if w.act_mode == 0 else mx.ops.ACT_SILU_MUL
-            srcs = [b.act if w.act_mode == 0 else b.act2 for b in sets]
-            outs = [mx.ops.act_quantize_mxfp8(am, t, rows, w.F, stream=stream) for t in srcs]
-            tmp = [b.act for b in sets]
-
-            def fused(i):
-                mx.ops.act_quantize_mxfp8(am, srcs[i % n_sets], rows, w.F, outs[i % n_sets], stream)
-
-            def separate(i):
-                if w.act_mode == 0:
-                    mx.ops.gelu_tanh_inplace(tmp[i % n_sets], rows * w.F, stream)
-                else:
-                    mx.ops.silu_mul(srcs[i % n_sets], rows, w.F, tmp[i % n_sets], stream)
-                mx.ops.quantize_blockscaled(mx.ops.Q_MXFP8, tmp[i % n_sets], w.F, rows, w.F, outs[i % n_sets], stream)
-
-            pair = {}
-            for name, fn in (("one_call", fused), ("two_calls", separate)):
-                for i in range(3):
-                    fn(i)
-                barrier()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                for i in range(K):
-                    fn(i)
-                e1.record(stream)
-                barrier()
-                pair[name] = round(e0.elapsed_time(e1) / K * 1e3, 2)
-            by = ((2 if w.act_mode == 0 else 4) + 1 + 1 / 32) * rows * w.F
-            res["act_quantize_mxfp8"] = {"act": "gelu_tanh" if w.act_mode == 0 else "silu_mul", "input": f"[{rows}, {w.F}]",
-                                         "us": pair["one_call"], "us_two_calls": pair["two_calls"], "bytes": int(by),
-                                         "gbs": round(by / pair["one_call"] / 1e3, 1),
-                                         "frac": round(by / pair["one_call"] / 1e3 / peak_gbs, 3)}
-            # the block's first norm and its quantisation in one pass, against the two calls
-            bsets = sets
-            nouts = [mx.ops.QMat(torch.empty(rows * w.dim, dtype=torch.uint8, device="cuda"),
-                                 torch.empty(mx.ops.qscale_bytes(1, rows, w.dim), dtype=torch.uint8, device="cuda")) for _ in bsets]
-
-            def mod(b, name):
-                return mx.row_mod(b.mods[name + "_t"], b.mods[name + "_p"], min(max(prefix_rows, 0), rows))
-
-            def norm_one(i):
-                b = bsets[i % n_sets]
-                if w.norm_mode == 0:
-                    mx.ops.layernorm_mod_quant_mxfp8(b.x, rows, w.dim, 1e-6, mod(b, "scale1"), mod(b, "shift1"), nouts[i % n_sets], stream)
-                else:
-                    mx.ops.rmsnorm_mod_quant_mxfp8(b.x, rows, w.dim, 1e-6, b.mods["norm1_w"], mod(b, "scale1"), mod(b, "shift1"), nouts[i % n_sets], stream)
-
-            def norm_two(i):
-                b = bsets[i % n_sets]
-                if w.norm_mode == 0:
-                    mx.ops.layernorm_mod(b.x, rows, w.dim, 1e-6, mod(b, "scale1"), mod(b, "shift1"), b.h1, stream)
-                else:
-                    mx.ops.rmsnorm_mod(b.x, rows, w.dim, 1e-6, b.mods["norm1_w"], mod(b, "scale1"), mod(b, "shift1"), b.h1, stream)
-                mx.ops.quantize_blockscaled(mx.ops.Q_MXFP8, b.h1, w.dim, rows, w.dim, nouts[i % n_sets], stream)
-
-            pair = {}
-            for name, fn in (("one_call", norm_one), ("two_calls", norm_two)):
-                for i in range(3):
-                    fn(i)
-                barrier()
-                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                e0.record(stream)
-                for i in range(K):
-                    fn(i)
-                e1.record(stream)
-                barrier()
-                pair[name] = round(e0.elapsed_time(e1) / K * 1e3, 2)
-            # bias add folded into the op that reads the GEMM output next, against add_bias_bf16 + the plain op
-            bias_f = torch.randn(2 * w.F, device="cuda") * 0.1
-            bias_d = torch.randn(w.dim, device="cuda") * 0.1
-
-            def fold(one, two, bytes_one):
-                t = {}
-                for name, fn in (("one_call", one), ("two_calls", two)):
-                    for i in range(3):
-                        fn(i)
-                    barrier()
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    e0.record(stream)
-                    for i in range(K):
-                        fn(i)
-                    e1.record(stream)
-                    barrier()
-                    t[name] = round(e0.elapsed_time(e1) / K * 1e3, 2)
-                return {"us": t["one_call"], "us_two_calls": t["two_calls"], "bytes": int(bytes_one),
-                        "gbs": round(bytes_one / t["one_call"] / 1e3, 1), "frac": round(bytes_one / t["one_call"] / 1e3 / peak_gbs, 3)}
-
-            if w.act_mode == 0:
-                a_one = lambda i: mx.ops.bias_gelu_tanh_inplace(bsets[i % n_sets].act, bias_f, rows, w.F, stream)
-
-                def a_two(i):
-                    mx.ops.add_bias_bf16(bsets[i % n_sets].act, bias_f, rows, w.F, stream)
-                    mx.ops.gelu_tanh_inplace(bsets[i % n_sets].act, rows * w.F, stream)
-                act_bytes = 4 * rows * w.F
-            else:
-                a_one = lambda i: mx.ops.bias_silu_mul(bsets[i % n_sets].act2, bias_f, rows, w.F, bsets[i % n_sets].act, stream)
-
-                def a_two(i):
-                    mx.ops.add_bias_bf16(bsets[i % n_sets].act2, bias_f, rows, 2 * w.F, stream)
-                    mx.ops.silu_mul(bsets[i % n_sets].act2, rows, w.F, bsets[i % n_sets].act, stream)
-                act_bytes = 6 * rows * w.F
-            r_one = lambda i: mx.ops.gated_residual_bias(bsets[i % n_sets].x, bsets[i % n_sets].attn_o, bias_d, rows, w.dim,
-                                                         mod(bsets[i % n_sets], "gate1"), w.gate_tanh, stream)
-
-            def r_two(i):
-                b = bsets[i % n_sets]
-                mx.ops.add_bias_bf16(b.attn_o, bias_d, rows, w.dim, stream)
-                mx.ops.gated_residual(b.x, b.attn_o, rows, w.dim, mod(b, "gate1"), w.gate_tanh, stream)
-            res["bias_folding"] = {"act": dict(op="bias + " + ("gelu_tanh" if w.act_mode == 0 else "silu_mul"), **fold(a_one, a_two, act_bytes)),
-                                   "gated_residual": dict(op="bias + gated_residual", **fold(r_one, r_two, 10 * rows * w.dim))}
-            by = (4 + 1 + 1 / 32) * rows * w.dim
-            res["norm_mod_quant_mxfp8"] = {"norm": "layernorm" if w.norm_mode == 0 else "rmsnorm", "input": f"[{rows}, {w.dim}]",
-                                           "us": pair["one_call"], "us_two_calls": pair["two_calls"], "bytes": int(by),
-                                           "gbs": round(by / pair["one_call"] / 1e3, 1),
-                                           "frac": round(by / pair["one_call"] / 1e3 / peak_gbs, 3)}
-        return res
-
-    K, Wm = max(args.steps, 1), max(args.warmup, 3)
-    peaks = {}
-    pk = ROOT / "MEASURED_PEAKS.json"
-    if pk.exists():
-        peaks = json.loads(pk.read_text())
-    peak_gbs, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+    total_rows = w.rows * (n_gpus if scaling == "weak" else 1)
+    job = Job(env, w, rows, row0, chain=args.chain)
+    if args.graph:
+        job.capture_graphs()
 
     if args.quant_only:
         if rank == 0:
-            print(json.dumps({"impl": args.impl, "workload": w.name, "steps": K, "next_rows": quant_rows()}), flush=True)
+            print(json.dumps({"impl": args.impl, "workload": w.name, "steps": K, "next_rows": quant_rows(env, job, K, "mxk")}), flush=True)
         return
 
-    ms, launches, clocks = timed(step, K, Wm)
+    ms, stats, launches, clocks = job.timed(K, Wm, args.repeats, clocks=True)
     job_bytes = w.bytes_per_row() * total_rows
     value = job_bytes / (ms * 1e-3) / 1e9
+    rows_max = int(env.max_over_ranks(float(rows)))
 
     line = {
         "metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": n_gpus, "steps": K, "warmup": Wm,
         "ms_per_step": round(ms, 4), "us_per_block": round(ms * 1e3, 1), "higher_is_better": True,
-        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": w.name, "desc": w.desc, "rows_per_gpu": rows, "rows_total": total_rows, "dim": w.dim,
-                   "heads": f"{w.H}x{w.D}", "F": w.F, "chain": args.chain, "launch": "cuda graph replay" if args.graph else "stream launches (programmatic dependent launch)", "io_dtype": "bf16 activations, fp32 residual",
-                   "bytes_per_row": w.bytes_per_row(), "parallelism": (f"row-sharded x{n_gpus}" + (f" ({args.shard if w.frames else 'rows'})" if args.scaling == "strong" and n_gpus > 1 else "") + ", no collective in the loop"),
-                   "l2": f"{n_sets} alternating buffer sets, {sets[0].nbytes() / 1e6:.0f} MB each (> 126 MB L2)"},
-        "frac_of_hbm_peak": round(value / n_gpus / peak_gbs, 4), "hbm_peak_gbs": peak_gbs, "hbm_peak_source": peak_src,
+        "scaling": scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": job_config(w, args.chain, n_gpus, scaling, shard_by),
+        "layout": {"rows_per_gpu": rows_max, "rows_total": total_rows,
+                   "launch": "cuda graph replay" if args.graph else "stream launches (programmatic dependent launch)",
+                   "buffer_sets": job.n_sets, "set_mb": round(job.set_bytes() / 1e6)},
+        "timing": dict(stats, ms_x_sm_mhz=(round(ms * clocks["sm_mhz"], 1) if clocks and clocks.get("sm_mhz") else None),
+                       method="median over `repeats` windows of exactly `steps` steps, CUDA events on the launching "
+                              "stream, barrier + synchronize around every window, max over ranks per window"),
+        "frac_of_hbm_peak": round(value / n_gpus / env.peak_gbs, 4), "hbm_peak_gbs": env.peak_gbs, "hbm_peak_source": env.peak_src,
         "clocks": clocks, "gpu_launches": int(launches),
     }
-    if args.impl != "mxk":
-        line["impl"] = args.impl
-        line["gpu_launches"] = 7 * K if not w.packed_qkv else 8 * K
-        if not args.no_extras:
-            line["next_rows"] = quant_rows()
-        print(json.dumps(line), flush=True)
-        return
+    if scaling == "strong" and n_gpus > 1:
+        line["timing"]["speedup_ceiling"] = round(w.rows / rows_max, 2)
 
     if not args.no_extras:
-        # per-op device times inside a timed pass (events between the launches), both chains
-        ot = mx.OpTimes()
-        per_chain = {}
-        for fused in (0, 1):
-            for b in sets:
-                b.args.fused = fused
-                keep = b.args.chunk_rows
-                b.args.chunk_rows = 0
-            acc = None
-            for i in range(3):
-                ot.run(sets[i % n_sets].args, stream)
-            barrier()
-            for i in range(K):
-                ot.run(sets[i % n_sets].args, stream)
-                t = ot.read()
-                acc = t if acc is None else [a + b for a, b in zip(acc, t)]
-            names = (["norm_mod", "qkv_norm_rope", "gated_residual_norm", "act", "gated_residual"] if fused else
-                     ["norm_mod"] + ["head_norm_rope"] * (3 if w.packed_qkv else 2) + ["gated_residual", "norm_mod", "act", "gated_residual"])
-            ob = w.op_bytes(rows)
-            act_name = "gelu_tanh_inplace" if w.act_mode == 0 else "silu_mul"
-            ops = []
-            for nme, tot in zip(names, acc):
-                key = act_name if nme == "act" else nme
-                by = ob[key] if key != "head_norm_rope" else ob[key] + 2 * (w.rot // 2) * 4 * rows
-                us = tot / K * 1e3
-                ops.append({"op": key, "us": round(us, 2), "bytes": by, "gbs": round(by / us / 1e3, 1),
-                            "frac": round(by / us / 1e3 / peak_gbs, 3)})
-            per_chain["fused" if fused else "dropin"] = {"us_per_block": round(sum(o["us"] for o in ops), 1), "ops": ops}
-            for b in sets:
-                b.args.chunk_rows = keep
-        ot.close()
+        per_chain = {"dropin": job.per_op(K, 0), "fused": job.per_op(K, 1)}
         line["per_op"] = per_chain
         ops = per_chain[args.chain]["ops"]
         top = max(ops, key=lambda o: o["us"])
-        line["roofline"] = {"bound": "hbm", "kernel": top["op"], "achieved": top["gbs"], "peak": peak_gbs, "unit": "GB/s",
-                            "frac": round(top["gbs"] / peak_gbs, 4), "traffic": None, "peak_source": peak_src}
+        line["roofline"] = {"bound": "hbm", "kernel": top["op"], "achieved": top["gbs"], "peak": env.peak_gbs, "unit": "GB/s",
+                            "frac": round(top["gbs"] / env.peak_gbs, 4), "traffic": None, "peak_source": env.peak_src}
         tr = ROOT / "profiles" / "dram_traffic.json"
         if tr.exists():
             try:
-                t = json.loads(tr.read_text()).get(w.name, {}).get(top["op"])
+                doc = json.loads(tr.read_text())
+                t = doc.get(w.name, {}).get(top["op"])
                 if t:
                     line["roofline"]["traffic"] = int(t["bytes_per_row"] * rows)
+                    line["roofline"]["traffic_note"] = ("from the ncu capture named in profiles/dram_traffic.json, scaled by rows; "
+                                                        "a lower bound for writes (lines still in L2 when the launch ends are not counted)")
             except Exception:
                 pass
         # the other chain, clean timing
         other = "fused" if args.chain == "dropin" else "dropin"
-        for b in sets:
-            b.args.fused = 1 if other == "fused" else 0
-        ms2, l2, _ = timed(step, K, 3)
+        job.set_chain(other)
+        ms2, st2, l2, _ = job.timed(K, 3, repeats=5)
         line["other_chain"] = {"chain": other, "ms_per_step": round(ms2, 4), "value": round(job_bytes / (ms2 * 1e-3) / 1e9, 1),
-                               "gpu_launches": int(l2)}
-        for b in sets:
-            b.args.fused = 1 if args.chain == "fused" else 0
+                               "gpu_launches": int(l2), "ms_per_step_min": st2["ms_per_step_min"], "ms_per_step_max": st2["ms_per_step_max"]}
+        job.set_chain(args.chain)
 
     if not args.no_extras and n_gpus == 1:
-        line["next_rows"] = quant_rows()
+        line["next_rows"] = quant_rows(env, job, K, "mxk")
+        line["reference_cuda"] = reference_cuda_record(env, job, min(K, 20))
+        if "us_per_block" in line["reference_cuda"]:
+            line["reference_cuda"]["speedup_of_this_library"] = round(line["reference_cuda"]["us_per_block"] / (ms * 1e3), 2)
+
+    mods, cos, sin = job.mods, job.cos, job.sin
+    job.close()
+
+    if not args.no_extras and n_gpus == 1 and w.rows >= 8 * 64:
+        # the same chain at the row count one rank of an 8-GPU job owns: what strong scaling is limited by
+        sh8 = shard_of(w, 8, 0, shard_by)
+        small = Job(env, w, sh8.rows, 0, mods=mods, chain=args.chain)
+        ms8, _, _, _ = small.timed(K, 3, repeats=5)
+        line["shard_size"] = {"rows": sh8.rows, "of": "one rank of an 8-way row split", "us_per_block": round(ms8 * 1e3, 1),
+                              "speedup_if_all_ranks_match": round(ms / ms8, 2),
+                              "per_op": {"dropin": small.per_op(K, 0), "fused": small.per_op(K, 1)}}
+        small.set_chain("fused")
+        msf, _, _, _ = small.timed(K, 3, repeats=5)
+        line["shard_size"]["us_per_block_fused"] = round(msf * 1e3, 1)
+        small.close()
+
+    if not args.no_extras and n_gpus > 1 and scaling == "strong":
+        # BASELINE.json's video shape (sharded by frame, the reference's split, and by equal row ranges) and the 2048^2 image
+        line["video_strong"] = strong_record(env, W["h3video"], min(K, 20), ("frames", "rows"))
+        line["strong_records"] = [strong_record(env, W["qwen2048"], min(K, 20), ("rows",))]
+        # replicas of the main workload, for the per-GPU rate next to the sharded one
+        rep = Job(env, w, w.rows, 0, mods=mods, chain=args.chain)
+        msr, _, _, _ = rep.timed(K, 3, repeats=3)
+        line["replicas"] = {"ms_per_step": round(msr, 4), "value": round(w.bytes_per_row() * w.rows * n_gpus / (msr * 1e-3) / 1e9, 1),
+                            "speedup": round(msr / ms, 2)}
+        rep.close()
 
     if not args.no_e2e:
-        # end to end: pinned host buffers in, results back in host memory, every step
-        hb = BlockBuffers(w, rows, prefix_rows, seed=7, mods=mods, cos=cos, sin=sin, host=True)
-        hb.args.fused = 1 if args.chain == "fused" else 0
-        pipe = mx.HostPipeline(args.e2e_chunk_rows, w.dim, w.F, w.H, w.D, w.rot, with_v=w.packed_qkv, act_mode=w.act_mode)
-        up = down = 0
-        for _ in range(2):
-            up, down = pipe.run(hb.args)
-        barrier()
-        Ke = max(3, min(K, 10))
-        t0 = time.perf_counter()
-        for _ in range(Ke):
-            pipe.run(hb.args)
-        torch.cuda.synchronize()
-        dt = max_over_ranks((time.perf_counter() - t0) / Ke)
-        barrier()
-        pipe.close()
-        line["e2e"] = {"value": round(job_bytes / dt / 1e9, 2), "unit": UNIT, "ms_per_step": round(dt * 1e3, 3),
-                       "h2d_bytes_per_step": int(up) * (n_gpus if args.scaling == "weak" else 1),
-                       "d2h_bytes_per_step": int(down) * (n_gpus if args.scaling == "weak" else 1), "steps": Ke,
-                       "api": f"mxk_dit_block_ops_host (pinned host buffers, {args.e2e_chunk_rows}-row chunks, 3 streams)"}
-        del hb
+        line["e2e"] = e2e_mxk(env, w, rows, row0, mods, args.chain, cos, sin, K, job_bytes)
 
     if rank == 0 and n_gpus == 1 and not args.no_cpu_baseline:
-        threads = host_threads()
-        crow = args.cpu_rows or min(w.rows, 2176)
-        sec = cpu_block(w, crow, min(w.prefix_rows, crow * w.prefix_rows // w.rows), threads, 3)
-        line["cpu_baseline"] = {"value": round(w.bytes_per_row() * crow / sec / 1e9, 3), "unit": UNIT, "cores": threads,
-                                "kind": "port", "sample": f"{crow} of {w.rows} rows, every op of the block, median of 3 passes",
-                                "ms_per_block_scaled": round(sec * 1e3 * w.rows / crow, 2)}
+        line["cpu_baseline"] = cpu_baseline(w, args.cpu_rows or min(w.rows, 2176), 3)
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    if env.distributed:
+        env.dist.destroy_process_group()
 
 
 if __name__ == "__main__":

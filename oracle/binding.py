@@ -23,11 +23,24 @@ class QwenSeg(C.Structure):
     _fields_ = [("is_text", C.c_int32), ("pad", C.c_int32), ("len", C.c_int64), ("ih", C.c_int64), ("iw", C.c_int64)]
 
 
+def reference_root() -> Path:
+    """Where the reference tree is expected: the Makefile's REF variable (environment REF, or its default)."""
+    import os
+    env = os.environ.get("REF")
+    if env:
+        return Path(env)
+    for line in (HERE / "Makefile").read_text().splitlines():
+        if line.startswith("REF ?="):
+            return Path(line.split("?=", 1)[1].strip())
+    raise RuntimeError("oracle/Makefile has no REF default")
+
+
 def build(ref: bool = True) -> None:
     """Compiles the oracle (and, when the reference tree is present, oracle/_ref)."""
     subprocess.run(["make", "-s", "-C", str(HERE), "all"], check=True)
-    if ref and Path("/root/reference/src/kernels/ops.cu").exists():
-        subprocess.run(["make", "-s", "-C", str(HERE), "_ref"], check=True)
+    root = reference_root()
+    if ref and (root / "src" / "kernels" / "ops.cu").exists():
+        subprocess.run(["make", "-s", "-C", str(HERE), "_ref", f"REF={root}"], check=True)
 
 
 _libs: dict[str, C.CDLL] = {}
@@ -81,6 +94,16 @@ def ref_ops() -> C.CDLL:
 
 def ref_layout() -> C.CDLL:
     return _load("_ref/libmx_ref_layout.so")
+
+
+def have_ref_builders() -> bool:
+    return (HERE / "_ref" / "libmx_ref_builders.so").exists()
+
+
+def ref_builders() -> C.CDLL:
+    """The reference's own table / embedding builder statements (src/models/qwen_image/dit.cpp,
+    src/models/minimax_h3/dit.cpp), cut out and compiled by oracle/Makefile; host only."""
+    return _load("_ref/libmx_ref_builders.so")
 
 
 # ---- bf16 helpers -------------------------------------------------------------------------------
@@ -266,6 +289,63 @@ def qwen_rope_table(segs, axes=(16, 56, 56), theta=10000.0):
     f.argtypes, f.restype = [C.POINTER(QwenSeg), _I, C.POINTER(C.c_int32), _F, _P, _P], _I64
     n = f(arr, len(segs), (C.c_int32 * 3)(*axes), theta, _ptr(cos), _ptr(sin))
     assert n == S
+    return cos, sin
+
+
+def qwen_segs(T, H, W, conds=()):
+    """The segment list of QwenImageDit::prepare (src/models/qwen_image/dit.cpp:128-144) for a text
+    sequence of T rows, condition images conds = [(slot0, h, w), ...] (each replaces h*w/4 placeholder
+    rows from slot0 on) and an H x W target image: text and image runs in order, the target last."""
+    segs, cur = [], 0
+    for slot0, h, w in conds:
+        if slot0 > cur:
+            segs.append(("text", slot0 - cur))
+        segs.append(("image", h, w))
+        cur = slot0 + h * w // 4
+    if T > cur:
+        segs.append(("text", T - cur))
+    segs.append(("image", H, W))
+    return segs
+
+
+def ref_qwen_rope_table(T, H, W, conds=()):
+    """(cos, sin) fp32 [S, 64] from the reference's own statements (QwenImageDit::prepare)."""
+    f = ref_builders().ref_qwen_rope_table
+    f.argtypes, f.restype = [_I64, _I64, _I64, _P, _I, _P, _P], _I64
+    flat = np.array([v for c in conds for v in c], np.int64).reshape(-1)
+    S = f(T, H, W, _ptr(flat) if flat.size else None, len(conds), None, None)
+    if S < 0:
+        raise RuntimeError("the reference rejected the layout")
+    cos, sin = np.empty((S, 64), np.float32), np.empty((S, 64), np.float32)
+    f(T, H, W, _ptr(flat) if flat.size else None, len(conds), _ptr(cos), _ptr(sin))
+    return cos, sin
+
+
+def ref_qwen_timestep_embedding(t):
+    out = np.empty((2, 256), np.float32)
+    f = ref_builders().ref_qwen_timestep_embedding
+    f.argtypes, f.restype = [_F, _P], None
+    f(t, _ptr(out))
+    return out
+
+
+def ref_h3_time_basis(ts, table):
+    grid, basis = table.shape
+    ts = np.ascontiguousarray(ts, np.float32)
+    out = np.empty((ts.size, basis), np.float32)
+    f = ref_builders().ref_h3_time_basis
+    f.argtypes, f.restype = [_P, _I64, _P, _I64, _I64, _P], None
+    f(_ptr(ts), ts.size, _ptr(table), grid, basis, _ptr(out))
+    return out
+
+
+def ref_h3_rope_table(positions, inv_freq, rot=None):
+    S, nf = positions.shape[0], inv_freq.size
+    rot = 6 * nf if rot is None else rot
+    cos, sin = np.empty((S, rot // 2), np.float32), np.empty((S, rot // 2), np.float32)
+    f = ref_builders().ref_h3_rope_table
+    f.argtypes, f.restype = [_P, _I64, _P, _I64, _I, _P, _P], None
+    f(_ptr(positions), S, _ptr(inv_freq), nf, rot, _ptr(cos), _ptr(sin))
     return cos, sin
 
 

@@ -305,3 +305,63 @@ def test_host_entry_points_report_a_timed_out_wait_as_a_status(mx):
     finally:
         pipe.close()
         mx.device_error(clear=True)
+
+
+# ---- the library's builders against the reference's own statements -------------------------------
+# tests/golden/ref_builders.npz holds what the reference's statements produced (generator:
+# tests/golden/make_ref_builders_golden.py); full tables for small layouts, SHA-256 digests for
+# benchmark-sized ones.
+
+def _gold():
+    import sys
+    from pathlib import Path
+    gdir = Path(__file__).resolve().parent / "golden"
+    if str(gdir) not in sys.path:
+        sys.path.insert(0, str(gdir))
+    import ref_builder_cases as cases
+    return np.load(gdir / "ref_builders.npz"), cases
+
+
+def _digest(*arrays):
+    import hashlib
+    h = hashlib.sha256()
+    for a in arrays:
+        h.update(np.ascontiguousarray(a).tobytes())
+    return np.frombuffer(h.digest(), np.uint8)
+
+
+def test_library_qwen_rope_table_equals_the_reference_statements(mx):
+    from miroxen_b200 import rope_tables
+    gold, cases = _gold()
+    for i, (T, Hh, W, conds) in enumerate(cases.QWEN_ROPE_FULL):
+        cos, sin = rope_tables.qwen_rope_table(orc.qwen_segs(T, Hh, W, conds))
+        assert np.array_equal(cos.cpu().numpy().view(np.uint32), gold[f"qwen_rope_full{i}_cos"].view(np.uint32)), i
+        assert np.array_equal(sin.cpu().numpy().view(np.uint32), gold[f"qwen_rope_full{i}_sin"].view(np.uint32)), i
+    for i, (T, Hh, W, conds) in enumerate(cases.QWEN_ROPE_DIGEST):
+        cos, sin = rope_tables.qwen_rope_table(orc.qwen_segs(T, Hh, W, conds))
+        assert cos.shape[0] == int(gold[f"qwen_rope_digest{i}_rows"][0])
+        assert np.array_equal(_digest(cos.cpu().numpy(), sin.cpu().numpy()), gold[f"qwen_rope_digest{i}"]), i
+
+
+def test_library_timestep_embedding_equals_the_reference_statements(mx):
+    from miroxen_b200 import rope_tables
+    gold, cases = _gold()
+    for on_host in (True, False):
+        got = np.stack([rope_tables.qwen_timestep_embedding(float(t), on_host=on_host).cpu().numpy() for t in cases.TIMESTEPS_FULL])
+        assert np.array_equal(got.view(np.uint32), gold["timestep_full"].view(np.uint32)), on_host
+    dev = [rope_tables.qwen_timestep_embedding(float(t)) for t in cases.timesteps_digest()]
+    assert np.array_equal(_digest(*[d.cpu().numpy() for d in dev]), gold["timestep_digest"])
+
+
+def test_library_h3_builders_equal_the_reference_statements(mx):
+    from miroxen_b200 import rope_tables
+    gold, cases = _gold()
+    table, ts, small = cases.h3_basis_inputs()
+    for tab, key in ((table, "h3_basis"), (small, "h3_basis_small")):
+        out = rope_tables.h3_time_basis(H.to_dev(torch, ts), H.to_dev(torch, tab))
+        assert np.array_equal(out.cpu().numpy().view(np.uint32), gold[key].view(np.uint32)), key
+    invf = cases.h3_inv_freq()
+    layouts = {"case0": (512, 21, 60, 104, 0, []), "case1": (37, 7, 30, 52, 25, ["first", "last"]), "case2": (5, 2, 4, 6, 3, ["last"])}
+    for name, (T, F_lat, Hh, W, A, anchors) in layouts.items():
+        cos, sin = rope_tables.h3_rope_table(T, F_lat, Hh, W, A, anchors, invf)
+        assert np.array_equal(_digest(cos.cpu().numpy(), sin.cpu().numpy()), gold[f"h3_rope_{name}_digest"]), name
