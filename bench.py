@@ -57,6 +57,9 @@ def parse():
                     help="strong scaling of a video workload: whole frames per rank (the reference's split) or equal "
                          "row ranges (default: rows for the main line; the video record reports both)")
     ap.add_argument("--e2e-chunk-rows", type=int, default=1024, help="rows per staged chunk of the end-to-end leg")
+    ap.add_argument("--rows", type=int, default=0, help="run only the first ROWS rows of the workload (tuning aid)")
+    ap.add_argument("--ops-only", action="store_true",
+                    help="time only the isolated per-op figures (profiling / tuning aid; prints its own line)")
     ap.add_argument("--quant-only", action="store_true",
                     help="time only the block-scale quantiser on the block's activations (profiling aid; prints its own line)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
@@ -492,6 +495,77 @@ class Job:
         ops = op_rows(w, names, [t / K * 1e3 for t in acc], self.rows, env.peak_gbs)
         return {"us_per_block": round(sum(o["us"] for o in ops), 1), "ops": ops}
 
+    def per_op_isolated(self, K):
+        """Each op of the block timed on its own: K back-to-back launches of the same op over the rotating
+        buffer sets (inputs never in L2; each launch's write-backs drain during the next launch of the same
+        op, so a launch window moves exactly the op's own bytes).  This is the per-op figure the in-chain
+        numbers are compared with: inside the chain an op also pays for the previous op's draining writes."""
+        env, mx, w, rows = self.env, self.env.mx, self.w, self.rows
+        st, n = env.stream, self.n_sets
+        pl = self.prefix_rows
+
+        def mod(b, name):
+            return mx.row_mod(b.mods[name + "_t"], b.mods[name + "_p"], pl)
+
+        def norm(b, k, out):
+            if w.norm_mode == 0:
+                mx.layernorm_mod(b.x, rows, w.dim, w.eps, mod(b, "scale" + k), mod(b, "shift" + k), out, st)
+            else:
+                mx.rmsnorm_mod(b.x, rows, w.dim, w.eps, b.mods["norm" + k + "_w"], mod(b, "scale" + k), mod(b, "shift" + k), out, st)
+
+        inner = w.inner
+        stride = 3 * inner if w.packed_qkv else inner
+
+        def rope(b, which):
+            src = b.qkv if w.packed_qkv else (b.q_in if which == 0 else b.k_in)
+            col0 = which * inner if w.packed_qkv else 0
+            out = (b.q_out, b.k_out, getattr(b, "v_out", None))[which]
+            if which < 2:
+                mx.head_norm_rope(src, rows, stride, col0, w.H, w.D, b.mods["norm_q" if which == 0 else "norm_k"], w.eps, b.cos, b.sin,
+                                  w.rot, w.rope_mode, out, st)
+            else:
+                mx.head_norm_rope(src, rows, stride, col0, w.H, w.D, None, 0.0, None, None, 0, 0, out, st)
+
+        def qkv(b):
+            specs = [mx.HeadSpec(b.qkv if w.packed_qkv else b.q_in, stride, 0, b.mods["norm_q"], b.q_out, w.rot, w.rope_mode),
+                     mx.HeadSpec(b.qkv if w.packed_qkv else b.k_in, stride, inner if w.packed_qkv else 0, b.mods["norm_k"], b.k_out, w.rot, w.rope_mode)]
+            if w.packed_qkv:
+                specs.append(mx.HeadSpec(b.qkv, stride, 2 * inner, None, b.v_out, 0, 0))
+            mx.qkv_norm_rope(specs, rows, w.H, w.D, w.eps, b.cos, b.sin, st)
+
+        def act(b):
+            if w.act_mode == 0:
+                mx.gelu_tanh_inplace(b.act, rows * w.F, st)
+            else:
+                mx.silu_mul(b.act2, rows, w.F, b.act, st)
+
+        def res_norm(b):
+            mx.gated_residual_norm(b.x, b.attn_o, rows, w.dim, mod(b, "gate1"), w.gate_tanh, w.norm_mode, w.eps,
+                                   b.mods.get("norm2_w"), mod(b, "scale2"), mod(b, "shift2"), b.h2, st)
+
+        ob = w.op_bytes(rows)
+        tab = 2 * (w.rot // 2) * 4 * rows
+        act_name = "gelu_tanh_inplace" if w.act_mode == 0 else "silu_mul"
+        ops = [("norm_mod", lambda b: norm(b, "1", b.h1), ob["norm_mod"]),
+               ("head_norm_rope", lambda b: rope(b, 0), ob["head_norm_rope"] + tab)]
+        if w.packed_qkv:
+            ops.append(("head_norm_rope (v copy)", lambda b: rope(b, 2), ob["head_norm_rope"]))
+        ops += [("gated_residual", lambda b: mx.gated_residual(b.x, b.attn_o, rows, w.dim, mod(b, "gate1"), w.gate_tanh, st), ob["gated_residual"]),
+                (act_name, act, ob[act_name]),
+                ("qkv_norm_rope", qkv, ob["qkv_norm_rope"]),
+                ("gated_residual_norm", res_norm, ob["gated_residual_norm"])]
+        out = []
+        for name, fn, by in ops:
+            step = lambda i, fn=fn: fn(self.sets[i % n])
+            for i in range(3):
+                step(i)
+            env.barrier()
+            reps = [env.event_ms(step, K) / K * 1e3 for _ in range(3)]
+            us = statistics.median(reps)
+            out.append({"op": name, "us": round(us, 2), "bytes": by, "gbs": round(by / us / 1e3, 1),
+                        "frac": round(by / us / 1e3 / env.peak_gbs, 3)})
+        return out
+
     def close(self):
         self.sets, self.graphs = [], None
         if self.impl != "mxk":
@@ -838,11 +912,20 @@ def main():
         rows, row0 = sh.rows, sh.row0
     else:
         rows, row0 = w.rows, 0
+    if args.rows > 0:
+        if not (args.ops_only or args.quant_only):
+            raise SystemExit("--rows goes with --ops-only / --quant-only: the bench line is defined on the whole workload")
+        rows = min(rows, args.rows)
     total_rows = w.rows * (n_gpus if scaling == "weak" else 1)
     job = Job(env, w, rows, row0, chain=args.chain)
     if args.graph:
         job.capture_graphs()
 
+    if args.ops_only:
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "workload": w.name, "rows": rows, "steps": K, "tune": args.tune,
+                              "per_op_isolated": job.per_op_isolated(K)}), flush=True)
+        return
     if args.quant_only:
         if rank == 0:
             print(json.dumps({"impl": args.impl, "workload": w.name, "steps": K, "next_rows": quant_rows(env, job, K, "mxk")}), flush=True)
@@ -873,6 +956,10 @@ def main():
     if not args.no_extras:
         per_chain = {"dropin": job.per_op(K, 0), "fused": job.per_op(K, 1)}
         line["per_op"] = per_chain
+        line["per_op_isolated"] = job.per_op_isolated(K)
+        line["per_op_note"] = ("per_op: events between the launches of a chain pass (an op also pays for the previous op's "
+                               "write-backs draining from L2); per_op_isolated: the same op launched back to back over "
+                               "rotating buffer sets, steady state")
         ops = per_chain[args.chain]["ops"]
         top = max(ops, key=lambda o: o["us"])
         line["roofline"] = {"bound": "hbm", "kernel": top["op"], "achieved": top["gbs"], "peak": env.peak_gbs, "unit": "GB/s",

@@ -161,6 +161,39 @@ typedef struct MxkHeadTensor {
 int mxk_qkv_norm_rope(const MxkHeadTensor* tensors_host, int n_tensors, int64_t S, int H, int D,
                       float eps, const float* cos, const float* sin, mxk_stream_t stream);
 
+/* ---- head exchange for sequence parallelism --------------------------------------------- */
+/* The reference's 2-card path (src/models/minimax_h3/dit_sp.cpp:83-112) shards token rows for the
+ * linear layers and attention heads for attention: after the QKV projection each card runs
+ * head_norm_rope once per card on that card's head range into a send buffer and copies it over
+ * (cudaMemcpyPeerAsync), so that every card ends with [S, H/2 * D] = all rows, its own heads.  Here
+ * that is one launch for any G <= MXK_MAX_HEAD_GROUPS: the q / k / v heads of this rank's `S` rows
+ * are normalised and rotated exactly as mxk_qkv_norm_rope does and head h of tensor i is stored
+ * straight into outs_host[i * groups + h / (H / groups)], a bf16 [*, H / groups, D] array, at row
+ * dst_row0 + s.  A destination may be a peer GPU's buffer (mxk_peer_buffer_open): the stores then
+ * cross NVLink and no send buffer or copy exists.  Stores are plain per-lane 128-bit stores; the
+ * kernel waits on nobody.  The caller orders the consumers of the destinations after every rank's
+ * launch (an event per peer as in dit_sp.cpp:111,116, or a barrier).  tensors[i].out is ignored.
+ * H must be a multiple of groups; D one of 32, 64, 128, 256; inputs 16-byte aligned. */
+#define MXK_MAX_HEAD_GROUPS 8
+int mxk_qkv_norm_rope_scatter(const MxkHeadTensor* tensors_host, int n_tensors, int64_t S, int H, int D, float eps,
+                              const float* cos, const float* sin, int groups, mxk_bf16* const* outs_host,
+                              int64_t dst_row0, mxk_stream_t stream);
+/* The way back (src/models/minimax_h3/dit_sp.cpp:137-149): rows [src_row0, src_row0 + rows) of the
+ * attention output are gathered from the `groups` head-sharded arrays srcs_host[g] (bf16
+ * [*, heads_per_group, D], this GPU's or a peer's: plain 128-bit loads) into out bf16
+ * [rows, groups * heads_per_group * D], the input layout of the out-projection. */
+int mxk_gather_head_groups(const mxk_bf16* const* srcs_host, int groups, int64_t src_row0, int64_t rows,
+                           int heads_per_group, int D, mxk_bf16* out, mxk_stream_t stream);
+/* Set-up helpers for the peer buffers (they allocate; never on the hot path).  alloc: cudaMalloc on
+ * the current device + an opaque 64-byte handle another process of the same box passes to open,
+ * which maps the buffer into its address space and enables peer access (CUDA IPC).  close undoes
+ * open; free releases an allocation of alloc. */
+int mxk_peer_buffer_alloc(int64_t bytes, void** ptr, unsigned char* handle64);
+int mxk_peer_buffer_open(const unsigned char* handle64, void** ptr);
+int mxk_peer_buffer_close(void* ptr);
+int mxk_peer_buffer_free(void* ptr);
+
+
 /* ---- RoPE tables and timestep embeddings ------------------------------------------------
  * The reference builds these on the host with libm and uploads them once per generation
  * (src/models/qwen_image/dit.cpp:151-185, src/models/minimax_h3/dit.cpp:254-262).  libm's

@@ -92,6 +92,12 @@ PROTOTYPES = {
     "mxk_axpby_f32": (_I, [_P, _P, _F, _F, _I64, _P]),
     "mxk_gated_residual_norm": (_I, [_P, _P, _I64, _I64, RowMod, _I, _I, _F, _P, RowMod, RowMod, _P, _P]),
     "mxk_qkv_norm_rope": (_I, [C.POINTER(HeadTensor), _I, _I64, _I, _I, _F, _P, _P, _P]),
+    "mxk_qkv_norm_rope_scatter": (_I, [C.POINTER(HeadTensor), _I, _I64, _I, _I, _F, _P, _P, _I, C.POINTER(_P), _I64, _P]),
+    "mxk_gather_head_groups": (_I, [C.POINTER(_P), _I, _I64, _I64, _I, _I, _P, _P]),
+    "mxk_peer_buffer_alloc": (_I, [_I64, C.POINTER(_P), _P]),
+    "mxk_peer_buffer_open": (_I, [_P, C.POINTER(_P)]),
+    "mxk_peer_buffer_close": (_I, [_P]),
+    "mxk_peer_buffer_free": (_I, [_P]),
     "mxk_rope_table_expand": (_I, [_P, _P, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32), _I,
                                    C.POINTER(RopeRun), _I, _I64, _I, _P, _P, _P]),
     "mxk_msrope_inv_freq_host": (_I, [C.POINTER(C.c_int32), _I, _F, _P]),

@@ -20,6 +20,7 @@ namespace {
 
 constexpr int kMaxTensors = 3;
 constexpr int kHeadsInFlight = 4;  // independent 128-bit loads each lane issues per batch
+constexpr int kMaxScatterGroups = MXK_MAX_HEAD_GROUPS;
 
 // What one bulk copy brings in: the bytes of one or more tensors for the tokens of a group.
 struct CopySeg {
@@ -46,6 +47,11 @@ struct RopeArgs {
   int tpc;          // tokens per stage (one group)
   int64_t groups_per_cta;
   int interleave;   // 1: CTA i takes groups i, i + grid, ...; 0: a contiguous range of groups
+  // head-group scatter (register kernel only): head h of tensor ti goes to scatter_out[ti][h / heads_per_group]
+  // at row scatter_row0 + s of a [*, heads_per_group, D] array (a peer GPU's buffer, or this GPU's own)
+  int scatter_groups, heads_per_group;
+  int64_t scatter_row0;
+  mxk_bf16* scatter_out[kMaxTensors][kMaxScatterGroups];
   CopySeg seg[kMaxTensors];
   int n_seg;
   int t_seg[kMaxTensors];  // segment that holds tensor ti
@@ -54,7 +60,7 @@ struct RopeArgs {
   int* err;
 };
 
-template <int LPH>
+template <int LPH, bool SCATTER = false>
 __global__ void __launch_bounds__(512) head_rope_kernel(const RopeArgs a) {
   constexpr int U = kHeadsInFlight;
   pdl_launch_dependents();
@@ -165,7 +171,15 @@ __global__ void __launch_bounds__(512) head_rope_kernel(const RopeArgs a) {
           }
           if (on[u]) {
             const int h = h0 + gh + u * a.gpt;
-            st_stream(reinterpret_cast<uint4*>(dst + int64_t(h) * a.D), pack8(v));
+            if constexpr (SCATTER) {
+              // the head's group decides the destination buffer; plain 128-bit stores, which reach a peer
+              // GPU's memory over NVLink when the pointer is a peer mapping
+              const int g = h / a.heads_per_group, hh = h - g * a.heads_per_group;
+              mxk_bf16* o = a.scatter_out[ti][g] + ((a.scatter_row0 + s) * a.heads_per_group + hh) * int64_t(a.D) + 8 * l;
+              *reinterpret_cast<uint4*>(o) = pack8(v);
+            } else {
+              st_stream(reinterpret_cast<uint4*>(dst + int64_t(h) * a.D), pack8(v));
+            }
           }
         }
       }
@@ -284,6 +298,111 @@ __device__ __forceinline__ void rope_tokens(const unsigned char* src, int tok_by
   }
 }
 
+// Sixteen channels per lane (the "wide" mapping): a head is held by LPH = D/16 lanes, lane l owning
+// channels 8l..8l+7 (chunk A) and D/2 + 8l .. D/2 + 8l + 7 (chunk B).  Against the 8-channel mapping
+// this halves the per-vector overhead (addressing, loop, barrier traffic), takes one shuffle round
+// out of the head reduction and puts both elements of every half-mode pair (i, i + D/2) in the same
+// lane, so that no partner exchange is needed when rot == D.
+struct WideRole {
+  int thread_off;  // byte offset of chunk A of head hp inside a token's H*D bf16
+  int pass_off;    // bytes from one pass's head to the next
+  int hp;
+  int tab_a, tab_b;  // first cos/sin entry of chunk A / chunk B (interleaved), of the lane's 8 pairs (half: tab_a)
+  bool rot_a, rot_b;  // the chunk lies inside the rotated channels
+};
+
+template <int LPH, bool NORM, int MODE, int PASSES>
+__device__ __forceinline__ void rope_tokens_wide(const unsigned char* src, int tok_bytes, const float* cos_row, const float* sin_row,
+                                                 int half, int ntok, unsigned char* dst, int out_tok_bytes, const float* wsm_a,
+                                                 const float* wsm_b, int chunk_b_off, float inv_d, float eps, int passes,
+                                                 int heads_per_pass, int H, const WideRole& r) {
+  float wa[8], wb[8];
+  if (NORM) {
+    const float4 a0 = *reinterpret_cast<const float4*>(wsm_a), a1 = *reinterpret_cast<const float4*>(wsm_a + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(wsm_b), b1 = *reinterpret_cast<const float4*>(wsm_b + 4);
+    wa[0] = a0.x, wa[1] = a0.y, wa[2] = a0.z, wa[3] = a0.w, wa[4] = a1.x, wa[5] = a1.y, wa[6] = a1.z, wa[7] = a1.w;
+    wb[0] = b0.x, wb[1] = b0.y, wb[2] = b0.z, wb[3] = b0.w, wb[4] = b1.x, wb[5] = b1.y, wb[6] = b1.z, wb[7] = b1.w;
+  }
+  for (int tk = 0; tk < ntok; tk++) {
+    // interleaved: c[0..3] / s[0..3] are chunk A's four pairs, c[4..7] / s[4..7] chunk B's;
+    // half (rot == D): pair i of the lane is (A[i], B[i]) with table entry tab_a + i
+    float c[8], sg[8];
+    if (MODE == MXK_ROPE_INTERLEAVED) {
+      const float4 ca = *reinterpret_cast<const float4*>(cos_row + r.tab_a), sa = *reinterpret_cast<const float4*>(sin_row + r.tab_a);
+      c[0] = ca.x, c[1] = ca.y, c[2] = ca.z, c[3] = ca.w, sg[0] = sa.x, sg[1] = sa.y, sg[2] = sa.z, sg[3] = sa.w;
+      if (r.rot_b) {
+        const float4 cb = *reinterpret_cast<const float4*>(cos_row + r.tab_b), sb = *reinterpret_cast<const float4*>(sin_row + r.tab_b);
+        c[4] = cb.x, c[5] = cb.y, c[6] = cb.z, c[7] = cb.w, sg[4] = sb.x, sg[5] = sb.y, sg[6] = sb.z, sg[7] = sb.w;
+      } else {
+        c[4] = c[5] = c[6] = c[7] = 1.f, sg[4] = sg[5] = sg[6] = sg[7] = 0.f;
+      }
+    } else if (MODE == MXK_ROPE_HALF) {
+      const float4 c0 = *reinterpret_cast<const float4*>(cos_row + r.tab_a), c1 = *reinterpret_cast<const float4*>(cos_row + r.tab_a + 4);
+      const float4 s0 = *reinterpret_cast<const float4*>(sin_row + r.tab_a), s1 = *reinterpret_cast<const float4*>(sin_row + r.tab_a + 4);
+      c[0] = c0.x, c[1] = c0.y, c[2] = c0.z, c[3] = c0.w, c[4] = c1.x, c[5] = c1.y, c[6] = c1.z, c[7] = c1.w;
+      sg[0] = s0.x, sg[1] = s0.y, sg[2] = s0.z, sg[3] = s0.w, sg[4] = s1.x, sg[5] = s1.y, sg[6] = s1.z, sg[7] = s1.w;
+    }
+    const unsigned char* sp = src;
+    unsigned char* dp = dst;
+#pragma unroll
+    for (int pass = 0; pass < (PASSES > 0 ? PASSES : passes); pass++) {
+      const bool on = PASSES > 0 || r.hp < (pass + 1 < passes ? heads_per_pass : H - pass * heads_per_pass);
+      uint4 ra = make_uint4(0u, 0u, 0u, 0u), rb = make_uint4(0u, 0u, 0u, 0u);
+      if (on) {
+        ra = *reinterpret_cast<const uint4*>(sp);
+        rb = *reinterpret_cast<const uint4*>(sp + chunk_b_off);
+      }
+      float va[8], vb[8];
+      unpack8(ra, va);
+      unpack8(rb, vb);
+      if (NORM) {
+        float qa = va[0] * va[0], qb = vb[0] * vb[0];
+#pragma unroll
+        for (int i = 1; i < 8; i++) qa = fmaf(va[i], va[i], qa), qb = fmaf(vb[i], vb[i], qb);
+        const float q = group_sum<LPH>(qa + qb);
+        const float rstd = rsqrt_approx(fmaf(q, inv_d, eps));
+#pragma unroll
+        for (int i = 0; i < 8; i++) va[i] = va[i] * rstd * wa[i], vb[i] = vb[i] * rstd * wb[i];
+      }
+      if (MODE == MXK_ROPE_INTERLEAVED) {
+        if (r.rot_a) {
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const float a0 = va[2 * i], b0 = va[2 * i + 1];
+            va[2 * i] = a0 * c[i] - b0 * sg[i];
+            va[2 * i + 1] = b0 * c[i] + a0 * sg[i];
+          }
+        }
+        if (r.rot_b) {
+#pragma unroll
+          for (int i = 0; i < 4; i++) {
+            const float a0 = vb[2 * i], b0 = vb[2 * i + 1];
+            vb[2 * i] = a0 * c[4 + i] - b0 * sg[4 + i];
+            vb[2 * i + 1] = b0 * c[4 + i] + a0 * sg[4 + i];
+          }
+        }
+      } else if (MODE == MXK_ROPE_HALF) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float a0 = va[i], b0 = vb[i];
+          va[i] = a0 * c[i] - b0 * sg[i];
+          vb[i] = fmaf(a0, sg[i], b0 * c[i]);
+        }
+      }
+      if (on) {
+        st_stream(reinterpret_cast<uint4*>(dp), pack8(va));
+        st_stream(reinterpret_cast<uint4*>(dp + chunk_b_off), pack8(vb));
+      }
+      sp += r.pass_off;
+      dp += r.pass_off;
+    }
+    src += tok_bytes;
+    dst += out_tok_bytes;
+    cos_row += half;
+    sin_row += half;
+  }
+}
+
 // The producer lane's loop: one group of `tpc` tokens per stage, in order; returns false when a
 // bounded wait on an `empty` barrier ran out.  `issued` counts the groups whose copies went out.
 __device__ __forceinline__ bool rope_produce(const RopeArgs& a, unsigned char* dyn, unsigned long long* full,
@@ -323,8 +442,9 @@ __device__ __forceinline__ bool rope_produce(const RopeArgs& a, unsigned char* d
   return true;
 }
 
-template <int LPH, int PASSES = 0>
-__global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
+// MINB (wide mapping only): resident CTAs per SM the register allocation is held to.
+template <int LPH, int PASSES = 0, bool WIDE = false, int MINB = 1>
+__global__ void __launch_bounds__(WIDE ? 160 : 544, MINB) head_rope_pipe_kernel(const RopeArgs a) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ __align__(8) unsigned long long full[8], empty[8];
   __shared__ __align__(16) float wsm[kMaxTensors][256];  // the tensors' norm weights
@@ -359,6 +479,62 @@ __global__ void __launch_bounds__(544) head_rope_pipe_kernel(const RopeArgs a) {
   int issued = 0;  // producer: groups whose copies were issued
   if (warp == n_cons_warps) {
     if (lane == 0) ok = rope_produce(a, dyn, full, empty, g_begin, g_step, my_groups, issued);
+  } else if constexpr (WIDE) {
+    const int l = tid % LPH;
+    WideRole r;
+    r.hp = tid / LPH;
+    r.thread_off = (r.hp * a.D + 8 * l) * 2;
+    r.pass_off = a.heads_per_pass * a.D * 2;
+    const int chunk_b_off = a.D;  // D/2 channels of bf16
+    r.rot_a = rope && 8 * l < a.rot;
+    r.rot_b = rope && a.D / 2 + 8 * l < a.rot;
+    if (a.mode == MXK_ROPE_INTERLEAVED) {
+      r.tab_a = r.rot_a ? 4 * l : 0;
+      r.tab_b = r.rot_b ? a.D / 4 + 4 * l : 0;
+    } else {
+      r.tab_a = r.tab_b = 8 * l;  // half mode on this path has rot == D: pair i of the lane is entry 8l + i
+    }
+    const float inv_d = 1.f / float(a.D);
+    const int tok_out_bytes = a.H * a.D * 2;
+    int st = 0;
+    unsigned ph = 0;
+    int64_t s0 = g_begin * a.tpc;
+    for (int it = 0; it < my_groups; it++, s0 += g_step * a.tpc) {
+      if (!mbar_wait(smem_u32(&full[st]), ph)) {
+        ok = false;
+        break;
+      }
+      const unsigned char* stage = dyn + size_t(st) * a.stage_bytes;
+      const int ntok = int(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
+      const float* cr = reinterpret_cast<const float*>(stage + a.cos_off);
+      const float* sr = reinterpret_cast<const float*>(stage + a.sin_off);
+#pragma unroll 1
+      for (int ti = 0; ti < a.n_tensors; ti++) {
+        const MxkHeadTensor& t = a.t[ti];
+        const CopySeg& sg = a.seg[a.t_seg[ti]];
+        const unsigned char* src = stage + sg.smem_off + a.t_off[ti] + r.thread_off;
+        unsigned char* dst = reinterpret_cast<unsigned char*>(t.out) + s0 * tok_out_bytes + r.thread_off;
+        const bool t_rope = t.mode != MXK_ROPE_NONE && t.rot > 0;
+        const float* wa = &wsm[ti][8 * l];
+        const float* wb = &wsm[ti][a.D / 2 + 8 * l];
+#define MXK_ROPE_CALL(NORM, MODE)                                                                                      \
+  rope_tokens_wide<LPH, NORM, MODE, PASSES>(src, sg.token_bytes, cr, sr, half, ntok, dst, tok_out_bytes, wa, wb, chunk_b_off, \
+                                            inv_d, a.eps, a.passes, a.heads_per_pass, a.H, r)
+        if (t.norm_w) {
+          if (!t_rope) MXK_ROPE_CALL(true, MXK_ROPE_NONE);
+          else if (a.mode == MXK_ROPE_INTERLEAVED) MXK_ROPE_CALL(true, MXK_ROPE_INTERLEAVED);
+          else MXK_ROPE_CALL(true, MXK_ROPE_HALF);
+        } else {
+          if (!t_rope) MXK_ROPE_CALL(false, MXK_ROPE_NONE);
+          else if (a.mode == MXK_ROPE_INTERLEAVED) MXK_ROPE_CALL(false, MXK_ROPE_INTERLEAVED);
+          else MXK_ROPE_CALL(false, MXK_ROPE_HALF);
+        }
+#undef MXK_ROPE_CALL
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&empty[st]));
+      if (++st == a.stages) st = 0, ph ^= 1u;
+    }
   } else {
     const int l = tid % LPH;
     LaneRole r;
@@ -501,7 +677,7 @@ bool fast_ok(const RopeArgs& a) {
 // Plans the bulk-copy pipeline: beyond fast_ok it needs one (rot, mode) for all rotating tensors
 // and table rows that are multiples of 16 bytes.  Tensors that are consecutive column blocks of
 // the same buffer (packed q|k|v) become one copy segment.
-bool pipe_plan(RopeArgs& a) {
+bool pipe_plan(RopeArgs& a, bool wide = false) {
   a.rot = 0, a.mode = MXK_ROPE_NONE;
   for (int i = 0; i < a.n_tensors; i++) {
     const MxkHeadTensor& t = a.t[i];
@@ -511,12 +687,22 @@ bool pipe_plan(RopeArgs& a) {
   }
   const int half = a.rot / 2;
   if (a.mode != MXK_ROPE_NONE && half % 4) return false;
-  const int lph = a.D / 8;
+  // the wide mapping needs a 32-byte head half and, in half mode, both elements of a pair in one lane (rot == D)
+  if (wide && (a.D % 16 != 0 || (a.mode == MXK_ROPE_HALF && a.rot != a.D))) return false;
+  const int lph = wide ? a.D / 16 : a.D / 8;
   int max_threads = tune(TUNE_ROPE_THREADS, 128);  // small CTAs, many per SM: measured best on B200
   if (max_threads > 512) max_threads = 512;
   if (max_threads < lph) max_threads = lph;
   int passes = 1;
   while (lph * int(ceil_div(a.H, passes)) > max_threads) passes++;
+  if (wide) {
+    // prefer a pass count that divides H into full warps (the pass loop then unrolls without predicates)
+    for (int p = passes; p <= passes + 6 && p <= a.H; p++)
+      if (a.H % p == 0 && (lph * (a.H / p)) % 32 == 0) {
+        passes = p;
+        break;
+      }
+  }
   a.passes = passes;
   a.heads_per_pass = int(ceil_div(a.H, passes));
   const int64_t hd = int64_t(a.H) * a.D;
@@ -564,9 +750,9 @@ bool pipe_plan(RopeArgs& a) {
   return size_t(stages) * a.stage_bytes <= 200 * 1024;
 }
 
-template <int LPH, int PASSES = 0>
+template <int LPH, int PASSES = 0, bool WIDE = false, int MINB = 1>
 int launch_pipe(const char* name, RopeArgs a, cudaStream_t stream) {
-  auto k = head_rope_pipe_kernel<LPH, PASSES>;
+  auto k = head_rope_pipe_kernel<LPH, PASSES, WIDE, MINB>;
   const int threads = int(ceil_div(int64_t(LPH) * a.heads_per_pass, 32) * 32) + 32;  // consumers + producer warp
   const size_t smem = size_t(a.stages) * a.stage_bytes;
   if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -581,7 +767,36 @@ int launch_pipe(const char* name, RopeArgs a, cudaStream_t stream) {
   return after_launch(name);
 }
 
+template <bool SCATTER>
+int launch_register(const char* name, RopeArgs a, cudaStream_t stream);
+int launch_generic(const char* name, RopeArgs a, cudaStream_t stream);
+
 int run(const char* name, RopeArgs a, cudaStream_t stream) {
+  // D = 128 (every model shape): sixteen channels per lane, eight lanes per head
+  if (a.D == 128 && fast_ok(a) && tune(TUNE_ROPE_PATH, 1) == 1 && tune(TUNE_ROPE_WIDE, 1) == 1 && a.S >= 2 && pipe_plan(a, true)) {
+    const bool exact = a.H == a.passes * a.heads_per_pass && (8 * a.heads_per_pass) % 32 == 0;
+    if (exact && tune(TUNE_ROPE_UNROLL, 1) == 1 && 8 * a.heads_per_pass + 32 <= 160) {
+      // register budget of the unrolled kernel: 1 = sized for four 160-thread CTAs per SM (about 96), 2 = the
+      // compiler's choice (110-170), 3 = sized for five (72, with a few spilled values)
+      const int regs = tune(TUNE_ROPE_WIDE_REGS, 1);
+#define MXK_WIDE_CASE(P)                                                                  \
+  case P:                                                                                 \
+    return regs == 3   ? launch_pipe<8, P, true, 5>(name, a, stream)                      \
+           : regs == 2 ? launch_pipe<8, P, true, 1>(name, a, stream)                      \
+                       : launch_pipe<8, P, true, 4>(name, a, stream)
+      switch (a.passes) {
+        MXK_WIDE_CASE(1);
+        MXK_WIDE_CASE(2);
+        MXK_WIDE_CASE(3);
+        MXK_WIDE_CASE(4);
+        MXK_WIDE_CASE(5);
+        MXK_WIDE_CASE(7);
+        default: break;
+      }
+#undef MXK_WIDE_CASE
+    }
+    if (8 * a.heads_per_pass + 32 <= 160) return launch_pipe<8, 0, true>(name, a, stream);
+  }
   if (fast_ok(a) && tune(TUNE_ROPE_PATH, 1) == 1 && a.S >= 2 && pipe_plan(a)) {
     switch (a.D / 8) {
       case 4: return launch_pipe<4>(name, a, stream);
@@ -604,7 +819,13 @@ int run(const char* name, RopeArgs a, cudaStream_t stream) {
       default: return launch_pipe<32>(name, a, stream);
     }
   }
-  if (fast_ok(a)) {
+  if (fast_ok(a)) return launch_register<false>(name, a, stream);
+  return launch_generic(name, a, stream);
+}
+
+template <bool SCATTER>
+int launch_register(const char* name, RopeArgs a, cudaStream_t stream) {
+  {
     const int lph = a.D / 8;
     a.gpt = int(ceil_div(a.H, kHeadsInFlight));
     const int per_token = lph * a.gpt;
@@ -622,14 +843,19 @@ int run(const char* name, RopeArgs a, cudaStream_t stream) {
         launch_pdl(kern, dim3(unsigned(grid)), dim3(threads), 0, stream, a);
       };
       switch (lph) {
-        case 4: go(head_rope_kernel<4>); break;
-        case 8: go(head_rope_kernel<8>); break;
-        case 16: go(head_rope_kernel<16>); break;
-        default: go(head_rope_kernel<32>); break;
+        case 4: go(head_rope_kernel<4, SCATTER>); break;
+        case 8: go(head_rope_kernel<8, SCATTER>); break;
+        case 16: go(head_rope_kernel<16, SCATTER>); break;
+        default: go(head_rope_kernel<32, SCATTER>); break;
       }
       return after_launch(name);
     }
   }
+  if (SCATTER) return fail(MXK_ERR_INVALID_ARG, "%s: H * D / 8 = %d lanes per token exceed a CTA", name, a.D / 8 * a.gpt);
+  return launch_generic(name, a, stream);
+}
+
+int launch_generic(const char* name, RopeArgs a, cudaStream_t stream) {
   int64_t grid = ceil_div(a.S * a.H, 8);
   const int64_t cap = int64_t(sm_count()) * 32;
   if (grid > cap) grid = cap;
@@ -683,6 +909,35 @@ int mxk_qkv_norm_rope(const MxkHeadTensor* tensors_host, int n_tensors, int64_t 
   a.n_tensors = n_tensors;
   a.S = S, a.H = H, a.D = D, a.eps = eps, a.cos = cos, a.sin = sin;
   return run("qkv_norm_rope", a, as_stream(stream));
+}
+
+int mxk_qkv_norm_rope_scatter(const MxkHeadTensor* tensors_host, int n_tensors, int64_t S, int H, int D, float eps,
+                              const float* cos, const float* sin, int groups, mxk_bf16* const* outs_host,
+                              int64_t dst_row0, mxk_stream_t stream) {
+  if (S <= 0 || n_tensors == 0) return MXK_OK;
+  if (!tensors_host || !outs_host || n_tensors < 0 || n_tensors > kMaxTensors)
+    return fail(MXK_ERR_INVALID_ARG, "qkv_norm_rope_scatter: n_tensors=%d (1..%d) or a null array", n_tensors, kMaxTensors);
+  if (groups < 1 || groups > kMaxScatterGroups || H <= 0 || H % groups != 0)
+    return fail(MXK_ERR_INVALID_ARG, "qkv_norm_rope_scatter: groups=%d (1..%d) must divide H=%d", groups, kMaxScatterGroups, H);
+  if (dst_row0 < 0) return fail(MXK_ERR_INVALID_ARG, "qkv_norm_rope_scatter: dst_row0=%lld", (long long)dst_row0);
+  RopeArgs a{};
+  for (int i = 0; i < n_tensors; i++) {
+    a.t[i] = tensors_host[i];
+    for (int g = 0; g < groups; g++) {
+      mxk_bf16* o = outs_host[i * groups + g];
+      if (!o || !aligned(o, 16)) return fail(MXK_ERR_INVALID_ARG, "qkv_norm_rope_scatter: destination %d of tensor %d is null or not 16-byte aligned", g, i);
+      a.scatter_out[i][g] = o;
+    }
+    a.t[i].out = a.scatter_out[i][0];
+    if (int rc = check("qkv_norm_rope_scatter", a.t[i], H, D, cos, sin)) return rc;
+  }
+  a.n_tensors = n_tensors;
+  a.S = S, a.H = H, a.D = D, a.eps = eps, a.cos = cos, a.sin = sin;
+  a.scatter_groups = groups, a.heads_per_group = H / groups, a.scatter_row0 = dst_row0;
+  if (!fast_ok(a))
+    return fail(MXK_ERR_INVALID_ARG, "qkv_norm_rope_scatter: needs D in {32, 64, 128, 256}, 16-byte aligned inputs and tables, "
+                "in_stride and col0 multiples of 8, rot a multiple of 8 (interleaved) or 16 (half)");
+  return launch_register<true>("qkv_norm_rope_scatter", a, as_stream(stream));
 }
 
 }  // extern "C"
