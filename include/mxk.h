@@ -394,6 +394,31 @@ int64_t mxk_qscale_bytes(int mode, int64_t rows, int64_t K);
 int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t rows, int64_t K, void* q, uint8_t* sf,
                              float* amax, mxk_stream_t stream);
 
+/* NVFP4 without the extra read pass.  The reference's quantiser reads an NVFP4 input twice: once for
+ * the tensor maximum no block can be scaled without (amax_kernel, src/kernels/blockscale.cu:47-70),
+ * once to quantise (:147-164).  The op that PRODUCES the tensor can take the maximum of its own bf16
+ * output as it stores it; these variants do (packed bf16 maxima per thread, one atomicMax per warp),
+ * clearing *amax_out first on the same stream:
+ *   mxk_layernorm_mod_amax / mxk_rmsnorm_mod_amax / mxk_gated_residual_norm_amax: the norm entry points
+ *     with one more argument;
+ *   mxk_act_amax: act_mode 0 GELU-tanh (out may be in: in place), 1 silu_mul (in bf16 [rows, 2F] ->
+ *     out [rows, F]), 2 GELU-erf; bias (may be NULL) is added first as in mxk_bias_gelu_tanh_inplace /
+ *     mxk_bias_silu_mul.
+ * mxk_quantize_nvfp4_known_amax then quantises in one pass from that device value (which it only
+ * reads).  Bytes (codes, scales, maximum) equal mxk_quantize_blockscaled(MXK_Q_NVFP4) on the same
+ * tensor.  No single counterpart in the reference (two adjacent calls become one and a half). */
+int mxk_layernorm_mod_amax(const float* x, int64_t rows, int64_t dim, float eps, MxkRowMod scale, MxkRowMod shift,
+                           mxk_bf16* out, float* amax_out, mxk_stream_t stream);
+int mxk_rmsnorm_mod_amax(const float* x, int64_t rows, int64_t dim, float eps, const float* w, MxkRowMod scale,
+                         MxkRowMod shift, mxk_bf16* out, float* amax_out, mxk_stream_t stream);
+int mxk_gated_residual_norm_amax(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, MxkRowMod gate, int gate_tanh,
+                                 int norm_mode, float eps, const float* w, MxkRowMod scale, MxkRowMod shift, mxk_bf16* out,
+                                 float* amax_out, mxk_stream_t stream);
+int mxk_act_amax(int act_mode, const mxk_bf16* in, const float* bias, int64_t rows, int64_t F, mxk_bf16* out, float* amax_out,
+                 mxk_stream_t stream);
+int mxk_quantize_nvfp4_known_amax(const mxk_bf16* x, int64_t ldx, int64_t rows, int64_t K, void* q, uint8_t* sf,
+                                  const float* amax, mxk_stream_t stream);
+
 /* Activation and MXFP8 quantisation in one pass over the data, for an activation whose only reader is the
  * next block-scaled GEMM (the MLP's hidden activation).  One call in place of two of the reference's:
  * gelu_tanh_inplace / gelu_erf_inplace / silu_mul (src/kernels/ops.h:36-41) followed by

@@ -61,6 +61,11 @@ PROTOTYPES = {
     "mxk_qdata_bytes": (_I64, [_I, _I64, _I64]),
     "mxk_qscale_bytes": (_I64, [_I, _I64, _I64]),
     "mxk_quantize_blockscaled": (_I, [_I, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
+    "mxk_layernorm_mod_amax": (_I, [_P, _I64, _I64, _F, RowMod, RowMod, _P, _P, _P]),
+    "mxk_rmsnorm_mod_amax": (_I, [_P, _I64, _I64, _F, _P, RowMod, RowMod, _P, _P, _P]),
+    "mxk_gated_residual_norm_amax": (_I, [_P, _P, _I64, _I64, RowMod, _I, _I, _F, _P, RowMod, RowMod, _P, _P, _P]),
+    "mxk_act_amax": (_I, [_I, _P, _P, _I64, _I64, _P, _P, _P]),
+    "mxk_quantize_nvfp4_known_amax": (_I, [_P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "mxk_act_quantize_mxfp8": (_I, [_I, _P, _P, _I64, _I64, _P, _P, _P]),
     "mxk_bias_gelu_tanh_inplace": (_I, [_P, _P, _I64, _I64, _P]),
     "mxk_bias_silu_mul": (_I, [_P, _P, _I64, _I64, _P, _P]),

@@ -1,6 +1,7 @@
 // silu_mul, gelu_tanh_inplace, gelu_erf_inplace, silu_inplace_f32
 // (reference: src/kernels/ops.cu:121-128, 212-233, 244-246).
 #include "act_math.cuh"
+#include "blockscale_math.cuh"
 #include "flat_map.cuh"
 #include "stream_pipe.cuh"
 
@@ -78,11 +79,14 @@ struct SiluPipeOp {
 template <int ACT>
 struct BiasActPipeOp : RowPieces {
   static constexpr int NSRC = ACT == ACT_SILU_MUL ? 2 : 1;
-  const float* bias;
+  const float* bias;  // may be null: the plain activation
   unsigned char* out;
-  struct State {};
-  __device__ State init() const { return State{}; }
-  __device__ void consume(State&, int64_t chunk, const unsigned char* stage, int tid, int n_cons) const {
+  float* amax;        // may be null; else max |out| is folded into it (cleared by the launcher)
+  struct State {
+    uint32_t m;  // two running bf16 maxima
+  };
+  __device__ State init() const { return State{0u}; }
+  __device__ void consume(State& st, int64_t chunk, const unsigned char* stage, int tid, int n_cons) const {
     unsigned row;
     int k0, n;
     where(chunk, row, k0, n);
@@ -90,22 +94,31 @@ struct BiasActPipeOp : RowPieces {
     const uint4* s1 = reinterpret_cast<const uint4*>(stage + stage_off);
     uint4* dst = reinterpret_cast<uint4*>(out + (int64_t(row) * K + k0) * 2);
     const int nvec = n >> 3;
+    uint32_t m = st.m;
     for (int i = tid; i < nvec; i += n_cons) {
-      const uint4 g = add_bias8(s0[i], bias + k0 + 8 * i);
-      const uint4 u = NSRC == 2 ? add_bias8(s1[i], bias + K + k0 + 8 * i) : g;
-      st_stream(dst + i, act8<ACT>(g, u));
+      uint4 g = s0[i], u = NSRC == 2 ? s1[i] : g;
+      if (bias) {
+        g = add_bias8(g, bias + k0 + 8 * i);
+        u = NSRC == 2 ? add_bias8(u, bias + K + k0 + 8 * i) : g;
+      }
+      const uint4 r = act8<ACT>(g, u);
+      st_stream(dst + i, r);
+      if (amax) m = absmax_bf16x2(m, absmax_bf16x2(r));
     }
+    st.m = m;
   }
-  __device__ void finish(State&, int) const {}
+  __device__ void finish(State& st, int) const {
+    if (amax) amax_commit(bf16x2_max_to_float(st.m), amax);
+  }
 };
 
 template <int ACT>
 int run_bias_act(const char* name, const mxk_bf16* in, const float* bias, int64_t rows, int64_t F, mxk_bf16* out,
-                 cudaStream_t s) {
+                 cudaStream_t s, float* amax = nullptr) {
   const bool two = ACT == ACT_SILU_MUL;
   if (F <= 0 || F % 8 != 0 || F > (int64_t(1) << 24) || !aligned(in, 16) || !aligned(out, 16) || !aligned(bias, 16))
     return fail(MXK_ERR_INVALID_ARG, "%s: needs F %% 8 == 0, F <= 2^24 and 16-byte aligned buffers; otherwise call "
-                "mxk_add_bias_bf16 and the activation separately", name);
+                "the separate ops", name);
   int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 8) * 1024 / (two ? 2 : 1);
   if (chunk_bytes > 32 * 1024) chunk_bytes = 32 * 1024;
   const int pieces = int(ceil_div(F * 2, chunk_bytes));
@@ -116,7 +129,7 @@ int run_bias_act(const char* name, const mxk_bf16* in, const float* bias, int64_
   op.x = reinterpret_cast<const unsigned char*>(in), op.ldx_bytes = F * (two ? 4 : 2), op.K = int(F);
   op.set_pieces(int(ceil_div(F, piece_elems)), piece_elems);
   op.src1_off = two ? F * 2 : 0, op.stage_off = (piece_elems * 2 + 127) & ~127;
-  op.bias = bias, op.out = reinterpret_cast<unsigned char*>(out);
+  op.bias = bias, op.out = reinterpret_cast<unsigned char*>(out), op.amax = amax;
   return run_stream_pipe(name, op, rows * op.pieces_per_row, piece_elems * 2, s, two ? 4 : 8, two ? 2 : 3);
 }
 
@@ -209,6 +222,20 @@ int mxk_bias_silu_mul(const mxk_bf16* gu, const float* bias, int64_t rows, int64
   if (!gu || !out) return fail(MXK_ERR_INVALID_ARG, "bias_silu_mul: null gu or out");
   if (!bias) return mxk_silu_mul(gu, rows, F, out, stream);
   return run_bias_act<ACT_SILU_MUL>("bias_silu_mul", gu, bias, rows, F, out, as_stream(stream));
+}
+
+int mxk_act_amax(int act_mode, const mxk_bf16* in, const float* bias, int64_t rows, int64_t F, mxk_bf16* out, float* amax_out,
+                 mxk_stream_t stream) {
+  if (!amax_out) return fail(MXK_ERR_INVALID_ARG, "act_amax: null amax_out");
+  if (act_mode < 0 || act_mode > 2) return fail(MXK_ERR_INVALID_ARG, "act_amax: act_mode %d (0 gelu tanh, 1 silu_mul, 2 gelu erf)", act_mode);
+  cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), as_stream(stream));
+  if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "act_amax: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  if (rows <= 0 || F <= 0) return MXK_OK;
+  if (!in || !out) return fail(MXK_ERR_INVALID_ARG, "act_amax: null in or out");
+  cudaStream_t s = as_stream(stream);
+  if (act_mode == 1) return run_bias_act<ACT_SILU_MUL>("act_amax", in, bias, rows, F, out, s, amax_out);
+  if (act_mode == 0) return run_bias_act<ACT_GELU_TANH>("act_amax", in, bias, rows, F, out, s, amax_out);
+  return run_bias_act<ACT_GELU_ERF>("act_amax", in, bias, rows, F, out, s, amax_out);
 }
 
 int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk_stream_t stream) {

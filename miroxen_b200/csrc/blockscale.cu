@@ -109,12 +109,6 @@ __device__ __forceinline__ uint32_t block_absmax(const uint4 (&raw)[2]) {
   return absmax_bf16x2(absmax_bf16x2(raw[0]), absmax_bf16x2(raw[1]));
 }
 
-__device__ __forceinline__ void amax_commit(float m, float* out) {
-#pragma unroll
-  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  // non-negative floats order like their bit patterns (src/kernels/blockscale.cu:68)
-  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
-}
 
 // ---- bulk-copy pipeline ops: chunk = one piece (pieces_per_row of them) of one row ----
 
@@ -306,8 +300,21 @@ int64_t mxk_qscale_bytes(int mode, int64_t rows, int64_t K) {
   return pad_to(rows, 128) * pad_to(K / (mode == MXK_Q_NVFP4 ? 16 : 32), 4);
 }
 
+static int quantize_impl(int mode, const mxk_bf16* x, int64_t ldx, int64_t rows, int64_t K, void* q, uint8_t* sf, float* amax,
+                         bool amax_known, mxk_stream_t stream);
+
 int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t rows, int64_t K, void* q, uint8_t* sf,
                              float* amax, mxk_stream_t stream) {
+  return quantize_impl(mode, x, ldx, rows, K, q, sf, amax, false, stream);
+}
+
+int mxk_quantize_nvfp4_known_amax(const mxk_bf16* x, int64_t ldx, int64_t rows, int64_t K, void* q, uint8_t* sf,
+                                  const float* amax, mxk_stream_t stream) {
+  return quantize_impl(MXK_Q_NVFP4, x, ldx, rows, K, q, sf, const_cast<float*>(amax), true, stream);
+}
+
+static int quantize_impl(int mode, const mxk_bf16* x, int64_t ldx, int64_t rows, int64_t K, void* q, uint8_t* sf, float* amax,
+                         bool amax_known, mxk_stream_t stream) {
   if (mode != MXK_Q_MXFP8 && mode != MXK_Q_NVFP4)
     return fail(MXK_ERR_INVALID_ARG, "quantize_blockscaled: mode %d is not a quantised mode (1 MXFP8, 2 NVFP4)", mode);
   // the reference's own check (src/kernels/blockscale.cu:151)
@@ -322,7 +329,7 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
   const bf16* xb = reinterpret_cast<const bf16*>(x);
   if (int rc = clear_scale_padding(mode, rows, K, sf, s)) return rc;
   cudaError_t e = cudaSuccess;
-  if (mode == MXK_Q_NVFP4) e = cudaMemsetAsync(amax, 0, sizeof(float), s);
+  if (mode == MXK_Q_NVFP4 && !amax_known) e = cudaMemsetAsync(amax, 0, sizeof(float), s);
   if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "quantize_blockscaled: cudaMemsetAsync: %s", cudaGetErrorString(e));
   const int nvec = int(K / 8);
   const int V = mode == MXK_Q_NVFP4 ? 16 : 32;
@@ -343,10 +350,12 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
     rp.x = reinterpret_cast<const unsigned char*>(x), rp.ldx_bytes = ldx * 2, rp.K = int(K);
     rp.set_pieces(ppr, piece_elems);
     if (fp4) {
-      AmaxPipeOp op;
-      static_cast<RowPieces&>(op) = rp;
-      op.out = amax;
-      if (int rc = run_stream_pipe("quantize_blockscaled (amax)", op, rows * ppr, piece_elems * 2, s, 4, 2)) return rc;
+      if (!amax_known) {
+        AmaxPipeOp op;
+        static_cast<RowPieces&>(op) = rp;
+        op.out = amax;
+        if (int rc = run_stream_pipe("quantize_blockscaled (amax)", op, rows * ppr, piece_elems * 2, s, 4, 2)) return rc;
+      }
       QuantPipeOp<2> qo;
       static_cast<RowPieces&>(qo) = rp;
       qo.q = static_cast<uint8_t*>(q), qo.sf = sf, qo.amax = amax, qo.nkb_pad = int(pad_to(K / V, 4));
@@ -357,7 +366,7 @@ int mxk_quantize_blockscaled(int mode, const mxk_bf16* x, int64_t ldx, int64_t r
     qo.q = static_cast<uint8_t*>(q), qo.sf = sf, qo.amax = nullptr, qo.nkb_pad = int(pad_to(K / V, 4));
     return run_stream_pipe("quantize_blockscaled", qo, rows * ppr, piece_elems * 2, s, 12, 3);
   }
-  if (mode == MXK_Q_NVFP4) {
+  if (mode == MXK_Q_NVFP4 && !amax_known) {
     int64_t grid = int64_t(sm_count()) * resident_ctas(amax_kernel, 256);
     if (grid > ceil_div(rows, kRowsInFlight)) grid = ceil_div(rows, kRowsInFlight);
     launch_pdl(amax_kernel, dim3(unsigned(grid)), dim3(256), 0, s, xb, ldx, rows, nvec, amax);

@@ -34,6 +34,15 @@ __device__ __forceinline__ float2 bf16x2_to_float2(uint32_t w) {
   return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
 }
 
+// Joins the warp's maxima and folds them into the tensor maximum at `out` (fp32, cleared beforehand): non-negative
+// floats order like their bit patterns, so an integer atomicMax does it (src/kernels/blockscale.cu:68).  All 32
+// lanes must call.
+__device__ __forceinline__ void amax_commit(float m, float* out) {
+#pragma unroll
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
+}
+
 // ue8m0 scale exponent of a block whose largest magnitude is the bf16 value bmax: the smallest e with
 // bmax / 2^e <= 448, clamped to [-127, 127] (src/kernels/blockscale.cu:111-119 computes it as
 // frexpf(bmax / 448)).  With bmax = 1.m * 2^E, RN(bmax / 448) = RN(1.m / 1.75) * 2^(E-8), and 1.m / 1.75

@@ -46,6 +46,34 @@ int mxk_rmsnorm_bf16(const mxk_bf16* x, int64_t rows, int64_t dim, float eps, co
                                   as_stream(stream));
 }
 
+// The same launches with the tensor maximum of the bf16 output as a by-product (see mxk.h).
+static int clear_amax(const char* name, float* amax_out, cudaStream_t s) {
+  if (!amax_out) return fail(MXK_ERR_INVALID_ARG, "%s: null amax_out", name);
+  cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), s);
+  if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "%s: cudaMemsetAsync: %s", name, cudaGetErrorString(e));
+  return MXK_OK;
+}
+
+int mxk_layernorm_mod_amax(const float* x, int64_t rows, int64_t dim, float eps, MxkRowMod scale, MxkRowMod shift,
+                           mxk_bf16* out, float* amax_out, mxk_stream_t stream) {
+  if (int rc = clear_amax("layernorm_mod_amax", amax_out, as_stream(stream))) return rc;
+  if (rows <= 0) return MXK_OK;
+  if (int rc = check_norm_common("layernorm_mod_amax", x, rows, dim, out, scale, shift)) return rc;
+  NormArgs a = make_args(x, rows, dim, eps, nullptr, scale, shift, out);
+  a.amax = amax_out;
+  return run_norm<0, float, false>("layernorm_mod_amax", a, as_stream(stream));
+}
+
+int mxk_rmsnorm_mod_amax(const float* x, int64_t rows, int64_t dim, float eps, const float* w, MxkRowMod scale,
+                         MxkRowMod shift, mxk_bf16* out, float* amax_out, mxk_stream_t stream) {
+  if (int rc = clear_amax("rmsnorm_mod_amax", amax_out, as_stream(stream))) return rc;
+  if (rows <= 0) return MXK_OK;
+  if (int rc = check_norm_common("rmsnorm_mod_amax", x, rows, dim, out, scale, shift)) return rc;
+  NormArgs a = make_args(x, rows, dim, eps, w, scale, shift, out);
+  a.amax = amax_out;
+  return run_norm<1, float, false>("rmsnorm_mod_amax", a, as_stream(stream));
+}
+
 int mxk_norm_path_probe(int op, const void* x, const void* y, const void* out, const float* w, MxkRowMod scale,
                         MxkRowMod shift, MxkRowMod gate, int64_t rows, int64_t dim) {
   if (rows <= 0 || dim <= 0 || dim > (int64_t(1) << 30)) return MXK_ERR_INVALID_ARG;

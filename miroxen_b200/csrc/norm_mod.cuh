@@ -41,6 +41,9 @@ struct NormArgs {
   uint8_t* q;
   uint8_t* sf;
   int nkb_pad;
+  // optional: max |out| over the launch, folded into *amax with atomicMax (the caller clears it first); what the
+  // NVFP4 quantiser needs before it can scale any block (src/kernels/blockscale.cu:47-70 is a pass of its own)
+  float* amax;
 };
 
 // Sum over the CTA; `red` is a 16-float scratch that must not be reused before the next
@@ -120,6 +123,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
   if (r0 < r1) fetch(r0);
 
   int parity = 0;
+  uint32_t run_max = 0u;  // two running bf16 maxima of this thread's outputs
   for (int64_t row = r0; row < r1; row++) {
     const int set = (row < a.scale.prefix_len ? 1 : 0) | (row < a.shift.prefix_len ? 2 : 0) |
                     (FUSE_RES && row < a.gate.prefix_len ? 4 : 0);
@@ -198,9 +202,14 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
       o[1] = o[1] * A[k].y + B[k].y;
       o[2] = o[2] * A[k].z + B[k].z;
       o[3] = o[3] * A[k].w + B[k].w;
-      if (on[k]) st_stream(reinterpret_cast<uint2*>(orow + 4 * (k * T + tid)), pack4(o));
+      if (on[k]) {
+        const uint2 pk = pack4(o);
+        st_stream(reinterpret_cast<uint2*>(orow + 4 * (k * T + tid)), pk);
+        if (a.amax) run_max = absmax_bf16x2(run_max, absmax_bf16x2(pk.x, pk.y));
+      }
     }
   }
+  if (a.amax) amax_commit(bf16x2_max_to_float(run_max), a.amax);
 }
 
 // ---- bulk-copy (TMA) pipelined variant ----------------------------------------------------------
@@ -271,6 +280,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
   unsigned phase = 0;
   int parity = 0;
   bool failed = false;
+  uint32_t run_max = 0u;  // two running bf16 maxima of this thread's outputs
   int64_t row = r0;
   for (; row < r1; row += step) {
     const int set = (row < a.scale.prefix_len ? 1 : 0) | (row < a.shift.prefix_len ? 2 : 0) |
@@ -386,6 +396,7 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
           if (on[k]) reinterpret_cast<uint2*>(dyn + size_t(stages) * stage_bytes)[k * T + tid] = pk;
         } else {
           if (on[k]) st_stream(reinterpret_cast<uint2*>(orow + 4 * (k * T + tid)), pk);
+          if (a.amax && on[k]) run_max = absmax_bf16x2(run_max, absmax_bf16x2(pk.x, pk.y));
         }
       }
       if constexpr (QUANT) {
@@ -413,6 +424,9 @@ __global__ void __launch_bounds__(norm_max_threads(VPT))
     }
   }
 
+  if constexpr (MODE != 2 && !QUANT) {
+    if (a.amax) amax_commit(bf16x2_max_to_float(run_max), a.amax);  // every thread of the CTA gets here
+  }
   if (failed && tid == 0) {
     if (a.err) atomicExch(a.err, kErrBulkTimeout);
     // Copies issued for rows [row, min(r1, row + stages)) may still be in flight into this CTA's
@@ -462,13 +476,17 @@ __global__ void __launch_bounds__(256) norm_rows_generic_kernel(const NormArgs a
   const float* sc = a.scale.target ? pick(a.scale, row) : nullptr;
   const float* sh = a.shift.target ? pick(a.shift, row) : nullptr;
   bf16* orow = a.out + row * a.dim;
+  float run_max = 0.f;
   for (int i = tid; i < a.dim; i += T) {
     float v = (ldx(i) - mean) * rstd;
     if (a.w) v *= a.w[i];
     if (sc) v *= 1.f + sc[i];
     if (sh) v += sh[i];
-    orow[i] = __float2bfloat16(v);
+    const bf16 o = __float2bfloat16(v);
+    orow[i] = o;
+    run_max = fmaxf(run_max, fabsf(bf16_to_f(o)));
   }
+  if (a.amax) amax_commit(run_max, a.amax);
 }
 
 // Launch plan shared by every instantiation: threads per CTA and vectors per thread.

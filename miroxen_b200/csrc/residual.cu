@@ -186,24 +186,45 @@ int mxk_gated_residual_bias(float* x, const mxk_bf16* y, const float* bias, int6
   return after_launch("gated_residual_bias");
 }
 
+static int gated_residual_norm_impl(const char* name, float* x, const mxk_bf16* y, int64_t rows, int64_t dim, MxkRowMod gate,
+                                    int gate_tanh, int norm_mode, float eps, const float* w, MxkRowMod scale, MxkRowMod shift,
+                                    mxk_bf16* out, float* amax_out, mxk_stream_t stream);
+
 int mxk_gated_residual_norm(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, MxkRowMod gate,
                             int gate_tanh, int norm_mode, float eps, const float* w,
                             MxkRowMod scale, MxkRowMod shift, mxk_bf16* out, mxk_stream_t stream) {
+  return gated_residual_norm_impl("gated_residual_norm", x, y, rows, dim, gate, gate_tanh, norm_mode, eps, w, scale, shift, out,
+                                  nullptr, stream);
+}
+
+int mxk_gated_residual_norm_amax(float* x, const mxk_bf16* y, int64_t rows, int64_t dim, MxkRowMod gate, int gate_tanh,
+                                 int norm_mode, float eps, const float* w, MxkRowMod scale, MxkRowMod shift, mxk_bf16* out,
+                                 float* amax_out, mxk_stream_t stream) {
+  if (!amax_out) return fail(MXK_ERR_INVALID_ARG, "gated_residual_norm_amax: null amax_out");
+  cudaError_t e = cudaMemsetAsync(amax_out, 0, sizeof(float), as_stream(stream));
+  if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "gated_residual_norm_amax: cudaMemsetAsync: %s", cudaGetErrorString(e));
+  return gated_residual_norm_impl("gated_residual_norm_amax", x, y, rows, dim, gate, gate_tanh, norm_mode, eps, w, scale, shift,
+                                  out, amax_out, stream);
+}
+
+static int gated_residual_norm_impl(const char* name, float* x, const mxk_bf16* y, int64_t rows, int64_t dim, MxkRowMod gate,
+                                    int gate_tanh, int norm_mode, float eps, const float* w, MxkRowMod scale, MxkRowMod shift,
+                                    mxk_bf16* out, float* amax_out, mxk_stream_t stream) {
   if (rows <= 0) return MXK_OK;
   if (norm_mode != 0 && norm_mode != 1)
-    return fail(MXK_ERR_INVALID_ARG, "gated_residual_norm: norm_mode=%d (0 LayerNorm, 1 RMSNorm)", norm_mode);
-  if (!y) return fail(MXK_ERR_INVALID_ARG, "gated_residual_norm: null y");
-  if (int rc = check_norm_common("gated_residual_norm", x, rows, dim, out, scale, shift)) return rc;
+    return fail(MXK_ERR_INVALID_ARG, "%s: norm_mode=%d (0 LayerNorm, 1 RMSNorm)", name, norm_mode);
+  if (!y) return fail(MXK_ERR_INVALID_ARG, "%s: null y", name);
+  if (int rc = check_norm_common(name, x, rows, dim, out, scale, shift)) return rc;
   if (gate.target && !gate.prefix && gate.prefix_len > 0)
-    return fail(MXK_ERR_INVALID_ARG, "gated_residual_norm: prefix_len > 0 with a null prefix vector");
+    return fail(MXK_ERR_INVALID_ARG, "%s: prefix_len > 0 with a null prefix vector", name);
   NormArgs a{};
   a.x = x, a.xw = x, a.y = reinterpret_cast<const bf16*>(y);
   a.gate = gate, a.gate_tanh = gate_tanh;
   a.rows = rows, a.dim = int(dim), a.nvec = int(dim / 4), a.eps = eps;
   a.w = norm_mode == 1 ? w : nullptr;
-  a.scale = scale, a.shift = shift, a.out = reinterpret_cast<bf16*>(out);
-  if (norm_mode == 0) return run_norm<0, float, true>("gated_residual_norm", a, as_stream(stream));
-  return run_norm<1, float, true>("gated_residual_norm", a, as_stream(stream));
+  a.scale = scale, a.shift = shift, a.out = reinterpret_cast<bf16*>(out), a.amax = amax_out;
+  if (norm_mode == 0) return run_norm<0, float, true>(name, a, as_stream(stream));
+  return run_norm<1, float, true>(name, a, as_stream(stream));
 }
 
 }  // extern "C"

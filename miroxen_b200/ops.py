@@ -29,6 +29,7 @@ __all__ = [
     "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8", "gated_residual_norm_quant_mxfp8",
     "qwen_latent_encode", "qwen_latent_decode", "h3_latent_video", "h3_latent_audio",
     "bias_gelu_tanh_inplace", "bias_silu_mul", "gated_residual_bias",
+    "quantize_nvfp4_known_amax", "layernorm_mod_amax", "rmsnorm_mod_amax", "gated_residual_norm_amax", "act_amax",
     "norm_path_probe", "NORM_PATH_GENERIC", "NORM_PATH_VECTOR", "NORM_PATH_BULK",
 ]
 
@@ -262,6 +263,37 @@ def act_quantize_mxfp8(act_mode: int, in_, rows: int, F: int, out: Optional[QMat
                    torch.empty(qscale_bytes(Q_MXFP8, rows, F), dtype=torch.uint8, device=in_.device))
     check(lib().mxk_act_quantize_mxfp8(act_mode, _p(in_), _p(bias), rows, F, _p(out.q), _p(out.sf), _stream(stream)))
     return out
+
+
+def quantize_nvfp4_known_amax(x, ldx: int, rows: int, K: int, amax, out: Optional[QMat] = None, stream=None) -> QMat:
+    """NVFP4 quantisation in one pass from a tensor maximum the producing op already left on the device
+    (`amax`, fp32 [1]; see the *_amax ops).  Same bytes as quantize_blockscaled(Q_NVFP4, ...)."""
+    if out is None:
+        out = QMat(torch.empty(qdata_bytes(Q_NVFP4, rows, K), dtype=torch.uint8, device=x.device),
+                   torch.empty(qscale_bytes(Q_NVFP4, rows, K), dtype=torch.uint8, device=x.device), amax)
+    check(lib().mxk_quantize_nvfp4_known_amax(_p(x), ldx, rows, K, _p(out.q), _p(out.sf), _p(amax), _stream(stream)))
+    return out
+
+
+def layernorm_mod_amax(x, rows, dim, eps, scale: RowMod, shift: RowMod, out, amax_out, stream=None):
+    check(lib().mxk_layernorm_mod_amax(_p(x), rows, dim, eps, scale or _NONE, shift or _NONE, _p(out), _p(amax_out), _stream(stream)))
+
+
+def rmsnorm_mod_amax(x, rows, dim, eps, w, scale: RowMod, shift: RowMod, out, amax_out, stream=None):
+    check(lib().mxk_rmsnorm_mod_amax(_p(x), rows, dim, eps, _p(w), scale or _NONE, shift or _NONE, _p(out), _p(amax_out),
+                                     _stream(stream)))
+
+
+def gated_residual_norm_amax(x, y, rows, dim, gate: RowMod, gate_tanh, norm_mode, eps, w, scale: RowMod, shift: RowMod, out,
+                             amax_out, stream=None):
+    check(lib().mxk_gated_residual_norm_amax(_p(x), _p(y), rows, dim, gate or _NONE, int(gate_tanh), norm_mode, eps, _p(w),
+                                             scale or _NONE, shift or _NONE, _p(out), _p(amax_out), _stream(stream)))
+
+
+def act_amax(act_mode: int, in_, rows: int, F: int, out, amax_out, bias=None, stream=None):
+    """The MLP activation (0 GELU-tanh, 1 silu_mul, 2 GELU-erf; optional bias first) writing bf16 `out` and the
+    tensor maximum of what it wrote."""
+    check(lib().mxk_act_amax(act_mode, _p(in_), _p(bias), rows, F, _p(out), _p(amax_out), _stream(stream)))
 
 
 def _qmat_for(x, rows, dim, out):
