@@ -60,6 +60,9 @@ def parse():
     ap.add_argument("--rows", type=int, default=0, help="run only the first ROWS rows of the workload (tuning aid)")
     ap.add_argument("--ops-only", action="store_true",
                     help="time only the isolated per-op figures (profiling / tuning aid; prints its own line)")
+    ap.add_argument("--linear-only", action="store_true",
+                    help="time only the linear layers with the residual in the GEMM epilogue against cuBLAS + the separate ops "
+                         "(prints its own line)")
     ap.add_argument("--quant-only", action="store_true",
                     help="time only the block-scale quantiser on the block's activations (profiling aid; prints its own line)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
@@ -495,6 +498,32 @@ class Job:
         ops = op_rows(w, names, [t / K * 1e3 for t in acc], self.rows, env.peak_gbs)
         return {"us_per_block": round(sum(o["us"] for o in ops), 1), "ops": ops}
 
+    def per_op_marginal(self, K, fused):
+        """Each op's cost inside the chain, launches overlapping as in the timed region: the chain's prefixes
+        (first op; first two ops; ...) are timed like the whole block and consecutive prefixes subtracted.
+        The figures add up to the block time by construction."""
+        env, mx, w = self.env, self.env.mx, self.w
+        keep_chain = self.chain
+        saved = []
+        for b in self.sets:
+            b.args.fused = fused
+            saved.append(b.args.chunk_rows)
+            b.args.chunk_rows = 0
+        names = ["norm_mod", "qkv_norm_rope", "gated_residual_norm", "act", "gated_residual"] if fused else dropin_op_names(w)
+        totals = []
+        for n in range(1, len(names) + 1):
+            step = lambda i, n=n: mx.dit_block_ops_prefix(self.sets[i % self.n_sets].args, n, env.stream)
+            for i in range(3):
+                step(i)
+            env.barrier()
+            totals.append(statistics.median([env.event_ms(step, K) / K * 1e3 for _ in range(5)]))
+        for b, c in zip(self.sets, saved):
+            b.args.chunk_rows = c
+        self.set_chain(keep_chain)
+        us = [totals[0]] + [max(totals[i] - totals[i - 1], 1e-3) for i in range(1, len(totals))]
+        ops = op_rows(w, names, us, self.rows, env.peak_gbs)
+        return {"us_per_block": round(totals[-1], 1), "ops": ops}
+
     def per_op_isolated(self, K):
         """Each op of the block timed on its own: K back-to-back launches of the same op over the rotating
         buffer sets (inputs never in L2; each launch's write-backs drain during the next launch of the same
@@ -856,6 +885,62 @@ def run_reference_cuda(args, W):
     print(json.dumps(line), flush=True)
 
 
+def linear_rows(env, w, rows, K):
+    """The two projections that feed a gated_residual (attention out-projection: K = H*D; second MLP
+    projection: K = F), as one tensor-core kernel with bias + gate + residual in its epilogue, against what it
+    replaces: the library GEMM (torch.matmul on bf16 = cuBLAS, the reference's linear()) + add_bias_bf16 +
+    gated_residual, and against the GEMM + this library's one-pass bias + residual."""
+    torch, mx = env.torch, env.mx
+    peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
+    peak_tf, src = (peaks["bf16_tflops"], "measured (burst)") if "bf16_tflops" in peaks else (1590.0, "fallback")
+    g = torch.Generator(device="cuda")
+    g.manual_seed(5)
+    N = w.dim
+    out = []
+    for name, Kd in (("attention out-projection", w.inner), ("second MLP projection", w.F)):
+        n_sets = max(2, math.ceil(3.2 * L2_BYTES / (rows * Kd * 2 + rows * N * 4)))
+        A = [torch.randn((rows, Kd), generator=g, device="cuda").to(torch.bfloat16) for _ in range(n_sets)]
+        W = (torch.randn((N, Kd), generator=g, device="cuda") / Kd ** 0.5).to(torch.bfloat16)
+        bias = torch.randn(N, generator=g, device="cuda") * 0.1
+        gate = mx.row_mod(torch.randn(N, generator=g, device="cuda") * 0.5)
+        x = [torch.randn((rows, N), generator=g, device="cuda") for _ in range(n_sets)]
+        y = [torch.empty((rows, N), dtype=torch.bfloat16, device="cuda") for _ in range(n_sets)]
+
+        def fused(i):
+            mx.ops.linear_gated_residual(A[i % n_sets], W, bias, rows, N, Kd, x[i % n_sets], gate, w.gate_tanh, env.stream)
+
+        def gemm_only(i):
+            torch.matmul(A[i % n_sets], W.T, out=y[i % n_sets])
+
+        def three_calls(i):
+            j = i % n_sets
+            torch.matmul(A[j], W.T, out=y[j])
+            mx.ops.add_bias_bf16(y[j], bias, rows, N, env.stream)
+            mx.ops.gated_residual(x[j], y[j], rows, N, gate, w.gate_tanh, env.stream)
+
+        def two_calls(i):
+            j = i % n_sets
+            torch.matmul(A[j], W.T, out=y[j])
+            mx.ops.gated_residual_bias(x[j], y[j], bias, rows, N, gate, w.gate_tanh, env.stream)
+
+        t = {}
+        for key, fn in (("fused", fused), ("cublas_gemm", gemm_only), ("cublas_bias_residual", three_calls), ("cublas_fused_bias_residual", two_calls)):
+            for i in range(3):
+                fn(i)
+            env.barrier()
+            t[key] = statistics.median([env.event_ms(fn, K) / K * 1e3 for _ in range(3)])
+        flops = 2.0 * rows * N * Kd
+        out.append({"layer": name, "M": rows, "N": N, "K": Kd, "us": round(t["fused"], 1),
+                    "tflops": round(flops / t["fused"] / 1e6, 1), "frac_of_bf16_peak": round(flops / t["fused"] / 1e6 / peak_tf, 3),
+                    "us_cublas_gemm_alone": round(t["cublas_gemm"], 1),
+                    "us_cublas_then_bias_then_residual": round(t["cublas_bias_residual"], 1),
+                    "us_cublas_then_fused_bias_residual": round(t["cublas_fused_bias_residual"], 1),
+                    "speedup_vs_reference_sequence": round(t["cublas_bias_residual"] / t["fused"], 3)})
+        del A, W, x, y
+    return {"what": "linear() + add_bias_bf16 + gated_residual as one tcgen05 kernel against cuBLAS + the separate ops",
+            "bf16_peak_tflops": peak_tf, "peak_source": src, "layers": out}
+
+
 def strong_record(env, w, K, splits):
     """Strong scaling of one workload inside this run: the whole workload on one GPU (every rank runs it,
     max over ranks), then each split of its rows over the ranks.  Times are ms per block, max over ranks."""
@@ -913,8 +998,8 @@ def main():
     else:
         rows, row0 = w.rows, 0
     if args.rows > 0:
-        if not (args.ops_only or args.quant_only):
-            raise SystemExit("--rows goes with --ops-only / --quant-only: the bench line is defined on the whole workload")
+        if not (args.ops_only or args.quant_only or args.linear_only):
+            raise SystemExit("--rows goes with --ops-only / --quant-only / --linear-only: the bench line is defined on the whole workload")
         rows = min(rows, args.rows)
     total_rows = w.rows * (n_gpus if scaling == "weak" else 1)
     job = Job(env, w, rows, row0, chain=args.chain)
@@ -925,6 +1010,12 @@ def main():
         if rank == 0:
             print(json.dumps({"impl": args.impl, "workload": w.name, "rows": rows, "steps": K, "tune": args.tune,
                               "per_op_isolated": job.per_op_isolated(K)}), flush=True)
+        return
+    if args.linear_only:
+        job.close()
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "workload": w.name, "rows": rows, "steps": K, "linear_epilogue": linear_rows(env, w, rows, K)}),
+                  flush=True)
         return
     if args.quant_only:
         if rank == 0:
@@ -954,12 +1045,17 @@ def main():
         line["timing"]["speedup_ceiling"] = round(w.rows / rows_max, 2)
 
     if not args.no_extras:
-        per_chain = {"dropin": job.per_op(K, 0), "fused": job.per_op(K, 1)}
+        chunked = w.chunk_rows > 0 and w.chunk_rows < rows
+        per_chain = {"dropin": job.per_op_marginal(K, 0), "fused": job.per_op_marginal(K, 1)}
         line["per_op"] = per_chain
+        line["per_op_events"] = {"dropin": job.per_op(K, 0), "fused": job.per_op(K, 1)}
         line["per_op_isolated"] = job.per_op_isolated(K)
-        line["per_op_note"] = ("per_op: events between the launches of a chain pass (an op also pays for the previous op's "
-                               "write-backs draining from L2); per_op_isolated: the same op launched back to back over "
-                               "rotating buffer sets, steady state")
+        line["per_op_note"] = ("per_op: each op's cost inside the chain, by timing the chain's prefixes and subtracting (the "
+                               "launches overlap as in the timed region and the figures add up to the block"
+                               + (", issued as one chunk here" if chunked else "") + "); per_op_events: events "
+                               "recorded between the launches, which serialises them (each interval also holds one whole launch "
+                               "latency and the previous op's write-backs); per_op_isolated: the op launched back to back over "
+                               "rotating buffer sets")
         ops = per_chain[args.chain]["ops"]
         top = max(ops, key=lambda o: o["us"])
         line["roofline"] = {"bound": "hbm", "kernel": top["op"], "achieved": top["gbs"], "peak": env.peak_gbs, "unit": "GB/s",
@@ -999,7 +1095,8 @@ def main():
         ms8, _, _, _ = small.timed(K, 3, repeats=5)
         line["shard_size"] = {"rows": sh8.rows, "of": "one rank of an 8-way row split", "us_per_block": round(ms8 * 1e3, 1),
                               "speedup_if_all_ranks_match": round(ms / ms8, 2),
-                              "per_op": {"dropin": small.per_op(K, 0), "fused": small.per_op(K, 1)}}
+                              "per_op": {"dropin": small.per_op_marginal(K, 0), "fused": small.per_op_marginal(K, 1)},
+                              "per_op_isolated": small.per_op_isolated(K)}
         small.set_chain("fused")
         msf, _, _, _ = small.timed(K, 3, repeats=5)
         line["shard_size"]["us_per_block_fused"] = round(msf * 1e3, 1)

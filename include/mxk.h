@@ -194,6 +194,24 @@ int mxk_peer_buffer_close(void* ptr);
 int mxk_peer_buffer_free(void* ptr);
 
 
+/* ---- linear layers with the following op in the GEMM epilogue ------------------------------- */
+/* The reference's linear() is a library GEMM that stores a bf16 matrix, followed by add_bias_bf16 as a
+ * read-modify-write of it (src/core/weights.cpp:159-177); the attention out-projection and the second
+ * MLP projection are then consumed by gated_residual (src/models/qwen_image/dit.cpp:304-305,313-314;
+ * src/models/minimax_h3/dit.cpp:238,245).  These entry points run the GEMM on the tensor cores
+ * (tcgen05.mma, accumulator in tensor memory, operands by TMA) and apply those ops in the epilogue with
+ * the reference's roundings, y = bf16(acc), y = bf16(y + bias), so the results are what the separate
+ * calls give up to the accumulation order of the GEMM.
+ *   A bf16 [M, K] row-major, W bf16 [N, K] row-major (the [out, in] weight layout), bias fp32 [N] or
+ *   NULL.  N % 32 == 0, K % 8 == 0, every pointer 16-byte aligned.
+ * mxk_linear_bf16:            y bf16 [M, N] = A W^T (+ bias)              = linear()
+ * mxk_linear_gated_residual:  x fp32 [M, N] += act(gate) * (A W^T (+ bias)) = linear() + gated_residual()
+ * No counterpart as single calls in the reference (each replaces two or three of its calls). */
+int mxk_linear_bf16(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, mxk_bf16* y,
+                    mxk_stream_t stream);
+int mxk_linear_gated_residual(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, float* x,
+                              MxkRowMod gate, int gate_tanh, mxk_stream_t stream);
+
 /* ---- RoPE tables and timestep embeddings ------------------------------------------------
  * The reference builds these on the host with libm and uploads them once per generation
  * (src/models/qwen_image/dit.cpp:151-185, src/models/minimax_h3/dit.cpp:254-262).  libm's
@@ -301,6 +319,12 @@ typedef struct MxkBlockArgs {
  * src/models/minimax_h3/dit.cpp:199-247: norm+mod, q/k(/v) head norm + rope, gated residual,
  * norm+mod, activation, gated residual. */
 int mxk_dit_block_ops(const MxkBlockArgs* a, mxk_stream_t stream);
+
+/* Measurement aid: only the first n_ops launches of that sequence (chunk_rows must be 0).  Timing the
+ * prefixes 1, 2, ... of a block and taking differences gives each op's cost inside the chain with the
+ * launches still overlapping as they do in mxk_dit_block_ops (events between the launches would
+ * serialise them). */
+int mxk_dit_block_ops_prefix(const MxkBlockArgs* a, int n_ops, mxk_stream_t stream);
 
 /* Per-op device timing of one mxk_dit_block_ops pass: a CUDA event is recorded on the stream before
  * the first op and after every op.  The handle owns 16 events (created here, not on the hot path). */

@@ -103,6 +103,8 @@ PROTOTYPES = {
     "mxk_peer_buffer_open": (_I, [_P, C.POINTER(_P)]),
     "mxk_peer_buffer_close": (_I, [_P]),
     "mxk_peer_buffer_free": (_I, [_P]),
+    "mxk_linear_bf16": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P]),
+    "mxk_linear_gated_residual": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, RowMod, _I, _P]),
     "mxk_rope_table_expand": (_I, [_P, _P, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32), _I,
                                    C.POINTER(RopeRun), _I, _I64, _I, _P, _P, _P]),
     "mxk_msrope_inv_freq_host": (_I, [C.POINTER(C.c_int32), _I, _F, _P]),
@@ -114,6 +116,7 @@ PROTOTYPES = {
     "mxk_qwen_timestep_embedding": (_I, [_F, _P, _P]),
     "mxk_h3_time_basis": (_I, [_P, _I64, _P, _I64, _I64, _P, _P]),
     "mxk_dit_block_ops": (_I, [C.POINTER(BlockArgs), _P]),
+    "mxk_dit_block_ops_prefix": (_I, [C.POINTER(BlockArgs), _I, _P]),
     "mxk_op_times_create": (_I, [C.POINTER(_P)]),
     "mxk_op_times_destroy": (None, [_P]),
     "mxk_dit_block_ops_timed": (_I, [C.POINTER(BlockArgs), _P, _P]),

@@ -63,10 +63,16 @@ struct OpTimer {
 };
 
 // Rows [r0, r0 + n) of the block.
-int block_rows(const MxkBlockArgs& a, int64_t r0, int64_t n, mxk_stream_t s, OpTimer* tm = nullptr) {
+int block_rows(const MxkBlockArgs& a, int64_t r0, int64_t n, mxk_stream_t s, OpTimer* tm = nullptr, int max_ops = 1 << 30) {
   OpTimer none;
   OpTimer& T = tm ? *tm : none;
   T.mark(s);
+  int ops_left = max_ops;
+#define MXK_OP_DONE()              \
+  do {                             \
+    if (--ops_left <= 0) return MXK_OK; \
+  } while (0)
+  if (ops_left <= 0) return MXK_OK;
   const int64_t dim = a.dim, inner = int64_t(a.H) * a.D, F = a.F, half = a.rot / 2;
   float* x = a.x + r0 * dim;
   mxk_bf16* h1 = a.h1 + r0 * dim;
@@ -79,6 +85,7 @@ int block_rows(const MxkBlockArgs& a, int64_t r0, int64_t n, mxk_stream_t s, OpT
   if (a.norm_mode == 0) MXK_TRY(mxk_layernorm_mod(x, n, dim, a.eps, sc1, sh1, h1, s));
   else MXK_TRY(mxk_rmsnorm_mod(x, n, dim, a.eps, a.norm1_w, sc1, sh1, h1, s));
   T.mark(s);
+  MXK_OP_DONE();
 
   MxkHeadTensor t[3];
   int nt = 0;
@@ -88,11 +95,13 @@ int block_rows(const MxkBlockArgs& a, int64_t r0, int64_t n, mxk_stream_t s, OpT
   if (a.fused) {
     MXK_TRY(mxk_qkv_norm_rope(t, nt, n, a.H, a.D, a.eps, cs, sn, s));
     T.mark(s);
+    MXK_OP_DONE();
   } else {
     for (int i = 0; i < nt; i++) {
       MXK_TRY(mxk_head_norm_rope(t[i].in, n, t[i].in_stride, t[i].col0, a.H, a.D, t[i].norm_w, i < 2 ? a.eps : 0.f,
                                  i < 2 ? cs : nullptr, i < 2 ? sn : nullptr, t[i].rot, t[i].mode, t[i].out, s));
       T.mark(s);
+      MXK_OP_DONE();
     }
   }
 
@@ -100,20 +109,25 @@ int block_rows(const MxkBlockArgs& a, int64_t r0, int64_t n, mxk_stream_t s, OpT
     MXK_TRY(mxk_gated_residual_norm(x, a.attn_o + r0 * dim, n, dim, g1, a.gate_tanh, a.norm_mode, a.eps, a.norm2_w, sc2,
                                     sh2, h2, s));
     T.mark(s);
+    MXK_OP_DONE();
   } else {
     MXK_TRY(mxk_gated_residual(x, a.attn_o + r0 * dim, n, dim, g1, a.gate_tanh, s));
     T.mark(s);
+    MXK_OP_DONE();
     if (a.norm_mode == 0) MXK_TRY(mxk_layernorm_mod(x, n, dim, a.eps, sc2, sh2, h2, s));
     else MXK_TRY(mxk_rmsnorm_mod(x, n, dim, a.eps, a.norm2_w, sc2, sh2, h2, s));
     T.mark(s);
+    MXK_OP_DONE();
   }
 
   if (a.act_mode == 0) MXK_TRY(mxk_gelu_tanh_inplace(a.act + r0 * F, n * F, s));
   else MXK_TRY(mxk_silu_mul(a.act2 + r0 * 2 * F, n, F, a.act + r0 * F, s));
   T.mark(s);
+  MXK_OP_DONE();
 
   MXK_TRY(mxk_gated_residual(x, a.mlp_o + r0 * dim, n, dim, g2, a.gate_tanh, s));
   T.mark(s);
+#undef MXK_OP_DONE
   return MXK_OK;
 }
 
@@ -156,6 +170,14 @@ int mxk_dit_block_ops(const MxkBlockArgs* a, mxk_stream_t stream) {
     if (int rc = block_rows(*a, r0, n, stream)) return rc;
   }
   return MXK_OK;
+}
+
+int mxk_dit_block_ops_prefix(const MxkBlockArgs* a, int n_ops, mxk_stream_t stream) {
+  if (int rc = check_block(a)) return rc;
+  if (a->chunk_rows > 0 && a->chunk_rows < a->rows)
+    return fail(MXK_ERR_INVALID_ARG, "dit_block_ops_prefix: covers one chunk (chunk_rows must be 0)");
+  if (a->rows == 0 || n_ops <= 0) return MXK_OK;
+  return block_rows(*a, 0, a->rows, stream, nullptr, n_ops);
 }
 
 int mxk_op_times_create(MxkOpTimes** out) {

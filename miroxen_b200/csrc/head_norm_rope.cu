@@ -46,6 +46,11 @@ struct RopeArgs {
   int rot, mode;    // shared by every rotating tensor of the launch
   int tpc;          // tokens per stage (one group)
   int64_t groups_per_cta;
+  // interleaved assignment: `full_rounds` rounds in which CTA i takes group round * grid + i (tpc tokens each);
+  // what is left (fewer than grid * tpc tokens, from tail_base on) is cut into one share of tail_tpc tokens per
+  // CTA, so that the last round keeps every CTA busy on a smaller piece instead of a few CTAs on whole groups
+  int full_rounds, tail_tpc;
+  int64_t tail_base;
   int interleave;   // 1: CTA i takes groups i, i + grid, ...; 0: a contiguous range of groups
   // head-group scatter (register kernel only): head h of tensor ti goes to scatter_out[ti][h / heads_per_group]
   // at row scatter_row0 + s of a [*, heads_per_group, D] array (a peer GPU's buffer, or this GPU's own)
@@ -403,20 +408,41 @@ __device__ __forceinline__ void rope_tokens_wide(const unsigned char* src, int t
   }
 }
 
+// First token and token count of this CTA's it-th group.
+__device__ __forceinline__ void rope_group(const RopeArgs& a, int it, int64_t g_begin, int64_t g_step, int64_t& s0, int& ntok) {
+  if (a.interleave) {
+    if (it < a.full_rounds) {
+      s0 = (int64_t(it) * gridDim.x + blockIdx.x) * a.tpc;
+      ntok = a.tpc;
+    } else {
+      s0 = a.tail_base + int64_t(blockIdx.x) * a.tail_tpc;
+      ntok = int(a.S - s0 < a.tail_tpc ? a.S - s0 : a.tail_tpc);
+    }
+  } else {
+    s0 = (g_begin + it * g_step) * a.tpc;
+    ntok = int(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
+  }
+}
+
 // The producer lane's loop: one group of `tpc` tokens per stage, in order; returns false when a
 // bounded wait on an `empty` barrier ran out.  `issued` counts the groups whose copies went out.
 __device__ __forceinline__ bool rope_produce(const RopeArgs& a, unsigned char* dyn, unsigned long long* full,
-                                             unsigned long long* empty, int64_t g_begin, int64_t g_step, int my_groups, int& issued) {
+                                             unsigned long long* empty, int64_t g_begin, int64_t g_step, int it_begin, int it_end,
+                                             int& issued) {
   const int half = a.rot >> 1;
   const bool rope = a.mode != MXK_ROPE_NONE && a.rot > 0;
+  // Called twice: for the first `stages` groups (no waits: every stage is free), before the CTA's set-up
+  // barrier, and for the rest after it.  it_begin is 0 or a.stages, so the ring starts at stage 0 either way.
   int st = 0;
   // Parity of the `empty` phase to wait for: the k-th refill of a stage (k >= 1) follows the
   // completion of its phase k - 1, so the first wait uses parity 0 and it flips per trip after that.
   unsigned ph = 0;
-  int64_t s0 = g_begin * a.tpc;
-  for (int it = 0; it < my_groups; it++, s0 += g_step * a.tpc) {
+  for (int it = it_begin; it < it_end; it++) {
     if (it >= a.stages && !mbar_wait(smem_u32(&empty[st]), ph)) return false;
-    const unsigned ntok = unsigned(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
+    int64_t s0;
+    int ntok_i;
+    rope_group(a, it, g_begin, g_step, s0, ntok_i);
+    const unsigned ntok = unsigned(ntok_i);
     const unsigned bar = smem_u32(&full[st]);
     const unsigned dst = smem_u32(dyn + size_t(st) * a.stage_bytes);
     unsigned bytes = rope ? 2u * ntok * unsigned(half) * 4u : 0u;
@@ -458,9 +484,11 @@ __global__ void __launch_bounds__(WIDE ? 160 : 544, MINB) head_rope_pipe_kernel(
   const int64_t g_step = a.interleave ? int64_t(gridDim.x) : 1;
   const int64_t g_begin = a.interleave ? int64_t(blockIdx.x) : int64_t(blockIdx.x) * a.groups_per_cta;
   const int64_t g_end = a.interleave ? n_groups : (g_begin + a.groups_per_cta < n_groups ? g_begin + a.groups_per_cta : n_groups);
-  const int my_groups = g_end > g_begin ? int((g_end - g_begin + g_step - 1) / g_step) : 0;
+  const int my_groups = a.interleave ? a.full_rounds + (a.tail_base + int64_t(blockIdx.x) * a.tail_tpc < a.S ? 1 : 0)
+                                     : (g_end > g_begin ? int((g_end - g_begin + g_step - 1) / g_step) : 0);
 
-  if (tid == 0) {
+  const bool producer = warp == n_cons_warps && lane == 0;
+  if (producer) {  // the barriers' first user initialises them: its copies go out before the CTA-wide barrier below
     for (int i = 0; i < a.stages; i++) {
       mbar_init(smem_u32(&full[i]), 1);
       mbar_init(smem_u32(&empty[i]), unsigned(n_cons_warps));
@@ -469,16 +497,18 @@ __global__ void __launch_bounds__(WIDE ? 160 : 544, MINB) head_rope_pipe_kernel(
   }
   pdl_launch_dependents();
   pdl_wait();  // nothing above touches global memory
+  bool ok = true;
+  int issued = 0;  // producer: groups whose copies were issued
+  // the first stages are on their way while the other warps fetch the norm weights
+  if (producer) ok = rope_produce(a, dyn, full, empty, g_begin, g_step, 0, my_groups < a.stages ? my_groups : a.stages, issued);
   for (int i = tid; i < a.n_tensors * a.D; i += blockDim.x) {
     const int ti = i / a.D, d = i - ti * a.D;
     wsm[ti][d] = a.t[ti].norm_w ? a.t[ti].norm_w[d] : 1.f;
   }
   __syncthreads();
 
-  bool ok = true;
-  int issued = 0;  // producer: groups whose copies were issued
   if (warp == n_cons_warps) {
-    if (lane == 0) ok = rope_produce(a, dyn, full, empty, g_begin, g_step, my_groups, issued);
+    if (lane == 0 && ok && my_groups > a.stages) ok = rope_produce(a, dyn, full, empty, g_begin, g_step, a.stages, my_groups, issued);
   } else if constexpr (WIDE) {
     const int l = tid % LPH;
     WideRole r;
@@ -498,14 +528,15 @@ __global__ void __launch_bounds__(WIDE ? 160 : 544, MINB) head_rope_pipe_kernel(
     const int tok_out_bytes = a.H * a.D * 2;
     int st = 0;
     unsigned ph = 0;
-    int64_t s0 = g_begin * a.tpc;
-    for (int it = 0; it < my_groups; it++, s0 += g_step * a.tpc) {
+    for (int it = 0; it < my_groups; it++) {
       if (!mbar_wait(smem_u32(&full[st]), ph)) {
         ok = false;
         break;
       }
       const unsigned char* stage = dyn + size_t(st) * a.stage_bytes;
-      const int ntok = int(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
+      int64_t s0;
+      int ntok;
+      rope_group(a, it, g_begin, g_step, s0, ntok);
       const float* cr = reinterpret_cast<const float*>(stage + a.cos_off);
       const float* sr = reinterpret_cast<const float*>(stage + a.sin_off);
 #pragma unroll 1
@@ -558,14 +589,15 @@ __global__ void __launch_bounds__(WIDE ? 160 : 544, MINB) head_rope_pipe_kernel(
 
     int st = 0;
     unsigned ph = 0;
-    int64_t s0 = g_begin * a.tpc;
-    for (int it = 0; it < my_groups; it++, s0 += g_step * a.tpc) {
+    for (int it = 0; it < my_groups; it++) {
       if (!mbar_wait(smem_u32(&full[st]), ph)) {
         ok = false;
         break;
       }
       const unsigned char* stage = dyn + size_t(st) * a.stage_bytes;
-      const int ntok = int(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
+      int64_t s0;
+      int ntok;
+      rope_group(a, it, g_begin, g_step, s0, ntok);
       const float* cr = reinterpret_cast<const float*>(stage + a.cos_off) + r.tab_idx;
       const float* sr = reinterpret_cast<const float*>(stage + a.sin_off) + r.tab_idx;
 #pragma unroll 1
@@ -763,7 +795,11 @@ int launch_pipe(const char* name, RopeArgs a, cudaStream_t stream) {
   a.groups_per_cta = ceil_div(n_groups, ctas);
   a.interleave = tune(TUNE_PIPE_INTERLEAVE, 1) == 1;
   a.err = device_error_word();
-  launch_pdl(k, dim3(unsigned(ceil_div(n_groups, a.groups_per_cta))), dim3(threads), smem, stream, a);
+  const int64_t grid = ceil_div(n_groups, a.groups_per_cta);
+  a.full_rounds = int(a.S / (grid * a.tpc));
+  a.tail_base = int64_t(a.full_rounds) * grid * a.tpc;
+  a.tail_tpc = int(ceil_div(a.S - a.tail_base, grid));  // 0 when the rounds cover every token
+  launch_pdl(k, dim3(unsigned(grid)), dim3(threads), smem, stream, a);
   return after_launch(name);
 }
 
@@ -776,14 +812,12 @@ int run(const char* name, RopeArgs a, cudaStream_t stream) {
   if (a.D == 128 && fast_ok(a) && tune(TUNE_ROPE_PATH, 1) == 1 && tune(TUNE_ROPE_WIDE, 1) == 1 && a.S >= 2 && pipe_plan(a, true)) {
     const bool exact = a.H == a.passes * a.heads_per_pass && (8 * a.heads_per_pass) % 32 == 0;
     if (exact && tune(TUNE_ROPE_UNROLL, 1) == 1 && 8 * a.heads_per_pass + 32 <= 160) {
-      // register budget of the unrolled kernel: 1 = sized for four 160-thread CTAs per SM (about 96), 2 = the
-      // compiler's choice (110-170), 3 = sized for five (72, with a few spilled values)
+      // register budget of the unrolled kernel: 1 = the compiler's choice (110-170 registers; measured best on
+      // the video shape and equal on the image shapes), 2 = held to four 160-thread CTAs per SM (96)
       const int regs = tune(TUNE_ROPE_WIDE_REGS, 1);
-#define MXK_WIDE_CASE(P)                                                                  \
-  case P:                                                                                 \
-    return regs == 3   ? launch_pipe<8, P, true, 5>(name, a, stream)                      \
-           : regs == 2 ? launch_pipe<8, P, true, 1>(name, a, stream)                      \
-                       : launch_pipe<8, P, true, 4>(name, a, stream)
+#define MXK_WIDE_CASE(P) \
+  case P:                \
+    return regs == 2 ? launch_pipe<8, P, true, 4>(name, a, stream) : launch_pipe<8, P, true, 1>(name, a, stream)
       switch (a.passes) {
         MXK_WIDE_CASE(1);
         MXK_WIDE_CASE(2);

@@ -1,0 +1,389 @@
+// Linear layer with the op that follows it folded into the GEMM epilogue (sm_100a: tcgen05 + TMEM + TMA).
+//
+// The reference runs every projection as a library GEMM that writes a bf16 matrix, then add_bias_bf16 as
+// a read-modify-write of that matrix (src/core/weights.cpp:159-177, `linear_one`), and for the attention
+// out-projection and the second MLP projection a gated_residual that reads it once more
+// (src/models/qwen_image/dit.cpp:304-305, 313-314; src/models/minimax_h3/dit.cpp:238, 245).  Here the GEMM
+// keeps its accumulator in tensor memory and the epilogue applies, per element and in the reference's
+// order and roundings,
+//     y  = bf16(acc)                       what the library GEMM would have stored
+//     y  = bf16(y + bias[col])             add_bias_bf16 (src/kernels/ops.cu:249-262), when a bias is given
+//     x += act(gate[col]) * y              gated_residual (src/kernels/ops.cu:73-84), EPI_RESIDUAL
+// so the bf16 projection output never exists in memory: 2·M·N bytes written and 4·M·N (bias) + 2·M·N
+// (residual) bytes re-read disappear.  EPI_STORE writes y as bf16 instead (a plain linear layer).
+//
+// y = A[M, K] · W[N, K]^T, both operands bf16 and K-major (activations row-major, weights in the
+// [out, in] layout the reference keeps them in), fp32 accumulation.
+//
+// Kernel shape: one persistent CTA per SM, 192 threads.
+//   warp 0, one lane:  TMA producer - 128 x 64 tiles of A and 256 x 64 tiles of W (128-byte swizzle) into a
+//                      4-stage shared-memory ring, completing on `full` mbarriers;
+//   warp 1, one lane:  issues tcgen05.mma (M 128, N 256, K 16, cta_group::1) from shared-memory descriptors
+//                      into one of two 256-column TMEM accumulators; tcgen05.commit releases a stage
+//                      (`empty`) and publishes a finished accumulator (`acc_full`);
+//   warps 2-5:         epilogue - each thread owns one row of the tile (its TMEM lane), reads the
+//                      accumulator 32 columns at a time (tcgen05.ld 32x32b), applies the chain above and
+//                      updates x with 128-bit accesses; the other accumulator is being filled meanwhile.
+// Every mbarrier wait is bounded (bulk_copy.cuh); on a timeout the role records kErrBulkTimeout in the
+// device error word and leaves its loop, the CTA still meets at the final barrier and frees its TMEM.
+// No cluster launch and no multi-CTA copies: the file may travel to multi-GPU runs.
+#include <cuda.h>
+
+#include <atomic>
+
+#include "bulk_copy.cuh"
+#include "common.cuh"
+
+namespace mxk {
+namespace {
+
+constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kStageA = BM * BK * 2, kStageB = BN * BK * 2;  // 16 KB + 32 KB
+constexpr int kAccCols = BN;                                  // fp32 columns of one accumulator
+constexpr int kTmemCols = 2 * kAccCols;                       // two accumulators: all 512 columns
+constexpr int kThreads = 192;
+constexpr int EPI_STORE = 0, EPI_RESIDUAL = 1;
+
+struct LinearArgs {
+  int64_t M, N, K;
+  const float* bias;  // fp32 [N] or null
+  bf16* y;            // EPI_STORE: bf16 [M, N]
+  float* x;           // EPI_RESIDUAL: fp32 [M, N], updated in place
+  MxkRowMod gate;     // EPI_RESIDUAL
+  int gate_tanh;
+  int* err;
+};
+
+struct __align__(1024) LinearSmem {
+  unsigned char a[kStages][kStageA];
+  unsigned char b[kStages][kStageB];
+  float bias[BN];           // the tile's bias slice (0 when absent)
+  float gate[2][BN];        // act(gate) for prefix rows [0] and target rows [1] (1 when absent)
+  unsigned long long full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  unsigned tmem_base;
+};
+
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+               "l"(map), "r"(bar), "r"(c0), "r"(c1)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_local(unsigned bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// AND of a predicate over the 128 epilogue threads (named barrier 1).
+__device__ __forceinline__ bool epilogue_all(bool v) {
+  unsigned r;
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(r)
+               : "r"(unsigned(v))
+               : "memory");
+  return r != 0;
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
+  unsigned r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, "
+      "%18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+        "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) wide under the
+// 128-byte swizzle: start address >> 4 in bits [0, 14); leading byte offset (unused by swizzled K-major
+// layouts) 1 in [16, 30); stride byte offset = 1024 (eight rows) >> 4 in [32, 46); descriptor version 1 in
+// [46, 48); layout type 2 (SWIZZLE_128B) in [61, 64).  The tile's base is 1024-byte aligned (base offset 0).
+__device__ __forceinline__ uint64_t smem_desc_sw128(unsigned addr) {
+  return uint64_t((addr & 0x3ffffu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+         (uint64_t(2) << 61);
+}
+// Instruction descriptor of kind::f16: fp32 accumulator (bits [4, 6) = 1), A and B bf16 ([7, 10) = [10, 13) = 1),
+// both K-major (bits 15, 16 = 0), N >> 3 in [17, 23), M >> 4 in [24, 29).
+constexpr unsigned kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (unsigned(BN >> 3) << 17) | (unsigned(BM >> 4) << 24);
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+    linear_epilogue_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const LinearArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  // dynamic shared memory is 16-byte aligned by contract; the tiles need 1024
+  LinearSmem& sm = *reinterpret_cast<LinearSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tiles_n = int((a.N + BN - 1) / BN), tiles_m = int((a.M + BM - 1) / BM);
+  const int n_tiles = tiles_m * tiles_n;
+  const int k_blocks = int((a.K + BK - 1) / BK);
+
+  if (tid == 0) {
+    for (int i = 0; i < kStages; i++) mbar_init(smem_u32(&sm.full[i]), 1), mbar_init(smem_u32(&sm.empty[i]), 1);
+    for (int i = 0; i < 2; i++) mbar_init(smem_u32(&sm.acc_full[i]), 1), mbar_init(smem_u32(&sm.acc_empty[i]), 4);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // one warp allocates (and later frees) the tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  pdl_launch_dependents();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = sm.tmem_base;
+  pdl_wait();  // nothing above touches global memory
+
+  bool ok = true;
+  long issued = 0;  // producer: stage fills issued so far
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer ----
+      int st = 0;
+      unsigned ph = 0;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+        for (int kb = 0; kb < k_blocks; kb++, issued++) {
+          if (issued >= kStages && !mbar_wait(smem_u32(&sm.empty[st]), ph ^ 1u)) {
+            ok = false;
+            break;
+          }
+          const unsigned bar = smem_u32(&sm.full[st]);
+          mbar_expect_tx(bar, kStageA + kStageB);
+          tma_load_2d(smem_u32(sm.a[st]), &map_a, kb * BK, m0, bar);
+          tma_load_2d(smem_u32(sm.b[st]), &map_w, kb * BK, n0, bar);
+          if (++st == kStages) st = 0, ph ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      int st = 0;
+      unsigned ph = 0;
+      int local = 0;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, local++) {
+        const int buf = local & 1;
+        // the epilogue must have drained this accumulator (its previous use was two tiles ago)
+        if (local >= 2 && !mbar_wait(smem_u32(&sm.acc_empty[buf]), unsigned(((local >> 1) - 1) & 1))) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const unsigned tmem_d = tmem_base + unsigned(buf * kAccCols);
+        for (int kb = 0; kb < k_blocks; kb++) {
+          if (!mbar_wait(smem_u32(&sm.full[st]), ph)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t da = smem_desc_sw128(smem_u32(sm.a[st])), db = smem_desc_sw128(smem_u32(sm.b[st]));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; k++)  // 32 bytes further along K per step: +2 in the (address >> 4) field
+            tc_mma(tmem_d, da + uint64_t(2 * k), db + uint64_t(2 * k), kInstrDesc, (kb | k) != 0 ? 1u : 0u);
+          tc_commit(smem_u32(&sm.empty[st]));  // the stage is free once these MMAs have read it
+          if (++st == kStages) st = 0, ph ^= 1u;
+        }
+        if (!ok) break;
+        tc_commit(smem_u32(&sm.acc_full[buf]));  // the accumulator is complete once every MMA so far has retired
+      }
+    }
+  } else {
+    // ---- epilogue: warps 2..5, each on the TMEM lane quarter its warp index selects ----
+    const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int et = tid - 64;  // 0..127
+    int local = 0;
+    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, local++) {
+      const int buf = local & 1;
+      const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+      // stage this tile's bias and act(gate) slices; the barrier (id 1, the four epilogue warps) also
+      // separates them from the previous tile's readers
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      for (int c = et; c < BN; c += 128) {
+        const int64_t col = n0 + c;
+        const bool in = col < a.N;
+        sm.bias[c] = (a.bias && in) ? a.bias[col] : 0.f;
+        if (EPI == EPI_RESIDUAL) {
+          float gp = 1.f, gt = 1.f;
+          if (a.gate.target && in) {
+            gt = a.gate.target[col];
+            gp = a.gate.prefix ? a.gate.prefix[col] : gt;
+            if (a.gate_tanh) gt = tanhf(gt), gp = tanhf(gp);
+          }
+          sm.gate[0][c] = gp, sm.gate[1][c] = gt;
+        }
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      // the four warps agree on the outcome of the wait, so that none is left alone at the next named barrier
+      const bool landed = mbar_wait(smem_u32(&sm.acc_full[buf]), unsigned((local >> 1) & 1));
+      if (!epilogue_all(landed)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int64_t row = int64_t(m0) + row_in_tile;
+      const bool row_on = row < a.M;
+      const float* g = sm.gate[(EPI == EPI_RESIDUAL && row < a.gate.prefix_len) ? 0 : 1];
+      const unsigned taddr = tmem_base + (unsigned(quarter * 32) << 16) + unsigned(buf * kAccCols);
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        float acc[32];
+        tc_ld32(taddr + unsigned(c0), acc);  // warp-wide: every lane takes part whether or not its row exists
+        if (!row_on || n0 + c0 >= a.N) continue;
+        if (EPI == EPI_RESIDUAL) {
+          float4* xr = reinterpret_cast<float4*>(a.x + row * a.N + n0 + c0);
+          float4 xv[8];
+#pragma unroll
+          for (int j = 0; j < 8; j++) xv[j] = xr[j];
+#pragma unroll
+          for (int j = 0; j < 8; j++) {
+            float y[4] = {acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]};
+            float o[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+              float v = __bfloat162float(__float2bfloat16(y[i]));                               // the GEMM's bf16 output
+              if (a.bias) v = __bfloat162float(__float2bfloat16(v + sm.bias[c0 + 4 * j + i]));  // add_bias_bf16
+              o[i] = fmaf(v, g[c0 + 4 * j + i], o[i]);                                          // gated_residual
+            }
+            xr[j] = make_float4(o[0], o[1], o[2], o[3]);
+          }
+        } else {
+          uint4* yr = reinterpret_cast<uint4*>(a.y + row * a.N + n0 + c0);
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              float v = __bfloat162float(__float2bfloat16(acc[8 * j + i]));
+              if (a.bias) v += sm.bias[c0 + 8 * j + i];
+              o[i] = v;
+            }
+            yr[j] = pack8(o);
+          }
+        }
+      }
+      // this warp is done reading the accumulator
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_local(smem_u32(&sm.acc_empty[buf]));
+    }
+  }
+
+  if (!ok && a.err) atomicExch(a.err, kErrBulkTimeout);
+  tc_fence_before();
+  // Every role's waits are bounded, so all threads arrive here.  After a failure the producer gives the
+  // copies of its last kStages fills a bounded chance to land before the CTA (and its shared memory) goes.
+  const bool any_failed = __syncthreads_or(!ok) != 0;
+  if (any_failed && tid == 0) {
+    for (long it = issued > kStages ? issued - kStages : 0; it < issued; it++)
+      mbar_wait(smem_u32(&sm.full[it % kStages]), unsigned((it / kStages) & 1));
+  }
+  if (any_failed) __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+  }
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link against libcuda).
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                              const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                              CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encode_fn() {
+  static std::atomic<EncodeFn> cached{nullptr};
+  EncodeFn f = cached.load(std::memory_order_acquire);
+  if (f) return f;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess || !p) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  f = reinterpret_cast<EncodeFn>(p);
+  cached.store(f, std::memory_order_release);
+  return f;
+}
+
+// bf16 [rows, K] row-major, boxes of box_rows x 64 elements, 128-byte swizzle; out-of-range parts of a box read as 0.
+int make_map(const char* name, CUtensorMap* map, const void* base, int64_t rows, int64_t K, int box_rows) {
+  EncodeFn enc = encode_fn();
+  if (!enc) return fail(MXK_ERR_CUDA, "%s: cuTensorMapEncodeTiled is not available from this driver", name);
+  const cuuint64_t dims[2] = {cuuint64_t(K), cuuint64_t(rows)};
+  const cuuint64_t strides[1] = {cuuint64_t(K) * 2};
+  const cuuint32_t box[2] = {cuuint32_t(BK), cuuint32_t(box_rows)};
+  const cuuint32_t elem[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(MXK_ERR_CUDA, "%s: cuTensorMapEncodeTiled failed with code %d", name, int(r));
+  return MXK_OK;
+}
+
+template <int EPI>
+int run_linear(const char* name, const mxk_bf16* A, const mxk_bf16* W, LinearArgs a, cudaStream_t s) {
+  if (a.M <= 0) return MXK_OK;
+  if (!A || !W) return fail(MXK_ERR_INVALID_ARG, "%s: null A or W", name);
+  if (a.N <= 0 || a.K <= 0 || a.N % 32 != 0 || a.K % 8 != 0 || a.M >= (int64_t(1) << 31) || a.N >= (int64_t(1) << 31) ||
+      a.K >= (int64_t(1) << 31))
+    return fail(MXK_ERR_INVALID_ARG, "%s: need N %% 32 == 0 and K %% 8 == 0 (N=%lld K=%lld)", name, (long long)a.N, (long long)a.K);
+  if (!aligned(A, 16) || !aligned(W, 16) || !aligned(a.bias, 16) || !aligned(a.x, 16) || !aligned(a.y, 16) ||
+      !aligned(a.gate.target, 16) || !aligned(a.gate.prefix, 16))
+    return fail(MXK_ERR_INVALID_ARG, "%s: every pointer must be 16-byte aligned", name);
+  if (a.gate.target && !a.gate.prefix && a.gate.prefix_len > 0)
+    return fail(MXK_ERR_INVALID_ARG, "%s: prefix_len > 0 with a null prefix vector", name);
+  CUtensorMap map_a, map_w;
+  if (int rc = make_map(name, &map_a, A, a.M, a.K, BM)) return rc;
+  if (int rc = make_map(name, &map_w, W, a.N, a.K, BN)) return rc;
+  auto k = linear_epilogue_kernel<EPI>;
+  const size_t smem = sizeof(LinearSmem) + 1024;
+  cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "%s: cudaFuncSetAttribute: %s", name, cudaGetErrorString(e));
+  const int64_t tiles = ceil_div(a.M, BM) * ceil_div(a.N, BN);
+  const int64_t grid = tiles < sm_count() ? tiles : sm_count();
+  a.err = device_error_word();
+  launch_pdl(k, dim3(unsigned(grid)), dim3(kThreads), smem, s, map_a, map_w, a);
+  return after_launch(name);
+}
+
+}  // namespace
+}  // namespace mxk
+
+using namespace mxk;
+
+extern "C" {
+
+int mxk_linear_bf16(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, mxk_bf16* y,
+                    mxk_stream_t stream) {
+  if (M > 0 && !y) return fail(MXK_ERR_INVALID_ARG, "linear_bf16: null y");
+  LinearArgs a{};
+  a.M = M, a.N = N, a.K = K, a.bias = bias, a.y = reinterpret_cast<bf16*>(y);
+  return run_linear<EPI_STORE>("linear_bf16", A, W, a, as_stream(stream));
+}
+
+int mxk_linear_gated_residual(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, float* x,
+                              MxkRowMod gate, int gate_tanh, mxk_stream_t stream) {
+  if (M > 0 && !x) return fail(MXK_ERR_INVALID_ARG, "linear_gated_residual: null x");
+  LinearArgs a{};
+  a.M = M, a.N = N, a.K = K, a.bias = bias, a.x = x, a.gate = gate, a.gate_tanh = gate_tanh;
+  return run_linear<EPI_RESIDUAL>("linear_gated_residual", A, W, a, as_stream(stream));
+}
+
+}  // extern "C"

@@ -24,12 +24,12 @@ __all__ = [
     "gated_residual", "add_inplace_bf16", "head_norm_rope", "silu_mul", "gelu_tanh_inplace", "gelu_erf_inplace",
     "scatter_rows", "silu_inplace_f32", "add_bias_bf16", "add_bias_f32", "f32_to_bf16", "bf16_to_f32", "axpy_f32",
     "axpby_f32", "gated_residual_norm", "qkv_norm_rope", "HeadSpec", "dit_block_ops", "BlockArgs", "RowMod",
-    "HostPipeline", "OpTimes", "dit_block_ops_host_static", "device_error", "launch_count", "reset_launch_count", "set_tuning",
+    "HostPipeline", "OpTimes", "dit_block_ops_prefix", "dit_block_ops_host_static", "device_error", "launch_count", "reset_launch_count", "set_tuning",
     "Q_MXFP8", "Q_NVFP4", "QMat", "qdata_bytes", "qscale_bytes", "quantize_blockscaled", "act_quantize_mxfp8",
     "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8", "gated_residual_norm_quant_mxfp8",
     "qwen_latent_encode", "qwen_latent_decode", "h3_latent_video", "h3_latent_audio",
     "bias_gelu_tanh_inplace", "bias_silu_mul", "gated_residual_bias",
-    "quantize_nvfp4_known_amax", "layernorm_mod_amax", "rmsnorm_mod_amax", "gated_residual_norm_amax", "act_amax",
+    "linear_bf16", "linear_gated_residual", "quantize_nvfp4_known_amax", "layernorm_mod_amax", "rmsnorm_mod_amax", "gated_residual_norm_amax", "act_amax",
     "norm_path_probe", "NORM_PATH_GENERIC", "NORM_PATH_VECTOR", "NORM_PATH_BULK",
 ]
 
@@ -170,6 +170,11 @@ def dit_block_ops(args: BlockArgs, stream=None):
     check(lib().mxk_dit_block_ops(C.byref(args), _stream(stream)))
 
 
+def dit_block_ops_prefix(args: BlockArgs, n_ops: int, stream=None):
+    """Only the first n_ops launches of dit_block_ops (measurement aid)."""
+    check(lib().mxk_dit_block_ops_prefix(C.byref(args), int(n_ops), _stream(stream)))
+
+
 class OpTimes:
     """mxk_op_times_*: per-op CUDA-event timing of a block pass."""
 
@@ -294,6 +299,16 @@ def act_amax(act_mode: int, in_, rows: int, F: int, out, amax_out, bias=None, st
     """The MLP activation (0 GELU-tanh, 1 silu_mul, 2 GELU-erf; optional bias first) writing bf16 `out` and the
     tensor maximum of what it wrote."""
     check(lib().mxk_act_amax(act_mode, _p(in_), _p(bias), rows, F, _p(out), _p(amax_out), _stream(stream)))
+
+
+def linear_bf16(A, W, bias, M, N, K, y, stream=None):
+    """y bf16 [M, N] = A [M, K] @ W [N, K]^T (+ bias): the reference's linear() as one tensor-core kernel."""
+    check(lib().mxk_linear_bf16(_p(A), _p(W), _p(bias), M, N, K, _p(y), _stream(stream)))
+
+
+def linear_gated_residual(A, W, bias, M, N, K, x, gate: RowMod, gate_tanh, stream=None):
+    """x fp32 [M, N] += act(gate) * bf16(A @ W^T (+ bias)): linear() and gated_residual() in one kernel."""
+    check(lib().mxk_linear_gated_residual(_p(A), _p(W), _p(bias), M, N, K, _p(x), gate or _NONE, int(gate_tanh), _stream(stream)))
 
 
 def _qmat_for(x, rows, dim, out):

@@ -62,7 +62,18 @@ def test_scatter_equals_the_dense_layout_group_by_group(mx, world, S, Hh, D, rot
     sp = specs_for(mx, qkv, nq, nk, inner, rot, mode)
     for t, o in zip(sp, dense):
         t.out = o
+    # the scatter runs on the register head kernel: the dense result of the same kernel family is its bit-exact
+    # counterpart (the bulk-copy pipeline, the default for the dense call, rounds a few elements the other way)
+    mx.set_tuning("rope_path", 2)
     mx.qkv_norm_rope(sp, S, Hh, D, 1e-6, cos, sin)
+    mx.set_tuning("rope_path", 0)
+    piped = [torch.empty((S, Hh, D), dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    for t, o in zip(sp, piped):
+        t.out = o
+    mx.qkv_norm_rope(sp, S, Hh, D, 1e-6, cos, sin)
+    torch.cuda.synchronize()
+    for o, p_ in zip(dense, piped):
+        H.assert_bf16_close(H.bits(o), H.bits(p_), "register vs pipeline head kernel")
     # G "ranks", every destination on this GPU
     bufs = [[H.Guarded(torch, (S, hg, D), torch.bfloat16) for _ in range(world)] for _ in range(3)]
     for r in range(world):
@@ -127,7 +138,9 @@ def _rank_main(rank, world, port, out_dir):
     sp = specs_for(mx, qkv, nq, nk, inner, rot, mode)
     for t, o in zip(sp, dense):
         t.out = o
+    mx.set_tuning("rope_path", 2)  # the kernel family the scatter uses: bit-exact counterpart
     mx.qkv_norm_rope(sp, S, Hh, D, 1e-6, cos, sin)
+    mx.set_tuning("rope_path", 0)
     ex = HeadExchange(plan, rank)
     ok = True
     try:

@@ -1,0 +1,104 @@
+"""The tensor-core linear layer with the following op in its epilogue (mxk_linear_bf16,
+mxk_linear_gated_residual) against the calls it replaces: the library GEMM (torch.matmul on bf16,
+i.e. cuBLAS, which is what the reference's linear() calls, src/core/weights.cpp:159-177), then
+mxk_add_bias_bf16, then mxk_gated_residual.  The GEMMs accumulate in different orders, so a bf16
+output may differ by one unit in the last place (tolerance of tests/helpers.py, stated there); the
+residual stream may then differ by |act(gate)| times that."""
+import numpy as np
+import pytest
+
+import helpers as H
+
+torch = pytest.importorskip("torch")
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def mx():
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import miroxen_b200 as m
+    m.lib()
+    yield m
+    torch.cuda.synchronize()
+    assert m.device_error() == 0, "a bounded wait of the GEMM ran out"
+
+
+def operands(M, N, K, seed):
+    g = torch.Generator(device="cuda")
+    g.manual_seed(seed)
+    A = torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16)
+    W = (torch.randn((N, K), generator=g, device="cuda") / (K ** 0.5)).to(torch.bfloat16)
+    bias = torch.randn(N, generator=g, device="cuda") * 0.1
+    return A, W, bias
+
+
+SHAPES = [(128, 256, 64), (256, 512, 128), (1000, 3072, 3072), (5, 320, 200), (129, 32, 8), (2176, 3072, 12288), (300, 5120, 1024)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_linear_bf16_equals_the_fp32_product(mx, M, N, K, with_bias):
+    A, W, bias = operands(M, N, K, M + N + K)
+    y = H.Guarded(torch, (M, N), torch.bfloat16)
+    mx.linear_bf16(A, W, bias if with_bias else None, M, N, K, y.t)
+    torch.cuda.synchronize()
+    y.check("linear y")
+    ref = (A.float() @ W.float().T).to(torch.bfloat16)      # fp32 accumulate, rounded as the GEMM output is
+    if with_bias:
+        ref = (ref.float() + bias).to(torch.bfloat16)       # add_bias_bf16
+    H.assert_bf16_close(H.bits(y.t), H.bits(ref), f"linear {M}x{N}x{K} bias={with_bias}")
+    # and against the library GEMM the reference calls
+    lib_y = A @ W.T
+    if with_bias:
+        mx.add_bias_bf16(lib_y, bias, M, N)
+    torch.cuda.synchronize()
+    H.assert_bf16_close(H.bits(y.t), H.bits(lib_y), f"linear vs cuBLAS {M}x{N}x{K}")
+
+
+@pytest.mark.parametrize("M,N,K", [(1000, 3072, 3072), (272, 3072, 12288), (130, 5120, 512), (5, 320, 200)])
+@pytest.mark.parametrize("mode", ["tanh_prefix_bias", "identity", "none"])
+def test_linear_gated_residual_equals_the_separate_calls(mx, M, N, K, mode):
+    A, W, bias = operands(M, N, K, M + K)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(7)
+    x0 = torch.randn((M, N), generator=g, device="cuda")
+    gt, gp = torch.randn(N, generator=g, device="cuda") * 0.7, torch.randn(N, generator=g, device="cuda") * 0.7
+    if mode == "tanh_prefix_bias":
+        gate, tanh, b = mx.row_mod(gt, gp, M // 2 + 1), 1, bias
+    elif mode == "identity":
+        gate, tanh, b = mx.row_mod(gt), 0, None
+    else:
+        gate, tanh, b = None, 0, None
+    # the calls it replaces
+    y = A @ W.T
+    if b is not None:
+        mx.add_bias_bf16(y, b, M, N)
+    x_ref = x0.clone()
+    mx.gated_residual(x_ref, y, M, N, gate, tanh)
+    x = H.Guarded(torch, (M, N), torch.float32, fill=x0)
+    mx.linear_gated_residual(A, W, b, M, N, K, x.t, gate, tanh)
+    torch.cuda.synchronize()
+    x.check("fused x")
+    # |x - x_ref| <= |act(gate)| * (one bf16 ulp of y, or the floor of tests/helpers.py) + fp32 rounding of the update
+    act = torch.ones(N, device="cuda") if gate is None else (torch.tanh(gt) if tanh else gt)
+    bound_rows = act.abs().expand(M, N).clone()
+    if mode == "tanh_prefix_bias":
+        bound_rows[:M // 2 + 1] = torch.tanh(gp).abs()
+    ulp = torch.maximum(y.float().abs(), torch.tensor(H.BF16_FLOOR, device="cuda")) * H.BF16_REL
+    tol = bound_rows * ulp + H.F32_REL * torch.maximum(x_ref.abs(), torch.tensor(1.0, device="cuda"))
+    err = (x.t - x_ref).abs()
+    assert bool((err <= tol).all()), f"{int((err > tol).sum())} of {err.numel()} beyond tolerance, worst {float((err - tol).max()):.3e}"
+    # the two GEMMs round nearly every element the same way: the results should agree exactly almost everywhere
+    assert float((x.t != x_ref).float().mean()) < 0.02
+
+
+def test_linear_argument_checks(mx):
+    L = mx.lib()
+    from miroxen_b200._lib import RowMod
+    none = RowMod(None, None, 0)
+    assert L.mxk_linear_bf16(256, 256, None, 4, 33, 64, 256, None) == -1      # N % 32
+    assert L.mxk_linear_bf16(256, 256, None, 4, 64, 12, 256, None) == -1      # K % 8
+    assert L.mxk_linear_bf16(258, 256, None, 4, 64, 64, 256, None) == -1      # alignment
+    assert L.mxk_linear_bf16(None, None, None, 0, 64, 64, None, None) == 0    # no rows
+    assert L.mxk_linear_gated_residual(256, 256, None, 4, 64, 64, None, none, 0, None) == -1
