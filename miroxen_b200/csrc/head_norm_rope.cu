@@ -431,8 +431,6 @@ __device__ __forceinline__ bool rope_produce(const RopeArgs& a, unsigned char* d
                                              int& issued) {
   const int half = a.rot >> 1;
   const bool rope = a.mode != MXK_ROPE_NONE && a.rot > 0;
-  // Called twice: for the first `stages` groups (no waits: every stage is free), before the CTA's set-up
-  // barrier, and for the rest after it.  it_begin is 0 or a.stages, so the ring starts at stage 0 either way.
   int st = 0;
   // Parity of the `empty` phase to wait for: the k-th refill of a stage (k >= 1) follows the
   // completion of its phase k - 1, so the first wait uses parity 0 and it flips per trip after that.
@@ -468,9 +466,10 @@ __device__ __forceinline__ bool rope_produce(const RopeArgs& a, unsigned char* d
   return true;
 }
 
-// MINB (wide mapping only): resident CTAs per SM the register allocation is held to.
-template <int LPH, int PASSES = 0, bool WIDE = false, int MINB = 1>
-__global__ void __launch_bounds__(WIDE ? 160 : 544, MINB) head_rope_pipe_kernel(const RopeArgs a) {
+// MINB (wide mapping only): 1 = CTAs of up to 128 threads, four per SM (at most 128 registers: one register more
+// would cost the fourth CTA); 4 = CTAs of up to 160 threads, four per SM (96 registers); 0 = no promise.
+template <int LPH, int PASSES = 0, bool WIDE = false, int MINB = 0>
+__global__ void __launch_bounds__(!WIDE ? 544 : MINB == 1 ? 128 : 160, MINB == 0 ? 1 : 4) head_rope_pipe_kernel(const RopeArgs a) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ __align__(8) unsigned long long full[8], empty[8];
   __shared__ __align__(16) float wsm[kMaxTensors][256];  // the tensors' norm weights
@@ -487,8 +486,7 @@ __global__ void __launch_bounds__(WIDE ? 160 : 544, MINB) head_rope_pipe_kernel(
   const int my_groups = a.interleave ? a.full_rounds + (a.tail_base + int64_t(blockIdx.x) * a.tail_tpc < a.S ? 1 : 0)
                                      : (g_end > g_begin ? int((g_end - g_begin + g_step - 1) / g_step) : 0);
 
-  const bool producer = warp == n_cons_warps && lane == 0;
-  if (producer) {  // the barriers' first user initialises them: its copies go out before the CTA-wide barrier below
+  if (tid == 0) {
     for (int i = 0; i < a.stages; i++) {
       mbar_init(smem_u32(&full[i]), 1);
       mbar_init(smem_u32(&empty[i]), unsigned(n_cons_warps));
@@ -497,18 +495,16 @@ __global__ void __launch_bounds__(WIDE ? 160 : 544, MINB) head_rope_pipe_kernel(
   }
   pdl_launch_dependents();
   pdl_wait();  // nothing above touches global memory
-  bool ok = true;
-  int issued = 0;  // producer: groups whose copies were issued
-  // the first stages are on their way while the other warps fetch the norm weights
-  if (producer) ok = rope_produce(a, dyn, full, empty, g_begin, g_step, 0, my_groups < a.stages ? my_groups : a.stages, issued);
   for (int i = tid; i < a.n_tensors * a.D; i += blockDim.x) {
     const int ti = i / a.D, d = i - ti * a.D;
     wsm[ti][d] = a.t[ti].norm_w ? a.t[ti].norm_w[d] : 1.f;
   }
   __syncthreads();
 
+  bool ok = true;
+  int issued = 0;  // producer: groups whose copies were issued
   if (warp == n_cons_warps) {
-    if (lane == 0 && ok && my_groups > a.stages) ok = rope_produce(a, dyn, full, empty, g_begin, g_step, a.stages, my_groups, issued);
+    if (lane == 0) ok = rope_produce(a, dyn, full, empty, g_begin, g_step, 0, my_groups, issued);
   } else if constexpr (WIDE) {
     const int l = tid % LPH;
     WideRole r;
@@ -782,7 +778,7 @@ bool pipe_plan(RopeArgs& a, bool wide = false) {
   return size_t(stages) * a.stage_bytes <= 200 * 1024;
 }
 
-template <int LPH, int PASSES = 0, bool WIDE = false, int MINB = 1>
+template <int LPH, int PASSES = 0, bool WIDE = false, int MINB = 0>
 int launch_pipe(const char* name, RopeArgs a, cudaStream_t stream) {
   auto k = head_rope_pipe_kernel<LPH, PASSES, WIDE, MINB>;
   const int threads = int(ceil_div(int64_t(LPH) * a.heads_per_pass, 32) * 32) + 32;  // consumers + producer warp
@@ -812,12 +808,12 @@ int run(const char* name, RopeArgs a, cudaStream_t stream) {
   if (a.D == 128 && fast_ok(a) && tune(TUNE_ROPE_PATH, 1) == 1 && tune(TUNE_ROPE_WIDE, 1) == 1 && a.S >= 2 && pipe_plan(a, true)) {
     const bool exact = a.H == a.passes * a.heads_per_pass && (8 * a.heads_per_pass) % 32 == 0;
     if (exact && tune(TUNE_ROPE_UNROLL, 1) == 1 && 8 * a.heads_per_pass + 32 <= 160) {
-      // register budget of the unrolled kernel: 1 = the compiler's choice (110-170 registers; measured best on
-      // the video shape and equal on the image shapes), 2 = held to four 160-thread CTAs per SM (96)
-      const int regs = tune(TUNE_ROPE_WIDE_REGS, 1);
+      // register budget of the unrolled kernel: CTAs of at most 128 threads are held to 128 registers (four CTAs
+      // per SM), larger ones (32 heads: 160 threads) to 96; rope_wide_regs = 2 asks for 96 everywhere
+      const bool small = 8 * a.heads_per_pass + 32 <= 128 && tune(TUNE_ROPE_WIDE_REGS, 1) == 1;
 #define MXK_WIDE_CASE(P) \
   case P:                \
-    return regs == 2 ? launch_pipe<8, P, true, 4>(name, a, stream) : launch_pipe<8, P, true, 1>(name, a, stream)
+    return small ? launch_pipe<8, P, true, 1>(name, a, stream) : launch_pipe<8, P, true, 4>(name, a, stream)
       switch (a.passes) {
         MXK_WIDE_CASE(1);
         MXK_WIDE_CASE(2);
