@@ -33,7 +33,7 @@ enum TuneKey {
   TUNE_QUANT_ROWS_PER_CTA, // rows per work item of the block-scale quantiser
   TUNE_QUANT_PATH,         // 1 bulk-copy streaming pipeline for the quantiser, 2 register kernels
   TUNE_ROPE_UNROLL,        // 1: head pipeline with the pass loop unrolled where the shape allows (default), 2: runtime loop
-  TUNE_ROPE_WIDE,          // 1: sixteen channels per lane for D = 128 (default), 2: eight channels per lane
+  TUNE_ROPE_WIDE,          // 1: sixteen channels per lane for D = 128, 2: eight channels per lane (default)
   TUNE_ROPE_WIDE_REGS,     // wide head kernel's register budget: 1 = 128 registers for CTAs of up to 128 threads (default), 2 = 96 everywhere
   TUNE_COUNT
 };

@@ -12,22 +12,25 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module", params=["bulk_copy", "registers"])
+@pytest.fixture(scope="module", params=["bulk_copy", "registers", "bulk_copy_wide_heads"])
 def mx(request):
-    """Every test runs twice: with the bulk-copy (TMA) pipelined row / head kernels, which are the
-    default, and with the register-prefetch kernels that serve the shapes the bulk copies cannot."""
+    """Every test runs three times: with the bulk-copy (TMA) pipelined row / head kernels, which are the
+    default; with the register-prefetch kernels that serve the shapes the bulk copies cannot; and with the
+    head pipeline's sixteen-channels-per-lane mapping (D = 128 shapes; the others fall to the default)."""
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     import miroxen_b200 as m
     m.lib()  # raises if libmxk.so is missing - there is no fallback
-    path = 1 if request.param == "bulk_copy" else 2
+    path = 2 if request.param == "registers" else 1
     m.set_tuning("norm_path", path)
     m.set_tuning("rope_path", path)
+    m.set_tuning("rope_wide", 1 if request.param == "bulk_copy_wide_heads" else 0)
     yield m
     torch.cuda.synchronize()
     assert m.device_error() == 0, "a kernel's bounded wait ran out"
     m.set_tuning("norm_path", 0)
     m.set_tuning("rope_path", 0)
+    m.set_tuning("rope_wide", 0)
 
 
 def dev_mod(mx, keep, target=None, prefix=None, prefix_len=0):
