@@ -63,6 +63,8 @@ def parse():
     ap.add_argument("--linear-only", action="store_true",
                     help="time only the linear layers with the residual in the GEMM epilogue against cuBLAS + the separate ops "
                          "(prints its own line)")
+    ap.add_argument("--exchange-only", action="store_true",
+                    help="time only the head exchange of sequence-parallel attention over the ranks' peer buffers (N >= 1)")
     ap.add_argument("--quant-only", action="store_true",
                     help="time only the block-scale quantiser on the block's activations (profiling aid; prints its own line)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
@@ -941,6 +943,75 @@ def linear_rows(env, w, rows, K):
             "bf16_peak_tflops": peak_tf, "peak_source": src, "layers": out}
 
 
+def exchange_rows(env, w, K):
+    """Head exchange of the sequence-parallel attention path on this job's ranks: every rank norm+ropes the q / k / v
+    heads of its row shard and stores each head group into its owner's [S, H/G, D] buffer (peer stores over NVLink),
+    then gathers all heads of its rows back from everybody's buffer (peer loads).  Times are max over ranks."""
+    from miroxen_b200.head_exchange import ExchangePlan, HeadExchange
+    torch, mx = env.torch, env.mx
+    G, rank = env.world, env.rank
+    plan = ExchangePlan(w.rows, w.H, w.D, G)
+    sh = plan.rows(rank)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(100 + rank)
+    inner = w.inner
+    n_sets = max(2, math.ceil(3.2 * L2_BYTES / (sh.rows * 3 * inner * 2)))
+    qkv = [torch.randn((sh.rows, 3 * inner), generator=g, device="cuda").to(torch.bfloat16) for _ in range(n_sets)]
+    nq = 1 + 0.05 * torch.randn(w.D, generator=g, device="cuda")
+    nk = 1 + 0.05 * torch.randn(w.D, generator=g, device="cuda")
+    ang = torch.rand((sh.rows, max(w.rot // 2, 1)), generator=g, device="cuda") * 6.2 - 3.1
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    out = torch.empty((sh.rows, inner), dtype=torch.bfloat16, device="cuda")
+    ex = HeadExchange(plan, rank)
+    try:
+        def specs(t):
+            return [mx.HeadSpec(t, 3 * inner, 0, nq, None, w.rot, w.rope_mode), mx.HeadSpec(t, 3 * inner, inner, nk, None, w.rot, w.rope_mode),
+                    mx.HeadSpec(t, 3 * inner, 2 * inner, None, None, 0, 0)]
+        sp = [specs(t) for t in qkv]
+        scatter = lambda i: ex.scatter_qkv(sp[i % n_sets], sh.rows, w.eps, cos, sin, stream=env.stream)
+        gather = lambda i: ex.gather_heads(out, buffer=0, stream=env.stream)
+        res = {}
+        for name, fn in (("scatter_qkv", scatter), ("gather_heads", gather)):
+            for i in range(3):
+                fn(i)
+            env.barrier()
+            reps = []
+            for _ in range(5):
+                ms = env.event_ms(fn, K) / K
+                env.barrier()
+                reps.append(env.max_over_ranks(ms))
+            res[name] = statistics.median(reps) * 1e3
+        # the local (single-GPU) form of the same work, for the cost of going over NVLink
+        dense = [torch.empty((sh.rows, w.H, w.D), dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+        dsp = [[mx.HeadSpec(t.in_, t.in_stride, t.col0, t.norm_w, o, t.rot, t.mode) for t, o in zip(s_, dense)] for s_ in sp]
+        local = lambda i: mx.qkv_norm_rope(dsp[i % n_sets], sh.rows, w.H, w.D, w.eps, cos, sin, env.stream)
+        for i in range(3):
+            local(i)
+        env.barrier()
+        res["local_qkv_norm_rope"] = env.max_over_ranks(env.event_ms(local, K) / K) * 1e3
+        env.barrier()
+    finally:
+        ex.barrier()
+        ex.close()
+    send = plan.send_bytes(rank, 3)
+    back = sh.rows * inner * 2 * (G - 1) // G
+    link = 770.0  # GB/s per direction per GPU, the measured peer-copy rate on this pool (900 nominal)
+    rec = {"workload": w.name, "n_gpus": G, "rows_per_gpu": sh.rows, "heads_per_group": plan.heads_per_group,
+           "scatter_qkv": {"us": round(res["scatter_qkv"], 1), "nvlink_bytes_per_rank": send,
+                           "formula": "3 * rows * H * D * 2 * (G - 1) / G",
+                           "nvlink_gbs_per_rank": round(send / res["scatter_qkv"] / 1e3, 1) if G > 1 else 0.0,
+                           "frac_of_peer_copy_rate": round(send / res["scatter_qkv"] / 1e3 / link, 3) if G > 1 else None,
+                           "us_local_qkv_norm_rope": round(res["local_qkv_norm_rope"], 1),
+                           "hbm_bytes_per_rank": sh.rows * (3 * inner * 2 * 2 + 2 * (w.rot // 2) * 4)},
+           "gather_heads": {"us": round(res["gather_heads"], 1), "nvlink_bytes_per_rank": back,
+                            "nvlink_gbs_per_rank": round(back / res["gather_heads"] / 1e3, 1) if G > 1 else 0.0,
+                            "frac_of_peer_copy_rate": round(back / res["gather_heads"] / 1e3 / link, 3) if G > 1 else None},
+           "link_rate_gbs": link,
+           "note": "one process per GPU, CUDA IPC peer buffers, plain peer stores / loads from this library's kernels; the only "
+                   "collective is the barrier between the two phases (untimed)"}
+    return rec
+
+
 def strong_record(env, w, K, splits):
     """Strong scaling of one workload inside this run: the whole workload on one GPU (every rank runs it,
     max over ranks), then each split of its rows over the ranks.  Times are ms per block, max over ranks."""
@@ -1010,6 +1081,15 @@ def main():
         if rank == 0:
             print(json.dumps({"impl": args.impl, "workload": w.name, "rows": rows, "steps": K, "tune": args.tune,
                               "per_op_isolated": job.per_op_isolated(K)}), flush=True)
+        return
+    if args.exchange_only:
+        job.close()
+        wl = W["h3video"] if args.workload == "qwen1024" else w   # the reference's sequence-parallel path is the video model's
+        rec = exchange_rows(env, wl, K)
+        if rank == 0:
+            print(json.dumps({"impl": args.impl, "steps": K, "head_exchange": rec}), flush=True)
+        if env.distributed:
+            env.dist.destroy_process_group()
         return
     if args.linear_only:
         job.close()

@@ -206,7 +206,16 @@ int mxk_peer_buffer_free(void* ptr);
  *   NULL.  N % 32 == 0, K % 8 == 0, every pointer 16-byte aligned.
  * mxk_linear_bf16:            y bf16 [M, N] = A W^T (+ bias)              = linear()
  * mxk_linear_gated_residual:  x fp32 [M, N] += act(gate) * (A W^T (+ bias)) = linear() + gated_residual()
+ * mxk_linear_qkv_norm_rope:   the QKV projection with head_norm_rope in its epilogue: W bf16
+ *   [n_tensors * H * 128, K] (the q | k | v rows of the packed projection, src/models/minimax_h3/dit.cpp:207-213;
+ *   three separate projections can be passed as one concatenated weight), bias fp32 [n_tensors * H * 128] or
+ *   NULL; tensors_host[i] gives tensor i's norm_w (NULL: none), rot, mode and out (bf16 [M, H, 128]); its in,
+ *   in_stride and col0 are ignored.  = linear() + head_norm_rope() per tensor, the [M, 3 H D] projection
+ *   output never written.  D must be 128 and H even; rot a multiple of 16 (interleaved) or 32 (half).
  * No counterpart as single calls in the reference (each replaces two or three of its calls). */
+int mxk_linear_qkv_norm_rope(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t K, int H, int D,
+                             const MxkHeadTensor* tensors_host, int n_tensors, float eps, const float* cos, const float* sin,
+                             mxk_stream_t stream);
 int mxk_linear_bf16(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, mxk_bf16* y,
                     mxk_stream_t stream);
 int mxk_linear_gated_residual(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, float* x,

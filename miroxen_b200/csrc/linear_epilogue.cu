@@ -43,7 +43,8 @@ constexpr int kStageA = BM * BK * 2, kStageB = BN * BK * 2;  // 16 KB + 32 KB
 constexpr int kAccCols = BN;                                  // fp32 columns of one accumulator
 constexpr int kTmemCols = 2 * kAccCols;                       // two accumulators: all 512 columns
 constexpr int kThreads = 192;
-constexpr int EPI_STORE = 0, EPI_RESIDUAL = 1;
+constexpr int EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV = 2;
+constexpr int kHeadDim = 128;  // EPI_QKV: a 256-column tile is exactly two heads
 
 struct LinearArgs {
   int64_t M, N, K;
@@ -52,6 +53,15 @@ struct LinearArgs {
   float* x;           // EPI_RESIDUAL: fp32 [M, N], updated in place
   MxkRowMod gate;     // EPI_RESIDUAL
   int gate_tanh;
+  // EPI_QKV: the N = n_tensors * H * 128 output columns are n_tensors projections of H heads each; head h of
+  // tensor i is normalised with norm_w[i] (null: no norm), rotated (rot[i], mode[i]) and stored to out[i] [M, H, 128]
+  int H;
+  const float* norm_w[3];
+  bf16* out[3];
+  int rot[3], mode[3];
+  float eps;
+  const float* cos;
+  const float* sin;
   int* err;
 };
 
@@ -59,7 +69,7 @@ struct __align__(1024) LinearSmem {
   unsigned char a[kStages][kStageA];
   unsigned char b[kStages][kStageB];
   float bias[BN];           // the tile's bias slice (0 when absent)
-  float gate[2][BN];        // act(gate) for prefix rows [0] and target rows [1] (1 when absent)
+  float gate[2][BN];        // act(gate) for prefix rows [0] and target rows [1] (1 when absent); EPI_QKV: [0][0..127] = norm weights
   unsigned long long full[kStages], empty[kStages], acc_full[2], acc_empty[2];
   unsigned tmem_base;
 };
@@ -109,6 +119,19 @@ __device__ __forceinline__ void tc_ld32(unsigned taddr, float (&v)[32]) {
       : "memory");
 #pragma unroll
   for (int i = 0; i < 32; i++) v[i] = __uint_as_float(r[i]);
+}
+
+__device__ __forceinline__ void tc_ld16(unsigned taddr, float (&v)[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n\t"
+      "tcgen05.wait::ld.sync.aligned;"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+        "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) wide under the
@@ -230,6 +253,10 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
           sm.gate[0][c] = gp, sm.gate[1][c] = gt;
         }
+        if (EPI == EPI_QKV && c < kHeadDim) {
+          const float* nw = a.norm_w[n0 / (a.H * kHeadDim)];
+          sm.gate[0][c] = nw ? nw[c] : 1.f;
+        }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
       // the four warps agree on the outcome of the wait, so that none is left alone at the next named barrier
@@ -243,6 +270,100 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool row_on = row < a.M;
       const float* g = sm.gate[(EPI == EPI_RESIDUAL && row < a.gate.prefix_len) ? 0 : 1];
       const unsigned taddr = tmem_base + (unsigned(quarter * 32) << 16) + unsigned(buf * kAccCols);
+      if constexpr (EPI == EPI_QKV) {
+        // The tile's 256 columns are heads h0 and h0 + 1 of one tensor; this thread holds one token's row of both.
+        // Per head: one pass over the accumulator for the sum of squares, a second one to normalise, rotate and
+        // store (re-reading tensor memory is cheaper than keeping 128 values in registers).  A value is what the
+        // separate calls would have read from memory: bf16(acc), then bf16(. + bias).
+        const int inner = a.H * kHeadDim;
+        const int ti = n0 / inner, h0 = (n0 - ti * inner) / kHeadDim;
+        const bool has_norm = a.norm_w[ti] != nullptr;
+        const int mode = a.mode[ti], rot = mode == MXK_ROPE_NONE ? 0 : a.rot[ti], half = rot >> 1;
+        const float* nw = sm.gate[0];
+        auto value = [&](float acc, int c) {  // c: column inside the tile
+          float v = __bfloat162float(__float2bfloat16(acc));
+          if (a.bias) v = __bfloat162float(__float2bfloat16(v + sm.bias[c]));
+          return v;
+        };
+        auto store16 = [&](bf16* dst, const float (&o)[16]) {
+          float lo[8], hi[8];
+#pragma unroll
+          for (int i = 0; i < 8; i++) lo[i] = o[i], hi[i] = o[8 + i];
+          reinterpret_cast<uint4*>(dst)[0] = pack8(lo);
+          reinterpret_cast<uint4*>(dst)[1] = pack8(hi);
+        };
+#pragma unroll 1
+        for (int hh = 0; hh < 2; hh++) {
+          const int cb = hh * kHeadDim;  // first column of the head inside the tile
+          float rstd = 1.f;
+          if (has_norm) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < kHeadDim; c += 16) {
+              float acc[16];
+              tc_ld16(taddr + unsigned(cb + c), acc);
+#pragma unroll
+              for (int i = 0; i < 16; i++) {
+                const float v = value(acc[i], cb + c + i);
+                ss = fmaf(v, v, ss);
+              }
+            }
+            rstd = rsqrtf(ss * (1.f / kHeadDim) + a.eps);
+          }
+          bf16* orow = row_on ? a.out[ti] + (row * a.H + h0 + hh) * kHeadDim : nullptr;
+          const float* cr = a.cos + row * half;
+          const float* sr = a.sin + row * half;
+          auto normed = [&](float (&v)[16], int c) {  // c: first column inside the head
+            float acc[16];
+            tc_ld16(taddr + unsigned(cb + c), acc);
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+              v[i] = value(acc[i], cb + c + i);
+              if (has_norm) v[i] = v[i] * rstd * nw[c + i];
+            }
+          };
+          if (mode == MXK_ROPE_HALF && rot > 0) {
+            // pairs (i, i + half): the 16-column chunk at c pairs with the one at half + c (half % 16 == 0)
+#pragma unroll 1
+            for (int c = 0; c < half; c += 16) {
+              float va[16], vb[16];
+              normed(va, c);
+              normed(vb, half + c);
+              if (row_on) {
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                  const float cs = cr[c + i], sn = sr[c + i], x0 = va[i], x1 = vb[i];
+                  va[i] = x0 * cs - x1 * sn;
+                  vb[i] = fmaf(x0, sn, x1 * cs);
+                }
+                store16(orow + c, va);
+                store16(orow + half + c, vb);
+              }
+            }
+          } else if (mode == MXK_ROPE_INTERLEAVED && rot > 0) {
+#pragma unroll 1
+            for (int c = 0; c < rot; c += 16) {  // pairs (2i, 2i + 1): eight of them per chunk (rot % 16 == 0)
+              float v[16];
+              normed(v, c);
+              if (row_on) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                  const float cs = cr[(c >> 1) + i], sn = sr[(c >> 1) + i], x0 = v[2 * i], x1 = v[2 * i + 1];
+                  v[2 * i] = x0 * cs - x1 * sn;
+                  v[2 * i + 1] = fmaf(x0, sn, x1 * cs);
+                }
+                store16(orow + c, v);
+              }
+            }
+          }
+#pragma unroll 1
+          for (int c = rot; c < kHeadDim; c += 16) {  // channels outside the rotation
+            float v[16];
+            normed(v, c);
+            if (row_on) store16(orow + c, v);
+          }
+        }
+      } else
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         float acc[32];
@@ -376,6 +497,35 @@ int mxk_linear_bf16(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int
   LinearArgs a{};
   a.M = M, a.N = N, a.K = K, a.bias = bias, a.y = reinterpret_cast<bf16*>(y);
   return run_linear<EPI_STORE>("linear_bf16", A, W, a, as_stream(stream));
+}
+
+int mxk_linear_qkv_norm_rope(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t K, int H, int D,
+                             const MxkHeadTensor* tensors_host, int n_tensors, float eps, const float* cos, const float* sin,
+                             mxk_stream_t stream) {
+  const char* name = "linear_qkv_norm_rope";
+  if (M <= 0 || n_tensors == 0) return MXK_OK;
+  if (!tensors_host || n_tensors < 0 || n_tensors > 3) return fail(MXK_ERR_INVALID_ARG, "%s: n_tensors=%d (1..3)", name, n_tensors);
+  if (D != kHeadDim || H <= 0 || (int64_t(H) * D) % BN != 0)
+    return fail(MXK_ERR_INVALID_ARG, "%s: needs D = 128 and an even head count (H=%d D=%d); otherwise call mxk_linear_bf16 and "
+                "mxk_qkv_norm_rope", name, H, D);
+  LinearArgs a{};
+  a.M = M, a.N = int64_t(n_tensors) * H * D, a.K = K, a.bias = bias, a.H = H, a.eps = eps, a.cos = cos, a.sin = sin;
+  for (int i = 0; i < n_tensors; i++) {
+    const MxkHeadTensor& t = tensors_host[i];
+    if (!t.out || !aligned(t.out, 16) || !aligned(t.norm_w, 16)) return fail(MXK_ERR_INVALID_ARG, "%s: tensor %d: null or unaligned out / norm_w", name, i);
+    if (t.mode != MXK_ROPE_NONE && t.mode != MXK_ROPE_INTERLEAVED && t.mode != MXK_ROPE_HALF)
+      return fail(MXK_ERR_INVALID_ARG, "%s: unknown rope mode %d", name, t.mode);
+    const bool rope = t.mode != MXK_ROPE_NONE && t.rot > 0;
+    if (rope && (t.rot > D || t.rot % (t.mode == MXK_ROPE_HALF ? 32 : 16) != 0))
+      return fail(MXK_ERR_INVALID_ARG, "%s: rot=%d must be a multiple of %d and <= D", name, t.rot, t.mode == MXK_ROPE_HALF ? 32 : 16);
+    if (rope && (!cos || !sin || !aligned(cos, 16) || !aligned(sin, 16)))
+      return fail(MXK_ERR_INVALID_ARG, "%s: rotary mode needs 16-byte aligned cos and sin tables", name);
+    a.norm_w[i] = t.norm_w, a.out[i] = reinterpret_cast<bf16*>(t.out), a.rot[i] = rope ? t.rot : 0, a.mode[i] = rope ? t.mode : MXK_ROPE_NONE;
+    // one table serves every rotating tensor of the call: they must agree on its row length
+    for (int j = 0; j < i; j++)
+      if (a.rot[j] && a.rot[i] && a.rot[j] != a.rot[i]) return fail(MXK_ERR_INVALID_ARG, "%s: tensors rotate %d and %d channels", name, a.rot[j], a.rot[i]);
+  }
+  return run_linear<EPI_QKV>(name, A, W, a, as_stream(stream));
 }
 
 int mxk_linear_gated_residual(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, float* x,

@@ -29,7 +29,7 @@ __all__ = [
     "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8", "gated_residual_norm_quant_mxfp8",
     "qwen_latent_encode", "qwen_latent_decode", "h3_latent_video", "h3_latent_audio",
     "bias_gelu_tanh_inplace", "bias_silu_mul", "gated_residual_bias",
-    "linear_bf16", "linear_gated_residual", "quantize_nvfp4_known_amax", "layernorm_mod_amax", "rmsnorm_mod_amax", "gated_residual_norm_amax", "act_amax",
+    "linear_bf16", "linear_gated_residual", "linear_qkv_norm_rope", "quantize_nvfp4_known_amax", "layernorm_mod_amax", "rmsnorm_mod_amax", "gated_residual_norm_amax", "act_amax",
     "norm_path_probe", "NORM_PATH_GENERIC", "NORM_PATH_VECTOR", "NORM_PATH_BULK",
 ]
 
@@ -309,6 +309,12 @@ def linear_bf16(A, W, bias, M, N, K, y, stream=None):
 def linear_gated_residual(A, W, bias, M, N, K, x, gate: RowMod, gate_tanh, stream=None):
     """x fp32 [M, N] += act(gate) * bf16(A @ W^T (+ bias)): linear() and gated_residual() in one kernel."""
     check(lib().mxk_linear_gated_residual(_p(A), _p(W), _p(bias), M, N, K, _p(x), gate or _NONE, int(gate_tanh), _stream(stream)))
+
+
+def linear_qkv_norm_rope(A, W, bias, M, K, H, D, tensors: Sequence[HeadSpec], eps, cos, sin, stream=None):
+    """The QKV projection with per-head RMSNorm + rotary embedding in its epilogue (specs: norm_w, out, rot, mode)."""
+    arr = (HeadTensor * len(tensors))(*[HeadTensor(None, 0, 0, _p(t.norm_w), _p(t.out), t.rot, t.mode) for t in tensors])
+    check(lib().mxk_linear_qkv_norm_rope(_p(A), _p(W), _p(bias), M, K, H, D, arr, len(tensors), eps, _p(cos), _p(sin), _stream(stream)))
 
 
 def _qmat_for(x, rows, dim, out):

@@ -99,6 +99,44 @@ def test_linear_gated_residual_equals_the_separate_calls(mx, M, N, K, mode):
     assert float((x.t != x_ref).float().mean()) < 0.02
 
 
+@pytest.mark.parametrize("M,Hh,K,rot,mode,n_t,with_bias", [(300, 24, 3072, 128, 1, 2, True), (1000, 40, 1024, 128, 2, 3, False),
+                                                          (130, 56, 512, 96, 2, 3, True), (5, 2, 64, 64, 1, 1, False)])
+def test_linear_qkv_norm_rope_equals_the_separate_calls(mx, M, Hh, K, rot, mode, n_t, with_bias):
+    """QKV projection + head_norm_rope in one kernel against the library GEMM + add_bias_bf16 + mxk_qkv_norm_rope.
+    A bf16 product that the two GEMMs round a unit apart moves its whole head by a relative 2^-7 / sqrt(128) at most
+    and its own element by one unit, so the outputs are compared at two bf16 units."""
+    D, inner = 128, Hh * 128
+    N = n_t * inner
+    A, W, bias = operands(M, N, K, M + Hh + K)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(21)
+    nq = 1 + 0.05 * torch.randn(D, generator=g, device="cuda")
+    nk = 1 + 0.05 * torch.randn(D, generator=g, device="cuda")
+    ang = torch.rand((M, rot // 2), generator=g, device="cuda") * 6.2 - 3.1
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    norms, rots, modes = [nq, nk, None][:n_t], [rot, rot, 0][:n_t], [mode, mode, 0][:n_t]
+    b = bias if with_bias else None
+    # the calls it replaces
+    y = A @ W.T
+    if b is not None:
+        mx.add_bias_bf16(y, b, M, N)
+    ref = [torch.empty((M, Hh, D), dtype=torch.bfloat16, device="cuda") for _ in range(n_t)]
+    mx.qkv_norm_rope([mx.HeadSpec(y, N, i * inner, norms[i], ref[i], rots[i], modes[i]) for i in range(n_t)], M, Hh, D, 1e-6, cos, sin)
+    outs = [H.Guarded(torch, (M, Hh, D), torch.bfloat16) for _ in range(n_t)]
+    mx.linear_qkv_norm_rope(A, W, b, M, K, Hh, D, [mx.HeadSpec(None, 0, 0, norms[i], outs[i].t, rots[i], modes[i]) for i in range(n_t)],
+                            1e-6, cos, sin)
+    torch.cuda.synchronize()
+    for i in range(n_t):
+        outs[i].check(f"tensor {i}")
+        got, want = outs[i].t.float(), ref[i].float()
+        err = (got - want).abs()
+        # rotation mixes two channels: bound by the larger of the pair, approximated by the head's largest magnitude
+        scale = torch.clamp(want.abs().amax(dim=-1, keepdim=True), min=H.BF16_FLOOR)
+        tol = 2.0 ** -6 * torch.maximum(want.abs(), 0.25 * scale)
+        assert bool((err <= tol).all()), f"tensor {i}: {int((err > tol).sum())} of {err.numel()} beyond tolerance, worst {float((err - tol).max()):.3e}"
+        assert float((outs[i].t != ref[i]).float().mean()) < 0.05, f"tensor {i}: too many elements differ"
+
+
 def test_linear_argument_checks(mx):
     L = mx.lib()
     from miroxen_b200._lib import RowMod
@@ -108,3 +146,7 @@ def test_linear_argument_checks(mx):
     assert L.mxk_linear_bf16(258, 256, None, 4, 64, 64, 256, None) == -1      # alignment
     assert L.mxk_linear_bf16(None, None, None, 0, 64, 64, None, None) == 0    # no rows
     assert L.mxk_linear_gated_residual(256, 256, None, 4, 64, 64, None, none, 0, None) == -1
+    from miroxen_b200.ops import HeadTensor
+    arr = (HeadTensor * 1)(HeadTensor(None, 0, 0, None, 256, 0, 0))
+    assert L.mxk_linear_qkv_norm_rope(256, 256, None, 4, 64, 3, 128, arr, 1, 1e-6, None, None, None) == -1   # odd head count
+    assert L.mxk_linear_qkv_norm_rope(256, 256, None, 4, 64, 2, 64, arr, 1, 1e-6, None, None, None) == -1    # D != 128
