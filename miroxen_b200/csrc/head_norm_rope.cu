@@ -233,11 +233,11 @@ struct LaneRole {
 template <int LPH, bool NORM, int MODE, int PASSES>
 __device__ __forceinline__ void rope_tokens(const unsigned char* src, int tok_bytes, const float* cr, const float* sr,
                                             int half, int ntok, unsigned char* dst, int out_tok_bytes,
-                                            const float* wsm_row, float inv_d, float eps, int passes, int heads_per_pass,
+                                            const float* w_row, float inv_d, float eps, int passes, int heads_per_pass,
                                             int H, const LaneRole& r) {
   float w[8];
   if (NORM) {
-    const float4 w0 = *reinterpret_cast<const float4*>(wsm_row), w1 = *reinterpret_cast<const float4*>(wsm_row + 4);
+    const float4 w0 = *reinterpret_cast<const float4*>(w_row), w1 = *reinterpret_cast<const float4*>(w_row + 4);
     w[0] = w0.x, w[1] = w0.y, w[2] = w0.z, w[3] = w0.w, w[4] = w1.x, w[5] = w1.y, w[6] = w1.z, w[7] = w1.w;
   }
   for (int tk = 0; tk < ntok; tk++) {
@@ -318,13 +318,13 @@ struct WideRole {
 
 template <int LPH, bool NORM, int MODE, int PASSES>
 __device__ __forceinline__ void rope_tokens_wide(const unsigned char* src, int tok_bytes, const float* cos_row, const float* sin_row,
-                                                 int half, int ntok, unsigned char* dst, int out_tok_bytes, const float* wsm_a,
-                                                 const float* wsm_b, int chunk_b_off, float inv_d, float eps, int passes,
+                                                 int half, int ntok, unsigned char* dst, int out_tok_bytes, const float* w_a,
+                                                 const float* w_b, int chunk_b_off, float inv_d, float eps, int passes,
                                                  int heads_per_pass, int H, const WideRole& r) {
   float wa[8], wb[8];
   if (NORM) {
-    const float4 a0 = *reinterpret_cast<const float4*>(wsm_a), a1 = *reinterpret_cast<const float4*>(wsm_a + 4);
-    const float4 b0 = *reinterpret_cast<const float4*>(wsm_b), b1 = *reinterpret_cast<const float4*>(wsm_b + 4);
+    const float4 a0 = *reinterpret_cast<const float4*>(w_a), a1 = *reinterpret_cast<const float4*>(w_a + 4);
+    const float4 b0 = *reinterpret_cast<const float4*>(w_b), b1 = *reinterpret_cast<const float4*>(w_b + 4);
     wa[0] = a0.x, wa[1] = a0.y, wa[2] = a0.z, wa[3] = a0.w, wa[4] = a1.x, wa[5] = a1.y, wa[6] = a1.z, wa[7] = a1.w;
     wb[0] = b0.x, wb[1] = b0.y, wb[2] = b0.z, wb[3] = b0.w, wb[4] = b1.x, wb[5] = b1.y, wb[6] = b1.z, wb[7] = b1.w;
   }
@@ -472,7 +472,6 @@ template <int LPH, int PASSES = 0, bool WIDE = false, int MINB = 0>
 __global__ void __launch_bounds__(!WIDE ? 544 : MINB == 1 ? 128 : 160, MINB == 0 ? 1 : 4) head_rope_pipe_kernel(const RopeArgs a) {
   extern __shared__ __align__(128) unsigned char dyn[];
   __shared__ __align__(8) unsigned long long full[8], empty[8];
-  __shared__ __align__(16) float wsm[kMaxTensors][256];  // the tensors' norm weights
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int n_cons_warps = (blockDim.x >> 5) - 1;
   const int half = a.rot >> 1;
@@ -494,12 +493,11 @@ __global__ void __launch_bounds__(!WIDE ? 544 : MINB == 1 ? 128 : 160, MINB == 0
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   pdl_launch_dependents();
-  pdl_wait();  // nothing above touches global memory
-  for (int i = tid; i < a.n_tensors * a.D; i += blockDim.x) {
-    const int ti = i / a.D, d = i - ti * a.D;
-    wsm[ti][d] = a.t[ti].norm_w ? a.t[ti].norm_w[d] : 1.f;
-  }
-  __syncthreads();
+  __syncthreads();  // the barriers exist for every warp; still nothing has touched global memory
+  pdl_wait();
+  // No staging step between the dependency wait and the first copies: the producer issues at once, and the
+  // consumers fetch their 8 (16) norm weights straight from global memory (L1 / L2 hits after the first stage)
+  // while those copies are in flight.
 
   bool ok = true;
   int issued = 0;  // producer: groups whose copies were issued
@@ -542,8 +540,8 @@ __global__ void __launch_bounds__(!WIDE ? 544 : MINB == 1 ? 128 : 160, MINB == 0
         const unsigned char* src = stage + sg.smem_off + a.t_off[ti] + r.thread_off;
         unsigned char* dst = reinterpret_cast<unsigned char*>(t.out) + s0 * tok_out_bytes + r.thread_off;
         const bool t_rope = t.mode != MXK_ROPE_NONE && t.rot > 0;
-        const float* wa = &wsm[ti][8 * l];
-        const float* wb = &wsm[ti][a.D / 2 + 8 * l];
+        const float* wa = t.norm_w ? t.norm_w + 8 * l : nullptr;
+        const float* wb = t.norm_w ? t.norm_w + a.D / 2 + 8 * l : nullptr;
 #define MXK_ROPE_CALL(NORM, MODE)                                                                                      \
   rope_tokens_wide<LPH, NORM, MODE, PASSES>(src, sg.token_bytes, cr, sr, half, ntok, dst, tok_out_bytes, wa, wb, chunk_b_off, \
                                             inv_d, a.eps, a.passes, a.heads_per_pass, a.H, r)
@@ -604,7 +602,7 @@ __global__ void __launch_bounds__(!WIDE ? 544 : MINB == 1 ? 128 : 160, MINB == 0
           const unsigned char* src = stage + sg.smem_off + a.t_off[ti] + r.thread_off;
           unsigned char* dst = reinterpret_cast<unsigned char*>(t.out) + s0 * tok_out_bytes + r.thread_off;
           const bool t_rope = t.mode != MXK_ROPE_NONE && t.rot > 0;
-          const float* wr = &wsm[ti][8 * l];
+          const float* wr = t.norm_w ? t.norm_w + 8 * l : nullptr;
 #define MXK_ROPE_CALL(NORM, MODE)                                                                          \
   rope_tokens<LPH, NORM, MODE, PASSES>(src, sg.token_bytes, cr, sr, half, ntok, dst, tok_out_bytes, wr, inv_d, a.eps, \
                                a.passes, a.heads_per_pass, a.H, r)
