@@ -707,6 +707,40 @@ def quant_rows(env, job, K, impl):
     res["norm_mod_quant_mxfp8"] = {"norm": "layernorm" if w.norm_mode == 0 else "rmsnorm", "input": f"[{rows}, {w.dim}]",
                                    "us": one, "us_two_calls": two, "bytes": int(by), "gbs": round(by / one / 1e3, 1),
                                    "frac": round(by / one / 1e3 / peak_gbs, 3)}
+    # NVFP4 in one pass: the producing op leaves the tensor maximum behind, the quantiser skips its first read pass
+    amax = [torch.zeros(1, dtype=torch.float32, device="cuda") for _ in sets]
+    fouts = [mx.ops.QMat(torch.empty(mx.ops.qdata_bytes(2, rows, w.dim), dtype=torch.uint8, device="cuda"),
+                         torch.empty(mx.ops.qscale_bytes(2, rows, w.dim), dtype=torch.uint8, device="cuda"), amax[i]) for i in range(n_sets)]
+
+    def norm_amax(i):
+        b = sets[i % n_sets]
+        if w.norm_mode == 0:
+            mx.ops.layernorm_mod_amax(b.x, rows, w.dim, 1e-6, mod(b, "scale1"), mod(b, "shift1"), b.h1, amax[i % n_sets], stream)
+        else:
+            mx.ops.rmsnorm_mod_amax(b.x, rows, w.dim, 1e-6, b.mods["norm1_w"], mod(b, "scale1"), mod(b, "shift1"), b.h1, amax[i % n_sets], stream)
+
+    def norm_plain(i):
+        b = sets[i % n_sets]
+        if w.norm_mode == 0:
+            mx.ops.layernorm_mod(b.x, rows, w.dim, 1e-6, mod(b, "scale1"), mod(b, "shift1"), b.h1, stream)
+        else:
+            mx.ops.rmsnorm_mod(b.x, rows, w.dim, 1e-6, b.mods["norm1_w"], mod(b, "scale1"), mod(b, "shift1"), b.h1, stream)
+
+    def fp4_one(i):
+        norm_amax(i)
+        mx.ops.quantize_nvfp4_known_amax(sets[i % n_sets].h1, w.dim, rows, w.dim, amax[i % n_sets], fouts[i % n_sets], stream)
+
+    def fp4_two(i):
+        norm_plain(i)
+        mx.ops.quantize_blockscaled(mx.ops.Q_NVFP4, sets[i % n_sets].h1, w.dim, rows, w.dim, fouts[i % n_sets], stream)
+
+    one, two = pair_us(fp4_one, fp4_two)
+    na, npl = pair_us(norm_amax, norm_plain)
+    res["norm_then_nvfp4"] = {"norm": "layernorm" if w.norm_mode == 0 else "rmsnorm", "input": f"[{rows}, {w.dim}]",
+                              "us_norm_amax_then_one_pass_quantiser": one, "us_norm_then_two_pass_quantiser": two,
+                              "us_norm_with_amax": na, "us_norm": npl,
+                              "note": "same bytes out; the tensor maximum is a by-product of the norm instead of a read pass of the quantiser"}
+    del fouts
     # bias add folded into the op that reads the GEMM output next, against add_bias_bf16 + the plain op
     bias_f = torch.randn(2 * w.F, device="cuda") * 0.1
     bias_d = torch.randn(w.dim, device="cuda") * 0.1

@@ -26,20 +26,25 @@
 //                      updates x with 128-bit accesses; the other accumulator is being filled meanwhile.
 // Every mbarrier wait is bounded (bulk_copy.cuh); on a timeout the role records kErrBulkTimeout in the
 // device error word and leaves its loop, the CTA still meets at the final barrier and frees its TMEM.
-// No cluster launch and no multi-CTA copies: the file may travel to multi-GPU runs.
+// Every copy lands in the shared memory of the CTA that issued it (no copy is broadcast to several CTAs), so the
+// file may travel to multi-GPU runs.
 #include <cuda.h>
 
 #include <atomic>
 
 #include "bulk_copy.cuh"
 #include "common.cuh"
+#include "tuning.h"
 
 namespace mxk {
 namespace {
 
 constexpr int BM = 128, BN = 256, BK = 64, UMMA_K = 16;
-constexpr int kStages = 4;
-constexpr int kStageA = BM * BK * 2, kStageB = BN * BK * 2;  // 16 KB + 32 KB
+constexpr int kStageA = BM * BK * 2;  // 16 KB: this CTA's 128 rows of A
+// CTAS = 1: the CTA holds the whole 256-row W tile (32 KB), 4 stages.  CTAS = 2 (a pair of CTAs in a cluster working
+// on a 256 x 256 tile, tcgen05 cta_group::2): each CTA holds its 128 rows of A and HALF of the W tile (16 KB), 6 stages.
+template <int CTAS> constexpr int kStageB = BN / CTAS * BK * 2;
+template <int CTAS> constexpr int kStages = CTAS == 1 ? 4 : 6;
 constexpr int kAccCols = BN;                                  // fp32 columns of one accumulator
 constexpr int kTmemCols = 2 * kAccCols;                       // two accumulators: all 512 columns
 constexpr int kThreads = 192;
@@ -65,12 +70,13 @@ struct LinearArgs {
   int* err;
 };
 
+template <int CTAS>
 struct __align__(1024) LinearSmem {
-  unsigned char a[kStages][kStageA];
-  unsigned char b[kStages][kStageB];
+  unsigned char a[kStages<CTAS>][kStageA];
+  unsigned char b[kStages<CTAS>][kStageB<CTAS>];
   float bias[BN];           // the tile's bias slice (0 when absent)
   float gate[2][BN];        // act(gate) for prefix rows [0] and target rows [1] (1 when absent); EPI_QKV: [0][0..127] = norm weights
-  unsigned long long full[kStages], empty[kStages], acc_full[2], acc_empty[2];
+  unsigned long long full[kStages<CTAS>], empty[kStages<CTAS>], acc_full[2], acc_empty[2], done;
   unsigned tmem_base;
 };
 
@@ -82,6 +88,48 @@ __device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map
 __device__ __forceinline__ void mbar_arrive_local(unsigned bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// ---- helpers of the two-CTA form -----------------------------------------------------------------------
+__device__ __forceinline__ unsigned cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address, in the cluster's shared window, of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ unsigned map_to_cta(unsigned addr, unsigned rank) {
+  unsigned r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// A pair's copy: lands in this CTA's shared memory, counts on a barrier of either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const CUtensorMap* map, int c0, int c1, unsigned bar_cluster) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(map), "r"(bar_cluster), "r"(c0), "r"(c1)
+      : "memory");
+}
+// Arrives, once the MMAs issued so far have retired, on the barrier at this shared-memory offset in BOTH CTAs of the
+// pair (the commit's own multicast form; it signals barriers and moves no data).
+__device__ __forceinline__ void tc_commit_pair(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+               "h"(static_cast<unsigned short>(3))
+               : "memory");
+}
+// D[tmem of both CTAs] (+)= A[256 rows: 128 per CTA] * B[256 columns: 128 per CTA], issued by the pair's first CTA
+__device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // AND of a predicate over the 128 epilogue threads (named barrier 1).
 __device__ __forceinline__ bool epilogue_all(bool v) {
   unsigned r;
@@ -144,32 +192,52 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(unsigned addr) {
 }
 // Instruction descriptor of kind::f16: fp32 accumulator (bits [4, 6) = 1), A and B bf16 ([7, 10) = [10, 13) = 1),
 // both K-major (bits 15, 16 = 0), N >> 3 in [17, 23), M >> 4 in [24, 29).
-constexpr unsigned kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (unsigned(BN >> 3) << 17) | (unsigned(BM >> 4) << 24);
+template <int CTAS>
+constexpr unsigned kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (unsigned(BN >> 3) << 17) | (unsigned(BM * CTAS >> 4) << 24);
 
-template <int EPI>
+// CTAS = 2: launched as clusters of two CTAs along M.  The pair works on a 256 x 256 tile; CTA r of the pair owns rows
+// [128 r, 128 r + 128) (its own TMEM lanes, its own epilogue) and loads those rows of A plus rows [128 r, 128 r + 128)
+// of the W tile.  The first CTA's MMA thread issues cta_group::2 MMAs that read both CTAs' shared memory and write both
+// CTAs' tensor memory.  Barriers: `full` lives in the first CTA and counts the bytes of both CTAs' copies; `empty` and
+// `acc_full` exist in both CTAs and are signalled in both by the issuing thread's commits; `acc_empty`
+// lives in the first CTA and collects the eight epilogue warps of the pair; `done` is the hand-shake before the
+// tensor memory is freed and a CTA leaves (nobody may still signal into a CTA that has exited).
+template <int EPI, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
     linear_epilogue_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const LinearArgs a) {
   extern __shared__ unsigned char smem_raw[];
-  // dynamic shared memory is 16-byte aligned by contract; the tiles need 1024
-  LinearSmem& sm = *reinterpret_cast<LinearSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // dynamic shared memory is 16-byte aligned by contract; the tiles need 1024 (the same offset in both CTAs of a pair)
+  using Smem = LinearSmem<CTAS>;
+  Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr int kSt = kStages<CTAS>;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int tiles_n = int((a.N + BN - 1) / BN), tiles_m = int((a.M + BM - 1) / BM);
+  const unsigned rank = CTAS == 2 ? cluster_rank() : 0u;
+  const int tiles_n = int((a.N + BN - 1) / BN), tiles_m = int((a.M + BM * CTAS - 1) / (BM * CTAS));
   const int n_tiles = tiles_m * tiles_n;
   const int k_blocks = int((a.K + BK - 1) / BK);
+  const int tile0 = int(blockIdx.x) / CTAS, tile_step = int(gridDim.x) / CTAS;
 
   if (tid == 0) {
-    for (int i = 0; i < kStages; i++) mbar_init(smem_u32(&sm.full[i]), 1), mbar_init(smem_u32(&sm.empty[i]), 1);
-    for (int i = 0; i < 2; i++) mbar_init(smem_u32(&sm.acc_full[i]), 1), mbar_init(smem_u32(&sm.acc_empty[i]), 4);
+    for (int i = 0; i < kSt; i++) mbar_init(smem_u32(&sm.full[i]), 1), mbar_init(smem_u32(&sm.empty[i]), 1);
+    for (int i = 0; i < 2; i++) mbar_init(smem_u32(&sm.acc_full[i]), 1), mbar_init(smem_u32(&sm.acc_empty[i]), 4 * CTAS);
+    mbar_init(smem_u32(&sm.done), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) {  // one warp allocates (and later frees) the tensor memory
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols)
-                 : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  if (warp == 1) {  // one warp (the same one in both CTAs of a pair) allocates and later frees the tensor memory
+    if (CTAS == 1) {
+      asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    } else {
+      asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)), "r"(kTmemCols)
+                   : "memory");
+      asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
   }
   pdl_launch_dependents();
   tc_fence_before();
   __syncthreads();
+  if (CTAS == 2) cluster_sync_all();  // both CTAs' barriers exist before either signals into the other
   tc_fence_after();
   const unsigned tmem_base = sm.tmem_base;
   pdl_wait();  // nothing above touches global memory
@@ -181,28 +249,36 @@ __global__ void __launch_bounds__(kThreads, 1)
       // ---- TMA producer ----
       int st = 0;
       unsigned ph = 0;
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+      for (int t = tile0; t < n_tiles && ok; t += tile_step) {
+        const int m0 = (t / tiles_n) * BM * CTAS + int(rank) * BM, n0 = (t % tiles_n) * BN + int(rank) * (BN / CTAS);
         for (int kb = 0; kb < k_blocks; kb++, issued++) {
-          if (issued >= kStages && !mbar_wait(smem_u32(&sm.empty[st]), ph ^ 1u)) {
+          if (issued >= kSt && !mbar_wait(smem_u32(&sm.empty[st]), ph ^ 1u)) {
             ok = false;
             break;
           }
-          const unsigned bar = smem_u32(&sm.full[st]);
-          mbar_expect_tx(bar, kStageA + kStageB);
-          tma_load_2d(smem_u32(sm.a[st]), &map_a, kb * BK, m0, bar);
-          tma_load_2d(smem_u32(sm.b[st]), &map_w, kb * BK, n0, bar);
-          if (++st == kStages) st = 0, ph ^= 1u;
+          if (CTAS == 1) {
+            const unsigned bar = smem_u32(&sm.full[st]);
+            mbar_expect_tx(bar, kStageA + kStageB<1>);
+            tma_load_2d(smem_u32(sm.a[st]), &map_a, kb * BK, m0, bar);
+            tma_load_2d(smem_u32(sm.b[st]), &map_w, kb * BK, n0, bar);
+          } else {
+            // the pair's `full` barrier is the first CTA's: it expects both CTAs' bytes, both CTAs' copies count on it
+            if (rank == 0) mbar_expect_tx(smem_u32(&sm.full[st]), 2 * (kStageA + kStageB<2>));
+            const unsigned bar = map_to_cta(smem_u32(&sm.full[st]), 0);
+            tma_load_2d_pair(smem_u32(sm.a[st]), &map_a, kb * BK, m0, bar);
+            tma_load_2d_pair(smem_u32(sm.b[st]), &map_w, kb * BK, n0, bar);
+          }
+          if (++st == kSt) st = 0, ph ^= 1u;
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      // ---- MMA issuer ----
+    if (lane == 0 && rank == 0) {
+      // ---- MMA issuer (the pair's first CTA only) ----
       int st = 0;
       unsigned ph = 0;
       int local = 0;
-      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, local++) {
+      for (int t = tile0; t < n_tiles && ok; t += tile_step, local++) {
         const int buf = local & 1;
         // the epilogue must have drained this accumulator (its previous use was two tiles ago)
         if (local >= 2 && !mbar_wait(smem_u32(&sm.acc_empty[buf]), unsigned(((local >> 1) - 1) & 1))) {
@@ -219,13 +295,25 @@ __global__ void __launch_bounds__(kThreads, 1)
           tc_fence_after();
           const uint64_t da = smem_desc_sw128(smem_u32(sm.a[st])), db = smem_desc_sw128(smem_u32(sm.b[st]));
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; k++)  // 32 bytes further along K per step: +2 in the (address >> 4) field
-            tc_mma(tmem_d, da + uint64_t(2 * k), db + uint64_t(2 * k), kInstrDesc, (kb | k) != 0 ? 1u : 0u);
-          tc_commit(smem_u32(&sm.empty[st]));  // the stage is free once these MMAs have read it
-          if (++st == kStages) st = 0, ph ^= 1u;
+          for (int k = 0; k < BK / UMMA_K; k++) {  // 32 bytes further along K per step: +2 in the (address >> 4) field
+            if (CTAS == 1) tc_mma(tmem_d, da + uint64_t(2 * k), db + uint64_t(2 * k), kInstrDesc<1>, (kb | k) != 0 ? 1u : 0u);
+            else tc_mma_pair(tmem_d, da + uint64_t(2 * k), db + uint64_t(2 * k), kInstrDesc<2>, (kb | k) != 0 ? 1u : 0u);
+          }
+          // the stage is free once these MMAs have read it (in both CTAs of a pair)
+          if (CTAS == 1) {
+            tc_commit(smem_u32(&sm.empty[st]));
+          } else {
+            tc_commit_pair(smem_u32(&sm.empty[st]));
+          }
+          if (++st == kSt) st = 0, ph ^= 1u;
         }
         if (!ok) break;
-        tc_commit(smem_u32(&sm.acc_full[buf]));  // the accumulator is complete once every MMA so far has retired
+        // the accumulator is complete once every MMA so far has retired
+        if (CTAS == 1) {
+          tc_commit(smem_u32(&sm.acc_full[buf]));
+        } else {
+          tc_commit_pair(smem_u32(&sm.acc_full[buf]));
+        }
       }
     }
   } else {
@@ -234,9 +322,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int row_in_tile = quarter * 32 + lane;
     const int et = tid - 64;  // 0..127
     int local = 0;
-    for (int t = blockIdx.x; t < n_tiles; t += gridDim.x, local++) {
+    for (int t = tile0; t < n_tiles; t += tile_step, local++) {
       const int buf = local & 1;
-      const int m0 = (t / tiles_n) * BM, n0 = (t % tiles_n) * BN;
+      const int m0 = (t / tiles_n) * BM * CTAS + int(rank) * BM, n0 = (t % tiles_n) * BN;
       // stage this tile's bias and act(gate) slices; the barrier (id 1, the four epilogue warps) also
       // separates them from the previous tile's readers
       asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -259,6 +347,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
       }
       asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (EPI == EPI_RESIDUAL) {
+        // While the tile's main loop is still running: pull this thread's row of x (1 KB) towards L2, so that the
+        // epilogue's loads, eight dependent round trips per tile otherwise, find it there.
+        const int64_t prow = int64_t(m0) + row_in_tile;
+        if (prow < a.M) {
+          const char* xr = reinterpret_cast<const char*>(a.x + prow * a.N + n0);
+          for (int j = 0; j < BN * 4 / 128; j++)
+            if (n0 + 32 * j < a.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(xr + 128 * j));
+        }
+      }
       // the four warps agree on the outcome of the wait, so that none is left alone at the next named barrier
       const bool landed = mbar_wait(smem_u32(&sm.acc_full[buf]), unsigned((local >> 1) & 1));
       if (!epilogue_all(landed)) {
@@ -401,10 +499,13 @@ __global__ void __launch_bounds__(kThreads, 1)
           }
         }
       }
-      // this warp is done reading the accumulator
+      // this warp is done reading the accumulator (the pair's `acc_empty` is the first CTA's)
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_local(smem_u32(&sm.acc_empty[buf]));
+      if (lane == 0) {
+        if (CTAS == 1) mbar_arrive_local(smem_u32(&sm.acc_empty[buf]));
+        else mbar_arrive_cluster(map_to_cta(smem_u32(&sm.acc_empty[buf]), 0));
+      }
     }
   }
 
@@ -413,14 +514,24 @@ __global__ void __launch_bounds__(kThreads, 1)
   // Every role's waits are bounded, so all threads arrive here.  After a failure the producer gives the
   // copies of its last kStages fills a bounded chance to land before the CTA (and its shared memory) goes.
   const bool any_failed = __syncthreads_or(!ok) != 0;
-  if (any_failed && tid == 0) {
-    for (long it = issued > kStages ? issued - kStages : 0; it < issued; it++)
-      mbar_wait(smem_u32(&sm.full[it % kStages]), unsigned((it / kStages) & 1));
+  if (any_failed && tid == 0 && (CTAS == 1 || rank == 0)) {
+    for (long it = issued > kSt ? issued - kSt : 0; it < issued; it++)
+      mbar_wait(smem_u32(&sm.full[it % kSt]), unsigned((it / kSt) & 1));
   }
   if (any_failed) __syncthreads();
+  if (CTAS == 2) {
+    // Hand-shake of the pair: each CTA tells the other that it will signal into it no more (its epilogue and its
+    // copies are done) and waits, bounded, for the same word from the other before it frees and leaves.
+    if (tid == 0) {
+      mbar_arrive_cluster(map_to_cta(smem_u32(&sm.done), rank ^ 1u));
+      if (!mbar_wait(smem_u32(&sm.done), 0) && a.err) atomicExch(a.err, kErrBulkTimeout);
+    }
+    __syncthreads();
+  }
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    if (CTAS == 1) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    else asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
   }
 }
 
@@ -458,6 +569,9 @@ int make_map(const char* name, CUtensorMap* map, const void* base, int64_t rows,
   return MXK_OK;
 }
 
+template <int EPI, int CTAS>
+int launch_linear(const char* name, const mxk_bf16* A, const mxk_bf16* W, const LinearArgs& a, cudaStream_t s);
+
 template <int EPI>
 int run_linear(const char* name, const mxk_bf16* A, const mxk_bf16* W, LinearArgs a, cudaStream_t s) {
   if (a.M <= 0) return MXK_OK;
@@ -470,17 +584,41 @@ int run_linear(const char* name, const mxk_bf16* A, const mxk_bf16* W, LinearArg
     return fail(MXK_ERR_INVALID_ARG, "%s: every pointer must be 16-byte aligned", name);
   if (a.gate.target && !a.gate.prefix && a.gate.prefix_len > 0)
     return fail(MXK_ERR_INVALID_ARG, "%s: prefix_len > 0 with a null prefix vector", name);
+  a.err = device_error_word();
+  // Two CTAs per tile (a cluster of two, half of the W tile each) when there is more than one 256-row tile; the
+  // single-CTA form otherwise and on request (`linear_ctas = 1`).
+  const bool pair = tune(TUNE_LINEAR_CTAS, 2) == 2 && a.M > BM;
+  return pair ? launch_linear<EPI, 2>(name, A, W, a, s) : launch_linear<EPI, 1>(name, A, W, a, s);
+}
+
+template <int EPI, int CTAS>
+int launch_linear(const char* name, const mxk_bf16* A, const mxk_bf16* W, const LinearArgs& a, cudaStream_t s) {
   CUtensorMap map_a, map_w;
   if (int rc = make_map(name, &map_a, A, a.M, a.K, BM)) return rc;
-  if (int rc = make_map(name, &map_w, W, a.N, a.K, BN)) return rc;
-  auto k = linear_epilogue_kernel<EPI>;
-  const size_t smem = sizeof(LinearSmem) + 1024;
+  if (int rc = make_map(name, &map_w, W, a.N, a.K, BN / CTAS)) return rc;
+  auto k = linear_epilogue_kernel<EPI, CTAS>;
+  const size_t smem = sizeof(LinearSmem<CTAS>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "%s: cudaFuncSetAttribute: %s", name, cudaGetErrorString(e));
-  const int64_t tiles = ceil_div(a.M, BM) * ceil_div(a.N, BN);
-  const int64_t grid = tiles < sm_count() ? tiles : sm_count();
-  a.err = device_error_word();
-  launch_pdl(k, dim3(unsigned(grid)), dim3(kThreads), smem, s, map_a, map_w, a);
+  const int64_t tiles = ceil_div(a.M, BM * CTAS) * ceil_div(a.N, BN);
+  int64_t units = sm_count() / CTAS;  // CTAs, or pairs of CTAs
+  if (units > tiles) units = tiles;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3(unsigned(units * CTAS)), cfg.blockDim = dim3(kThreads), cfg.dynamicSmemBytes = smem, cfg.stream = s;
+  cudaLaunchAttribute at[2];
+  int n_at = 0;
+  if (pdl_enabled()) {
+    at[n_at].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[n_at].val.programmaticStreamSerializationAllowed = 1;
+    n_at++;
+  }
+  if (CTAS == 2) {
+    at[n_at].id = cudaLaunchAttributeClusterDimension;
+    at[n_at].val.clusterDim.x = 2, at[n_at].val.clusterDim.y = 1, at[n_at].val.clusterDim.z = 1;
+    n_at++;
+  }
+  cfg.attrs = at, cfg.numAttrs = unsigned(n_at);
+  cudaLaunchKernelEx(&cfg, k, map_a, map_w, a);  // errors surface through cudaGetLastError() in after_launch()
   return after_launch(name);
 }
 

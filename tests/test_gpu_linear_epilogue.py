@@ -13,14 +13,18 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module")
-def mx():
+@pytest.fixture(scope="module", params=["cta_pair", "single_cta"])
+def mx(request):
+    """Every test runs with the two-CTA form (a cluster of two CTAs per 256 x 256 tile, the default for M > 128) and
+    with the single-CTA form (128 x 256 tiles)."""
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     import miroxen_b200 as m
     m.lib()
+    m.set_tuning("linear_ctas", 2 if request.param == "cta_pair" else 1)
     yield m
     torch.cuda.synchronize()
+    m.set_tuning("linear_ctas", 0)
     assert m.device_error() == 0, "a bounded wait of the GEMM ran out"
 
 
