@@ -973,7 +973,49 @@ def linear_rows(env, w, rows, K):
                     "us_cublas_then_fused_bias_residual": round(t["cublas_fused_bias_residual"], 1),
                     "speedup_vs_reference_sequence": round(t["cublas_bias_residual"] / t["fused"], 3)})
         del A, W, x, y
-    return {"what": "linear() + add_bias_bf16 + gated_residual as one tcgen05 kernel against cuBLAS + the separate ops",
+    # the QKV projection with head norm + rope in its epilogue, against cuBLAS + add_bias_bf16 + qkv_norm_rope
+    inner, Kd, Nq = w.inner, w.dim, 3 * w.inner
+    n_sets = max(2, math.ceil(3.2 * L2_BYTES / (rows * Kd * 2 + rows * Nq * 2)))
+    A = [torch.randn((rows, Kd), generator=g, device="cuda").to(torch.bfloat16) for _ in range(n_sets)]
+    W = (torch.randn((Nq, Kd), generator=g, device="cuda") / Kd ** 0.5).to(torch.bfloat16)
+    bias = torch.randn(Nq, generator=g, device="cuda") * 0.1
+    nq = 1 + 0.05 * torch.randn(w.D, generator=g, device="cuda")
+    nk = 1 + 0.05 * torch.randn(w.D, generator=g, device="cuda")
+    ang = torch.rand((rows, max(w.rot // 2, 1)), generator=g, device="cuda") * 6.2 - 3.1
+    cos, sin = torch.cos(ang).contiguous(), torch.sin(ang).contiguous()
+    y = [torch.empty((rows, Nq), dtype=torch.bfloat16, device="cuda") for _ in range(n_sets)]
+    outs = [[torch.empty((rows, w.H, w.D), dtype=torch.bfloat16, device="cuda") for _ in range(3)] for _ in range(n_sets)]
+    norms, rots, modes = [nq, nk, None], [w.rot, w.rot, 0], [w.rope_mode, w.rope_mode, 0]
+    fused_specs = [[mx.HeadSpec(None, 0, 0, norms[i], o[i], rots[i], modes[i]) for i in range(3)] for o in outs]
+    sep_specs = [[mx.HeadSpec(y[j], Nq, i * inner, norms[i], outs[j][i], rots[i], modes[i]) for i in range(3)] for j in range(n_sets)]
+
+    def q_fused(i):
+        mx.ops.linear_qkv_norm_rope(A[i % n_sets], W, bias, rows, Kd, w.H, w.D, fused_specs[i % n_sets], w.eps, cos, sin, env.stream)
+
+    def q_sep(i):
+        j = i % n_sets
+        torch.matmul(A[j], W.T, out=y[j])
+        mx.ops.add_bias_bf16(y[j], bias, rows, Nq, env.stream)
+        mx.qkv_norm_rope(sep_specs[j], rows, w.H, w.D, w.eps, cos, sin, env.stream)
+
+    def q_gemm(i):
+        torch.matmul(A[i % n_sets], W.T, out=y[i % n_sets])
+
+    if w.D == 128 and w.H % 2 == 0:
+        t = {}
+        for key, fn in (("fused", q_fused), ("cublas_gemm", q_gemm), ("separate", q_sep)):
+            for i in range(3):
+                fn(i)
+            env.barrier()
+            t[key] = statistics.median([env.event_ms(fn, K) / K * 1e3 for _ in range(3)])
+        flops = 2.0 * rows * Nq * Kd
+        out.append({"layer": "QKV projection + head norm + rope", "M": rows, "N": Nq, "K": Kd, "us": round(t["fused"], 1),
+                    "tflops": round(flops / t["fused"] / 1e6, 1), "frac_of_bf16_peak": round(flops / t["fused"] / 1e6 / peak_tf, 3),
+                    "us_cublas_gemm_alone": round(t["cublas_gemm"], 1),
+                    "us_cublas_then_bias_then_qkv_norm_rope": round(t["separate"], 1),
+                    "speedup_vs_reference_sequence": round(t["separate"] / t["fused"], 3)})
+    del A, W, y, outs
+    return {"what": "linear() + add_bias_bf16 + gated_residual (or head_norm_rope) as one tcgen05 kernel against cuBLAS + the separate ops",
             "bf16_peak_tflops": peak_tf, "peak_source": src, "layers": out}
 
 

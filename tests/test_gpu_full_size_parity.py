@@ -87,8 +87,9 @@ def compare(w, b, ref, what):
     H.assert_f32_close(host(b.x), ref["x"], f"{what} x")
 
 
-CASES = [("qwen1024", 0), ("qwen1024", 1), ("qwen2048", 0), ("h3video", 0), ("h3video", 1), ("qwen21_true", 0),
-         ("h3_true", 0)]
+# (the two 33 272-row shapes take the oracle about a minute each on 16 host threads: one chain each, the drop-in one on the
+# benchmark shape and the fused one on the reference's true widths; both chains run at 8704 rows)
+CASES = [("qwen1024", 0), ("qwen1024", 1), ("qwen2048", 0), ("h3video", 0), ("qwen21_true", 0), ("h3_true", 1)]
 
 
 @pytest.mark.parametrize("name,fused", CASES)
