@@ -67,6 +67,9 @@ def parse():
                     help="time only the head exchange of sequence-parallel attention over the ranks' peer buffers (N >= 1)")
     ap.add_argument("--quant-only", action="store_true",
                     help="time only the block-scale quantiser on the block's activations (profiling aid; prints its own line)")
+    ap.add_argument("--no-numa-bind", action="store_true",
+                    help="leave the process where the launcher put it (default: each rank moves onto the CPUs of its GPU's NUMA "
+                         "node before it allocates pinned host buffers; a no-op where the host reports no node)")
     ap.add_argument("--tune", action="append", default=[], metavar="KNOB=VALUE",
                     help="override a launch-shape knob of libmxk (see miroxen_b200/csrc/tuning.h); repeatable")
     ap.add_argument("--cpu-rows", type=int, default=0, help="rows of the CPU sample (default: chosen for ~10-30 s)")
@@ -338,6 +341,12 @@ class Env:
         if not torch.cuda.is_available():
             raise SystemExit("bench.py needs a CUDA device (there is no CPU fallback for the product path)")
         torch.cuda.set_device(self.local)
+        # host-buffer path: run on (and allocate pinned memory from) the NUMA node next to this rank's GPU
+        self.host_placement = {"node": None, "why": "--no-numa-bind"}
+        if not self.args.no_numa_bind:
+            from miroxen_b200 import hostmem
+            self.host_placement = hostmem.bind_to_device_node(self.local)
+            self.host_placement["cpus"] = len(self.host_placement.get("cpus", []))
         if distributed and self.world > 1:
             self.dist.init_process_group("nccl", device_id=torch.device("cuda", self.local))
             self.distributed = True
@@ -841,7 +850,8 @@ def e2e_mxk(env, w, rows, row0, mods, chain, cos, sin, K, total_bytes):
     return {"value": round(total_bytes / dt / 1e9, 2), "unit": UNIT, "ms_per_step": round(dt * 1e3, 3),
             "h2d_bytes_per_step": int(up_all), "d2h_bytes_per_step": int(down_all), "steps": Ke,
             "bytes_note": "summed over the ranks' copies",
-            "api": f"mxk_dit_block_ops_host (pinned host buffers, {args.e2e_chunk_rows}-row chunks, 3 streams per GPU)"}
+            "api": f"mxk_dit_block_ops_host (pinned host buffers, {args.e2e_chunk_rows}-row chunks, 3 streams per GPU)",
+            "host_placement": env.host_placement}
 
 
 def e2e_reference(env, job, K):
@@ -964,9 +974,12 @@ def linear_rows(env, w, rows, K):
             for i in range(3):
                 fn(i)
             env.barrier()
-            t[key] = statistics.median([env.event_ms(fn, K) / K * 1e3 for _ in range(3)])
+            w3 = [env.event_ms(fn, K) / K * 1e3 for _ in range(3)]
+            t[key] = statistics.median(w3)
+            if key == "fused":
+                spread = [round(min(w3), 1), round(max(w3), 1)]
         flops = 2.0 * rows * N * Kd
-        out.append({"layer": name, "M": rows, "N": N, "K": Kd, "us": round(t["fused"], 1),
+        out.append({"layer": name, "M": rows, "N": N, "K": Kd, "us": round(t["fused"], 1), "us_min_max": spread,
                     "tflops": round(flops / t["fused"] / 1e6, 1), "frac_of_bf16_peak": round(flops / t["fused"] / 1e6 / peak_tf, 3),
                     "us_cublas_gemm_alone": round(t["cublas_gemm"], 1),
                     "us_cublas_then_bias_then_residual": round(t["cublas_bias_residual"], 1),
@@ -1007,9 +1020,12 @@ def linear_rows(env, w, rows, K):
             for i in range(3):
                 fn(i)
             env.barrier()
-            t[key] = statistics.median([env.event_ms(fn, K) / K * 1e3 for _ in range(3)])
+            w3 = [env.event_ms(fn, K) / K * 1e3 for _ in range(3)]
+            t[key] = statistics.median(w3)
+            if key == "fused":
+                spread = [round(min(w3), 1), round(max(w3), 1)]
         flops = 2.0 * rows * Nq * Kd
-        out.append({"layer": "QKV projection + head norm + rope", "M": rows, "N": Nq, "K": Kd, "us": round(t["fused"], 1),
+        out.append({"layer": "QKV projection + head norm + rope", "M": rows, "N": Nq, "K": Kd, "us": round(t["fused"], 1), "us_min_max": spread,
                     "tflops": round(flops / t["fused"] / 1e6, 1), "frac_of_bf16_peak": round(flops / t["fused"] / 1e6 / peak_tf, 3),
                     "us_cublas_gemm_alone": round(t["cublas_gemm"], 1),
                     "us_cublas_then_bias_then_qkv_norm_rope": round(t["separate"], 1),

@@ -15,15 +15,16 @@
 // y = A[M, K] · W[N, K]^T, both operands bf16 and K-major (activations row-major, weights in the
 // [out, in] layout the reference keeps them in), fp32 accumulation.
 //
-// Kernel shape: one persistent CTA per SM, 192 threads.
+// Kernel shape: one persistent CTA per SM, 320 threads.
 //   warp 0, one lane:  TMA producer - 128 x 64 tiles of A and 256 x 64 tiles of W (128-byte swizzle) into a
 //                      4-stage shared-memory ring, completing on `full` mbarriers;
 //   warp 1, one lane:  issues tcgen05.mma (M 128, N 256, K 16, cta_group::1) from shared-memory descriptors
 //                      into one of two 256-column TMEM accumulators; tcgen05.commit releases a stage
 //                      (`empty`) and publishes a finished accumulator (`acc_full`);
-//   warps 2-5:         epilogue - each thread owns one row of the tile (its TMEM lane), reads the
-//                      accumulator 32 columns at a time (tcgen05.ld 32x32b), applies the chain above and
-//                      updates x with 128-bit accesses; the other accumulator is being filled meanwhile.
+//   warps 2-9:         epilogue - each thread owns one row of the tile (its TMEM lane; the warp's index modulo 4
+//                      selects the lane quarter) and one half of its 256 columns (warps 2-5 the first, 6-9 the
+//                      second), reads the accumulator 32 columns at a time (tcgen05.ld 32x32b), applies the chain
+//                      above and updates x with 128-bit accesses; the other accumulator is being filled meanwhile.
 // Every mbarrier wait is bounded (bulk_copy.cuh); on a timeout the role records kErrBulkTimeout in the
 // device error word and leaves its loop, the CTA still meets at the final barrier and frees its TMEM.
 // Every copy lands in the shared memory of the CTA that issued it (no copy is broadcast to several CTAs), so the
@@ -47,9 +48,10 @@ template <int CTAS> constexpr int kStageB = BN / CTAS * BK * 2;
 template <int CTAS> constexpr int kStages = CTAS == 1 ? 4 : 6;
 constexpr int kAccCols = BN;                                  // fp32 columns of one accumulator
 constexpr int kTmemCols = 2 * kAccCols;                       // two accumulators: all 512 columns
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8, kEpiThreads = 32 * kEpiWarps;
+constexpr int kThreads = 64 + kEpiThreads;  // producer warp, MMA warp, epilogue warps
 constexpr int EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV = 2;
-constexpr int kHeadDim = 128;  // EPI_QKV: a 256-column tile is exactly two heads
+constexpr int kHeadDim = 128;  // EPI_QKV: a 256-column tile is exactly two heads, one per half of the epilogue warps
 
 struct LinearArgs {
   int64_t M, N, K;
@@ -67,8 +69,21 @@ struct LinearArgs {
   float eps;
   const float* cos;
   const float* sin;
+  int group_m;  // tile order: bands of this many row tiles, walked down the rows first (see tile_coords)
   int* err;
 };
+
+// Tile t of the persistent loop -> (row tile, column tile).  Tiles are numbered band by band; a band is `group_m` row
+// tiles high and as wide as the matrix, and inside a band the number runs down the rows first.  The CTAs of one wave
+// (consecutive numbers) then cover a block of about group_m x (CTAs / group_m) tiles: per wave they read group_m row
+// tiles of A and CTAs / group_m column tiles of W instead of one or two row tiles and ALL of W, which matters once W
+// is larger than L2 (a QKV projection of 15360 x 5120 is 157 MB).
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& mt, int& nt) {
+  const int band = t / (group_m * tiles_n), first = band * group_m;
+  const int rows = tiles_m - first < group_m ? tiles_m - first : group_m;  // the last band may be lower
+  const int r = t - band * group_m * tiles_n;
+  mt = first + r % rows, nt = r / rows;
+}
 
 template <int CTAS>
 struct __align__(1024) LinearSmem {
@@ -130,12 +145,12 @@ __device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, uint64_t desc_a, ui
       : "memory");
 }
 
-// AND of a predicate over the 128 epilogue threads (named barrier 1).
+// AND of a predicate over the epilogue threads (named barrier 1).
 __device__ __forceinline__ bool epilogue_all(bool v) {
   unsigned r;
-  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, 1, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+  asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.b32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, 1, %2, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                : "=r"(r)
-               : "r"(unsigned(v))
+               : "r"(unsigned(v)), "n"(kEpiThreads)
                : "memory");
   return r != 0;
 }
@@ -182,6 +197,106 @@ __device__ __forceinline__ void tc_ld16(unsigned taddr, float (&v)[16]) {
   for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
+// EPI_QKV: normalise, rotate and store one head (128 channels) of one token from its packed bf16 pairs.
+// HC > 0: half mode, pairs (i, i + 16 HC) over the first 32 HC channels; HC == 0: interleaved pairs (2i, 2i + 1)
+// over the first `rot` channels (a multiple of 16; 0: no rotation).  cos / sin rows are read with 128-bit
+// non-coherent loads (the launcher checks their alignment), which the compiler may move ahead of the stores.
+// Channels [C, C + 16) of a head from its packed bf16 pairs, normalised when a weight is given.
+template <int C>
+__device__ __forceinline__ void qkv_chunk(const unsigned (&P)[kHeadDim / 2], bool has_norm, float rstd, const float* nw, float (&v)[16]) {
+#pragma unroll
+  for (int i = 0; i < 8; i++) {
+    const unsigned p = P[C / 2 + i];
+    v[2 * i] = __uint_as_float(p << 16), v[2 * i + 1] = __uint_as_float(p & 0xffff0000u);
+  }
+  if (has_norm) {
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = v[i] * rstd * nw[C + i];
+  }
+}
+template <int N4>
+__device__ __forceinline__ void qkv_table(const float* p, float (&o)[4 * N4]) {  // N4 128-bit loads
+#pragma unroll
+  for (int j = 0; j < N4; j++) {
+    const float4 q = __ldg(reinterpret_cast<const float4*>(p) + j);
+    o[4 * j] = q.x, o[4 * j + 1] = q.y, o[4 * j + 2] = q.z, o[4 * j + 3] = q.w;
+  }
+}
+__device__ __forceinline__ void qkv_store16(bf16* dst, const float (&o)[16]) {
+  float lo[8], hi[8];
+#pragma unroll
+  for (int i = 0; i < 8; i++) lo[i] = o[i], hi[i] = o[8 + i];
+  reinterpret_cast<uint4*>(dst)[0] = pack8(lo);
+  reinterpret_cast<uint4*>(dst)[1] = pack8(hi);
+}
+// Half mode, chunk C of the first half: pairs (C + i, 16 HC + C + i); recursion over the chunks keeps every register
+// index a constant.
+template <int HC, int C>
+__device__ __forceinline__ void qkv_half_chunks(const unsigned (&P)[kHeadDim / 2], bool has_norm, float rstd, const float* nw,
+                                                const float* cr, const float* sr, bf16* orow) {
+  if constexpr (C < 16 * HC) {
+    constexpr int half = 16 * HC;
+    float cs[16], sn[16], va[16], vb[16];
+    qkv_table<4>(cr + C, cs);
+    qkv_table<4>(sr + C, sn);
+    qkv_chunk<C>(P, has_norm, rstd, nw, va);
+    qkv_chunk<half + C>(P, has_norm, rstd, nw, vb);
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+      const float x0 = va[i], x1 = vb[i];
+      va[i] = x0 * cs[i] - x1 * sn[i];
+      vb[i] = fmaf(x0, sn[i], x1 * cs[i]);
+    }
+    qkv_store16(orow + C, va);
+    qkv_store16(orow + half + C, vb);
+    qkv_half_chunks<HC, C + 16>(P, has_norm, rstd, nw, cr, sr, orow);
+  }
+}
+// Channels [C, 128) without rotation.
+template <int C>
+__device__ __forceinline__ void qkv_plain_chunks(const unsigned (&P)[kHeadDim / 2], bool has_norm, float rstd, const float* nw, bf16* orow) {
+  if constexpr (C < kHeadDim) {
+    float v[16];
+    qkv_chunk<C>(P, has_norm, rstd, nw, v);
+    qkv_store16(orow + C, v);
+    qkv_plain_chunks<C + 16>(P, has_norm, rstd, nw, orow);
+  }
+}
+// Interleaved mode (or none): pairs (2i, 2i + 1) over the first `rot` channels.
+template <int C>
+__device__ __forceinline__ void qkv_interleaved_chunks(const unsigned (&P)[kHeadDim / 2], bool has_norm, float rstd, const float* nw,
+                                                       const float* cr, const float* sr, int rot, bf16* orow) {
+  if constexpr (C < kHeadDim) {
+    float v[16];
+    if (C < rot) {
+      float cs[8], sn[8];
+      qkv_table<2>(cr + C / 2, cs);
+      qkv_table<2>(sr + C / 2, sn);
+      qkv_chunk<C>(P, has_norm, rstd, nw, v);
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float x0 = v[2 * i], x1 = v[2 * i + 1];
+        v[2 * i] = x0 * cs[i] - x1 * sn[i];
+        v[2 * i + 1] = fmaf(x0, sn[i], x1 * cs[i]);
+      }
+    } else {
+      qkv_chunk<C>(P, has_norm, rstd, nw, v);
+    }
+    qkv_store16(orow + C, v);
+    qkv_interleaved_chunks<C + 16>(P, has_norm, rstd, nw, cr, sr, rot, orow);
+  }
+}
+template <int HC>
+__device__ __forceinline__ void qkv_head_store(const unsigned (&P)[kHeadDim / 2], bool has_norm, float rstd, const float* nw,
+                                               const float* cr, const float* sr, int rot, bf16* orow) {
+  if constexpr (HC > 0) {
+    qkv_half_chunks<HC, 0>(P, has_norm, rstd, nw, cr, sr, orow);
+    qkv_plain_chunks<32 * HC>(P, has_norm, rstd, nw, orow);
+  } else {
+    qkv_interleaved_chunks<0>(P, has_norm, rstd, nw, cr, sr, rot, orow);
+  }
+}
+
 // Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes (64 bf16) wide under the
 // 128-byte swizzle: start address >> 4 in bits [0, 14); leading byte offset (unused by swizzled K-major
 // layouts) 1 in [16, 30); stride byte offset = 1024 (eight rows) >> 4 in [32, 46); descriptor version 1 in
@@ -200,7 +315,7 @@ constexpr unsigned kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (unsigned(B
 // of the W tile.  The first CTA's MMA thread issues cta_group::2 MMAs that read both CTAs' shared memory and write both
 // CTAs' tensor memory.  Barriers: `full` lives in the first CTA and counts the bytes of both CTAs' copies; `empty` and
 // `acc_full` exist in both CTAs and are signalled in both by the issuing thread's commits; `acc_empty`
-// lives in the first CTA and collects the eight epilogue warps of the pair; `done` is the hand-shake before the
+// lives in the first CTA and collects the sixteen epilogue warps of the pair; `done` is the hand-shake before the
 // tensor memory is freed and a CTA leaves (nobody may still signal into a CTA that has exited).
 template <int EPI, int CTAS>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -219,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
   if (tid == 0) {
     for (int i = 0; i < kSt; i++) mbar_init(smem_u32(&sm.full[i]), 1), mbar_init(smem_u32(&sm.empty[i]), 1);
-    for (int i = 0; i < 2; i++) mbar_init(smem_u32(&sm.acc_full[i]), 1), mbar_init(smem_u32(&sm.acc_empty[i]), 4 * CTAS);
+    for (int i = 0; i < 2; i++) mbar_init(smem_u32(&sm.acc_full[i]), 1), mbar_init(smem_u32(&sm.acc_empty[i]), kEpiWarps * CTAS);
     mbar_init(smem_u32(&sm.done), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -250,7 +365,9 @@ __global__ void __launch_bounds__(kThreads, 1)
       int st = 0;
       unsigned ph = 0;
       for (int t = tile0; t < n_tiles && ok; t += tile_step) {
-        const int m0 = (t / tiles_n) * BM * CTAS + int(rank) * BM, n0 = (t % tiles_n) * BN + int(rank) * (BN / CTAS);
+        int mt, nt;
+        tile_coords(t, tiles_m, tiles_n, a.group_m, mt, nt);
+        const int m0 = mt * BM * CTAS + int(rank) * BM, n0 = nt * BN + int(rank) * (BN / CTAS);
         for (int kb = 0; kb < k_blocks; kb++, issued++) {
           if (issued >= kSt && !mbar_wait(smem_u32(&sm.empty[st]), ph ^ 1u)) {
             ok = false;
@@ -317,18 +434,21 @@ __global__ void __launch_bounds__(kThreads, 1)
       }
     }
   } else {
-    // ---- epilogue: warps 2..5, each on the TMEM lane quarter its warp index selects ----
+    // ---- epilogue: warps 2..9; the warp's index modulo 4 selects its TMEM lane quarter, its group the column half ----
     const int quarter = warp & 3;
+    const int cb = ((warp - 2) >> 2) * (BN / 2);  // first of this thread's 128 columns inside the tile
     const int row_in_tile = quarter * 32 + lane;
-    const int et = tid - 64;  // 0..127
+    const int et = tid - 64;  // 0..255
     int local = 0;
     for (int t = tile0; t < n_tiles; t += tile_step, local++) {
       const int buf = local & 1;
-      const int m0 = (t / tiles_n) * BM * CTAS + int(rank) * BM, n0 = (t % tiles_n) * BN;
-      // stage this tile's bias and act(gate) slices; the barrier (id 1, the four epilogue warps) also
+      int mt, nt;
+      tile_coords(t, tiles_m, tiles_n, a.group_m, mt, nt);
+      const int m0 = mt * BM * CTAS + int(rank) * BM, n0 = nt * BN;
+      // stage this tile's bias and act(gate) slices; the barrier (id 1, the epilogue warps) also
       // separates them from the previous tile's readers
-      asm volatile("bar.sync 1, 128;" ::: "memory");
-      for (int c = et; c < BN; c += 128) {
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
+      for (int c = et; c < BN; c += kEpiThreads) {
         const int64_t col = n0 + c;
         const bool in = col < a.N;
         sm.bias[c] = (a.bias && in) ? a.bias[col] : 0.f;
@@ -346,18 +466,18 @@ __global__ void __launch_bounds__(kThreads, 1)
           sm.gate[0][c] = nw ? nw[c] : 1.f;
         }
       }
-      asm volatile("bar.sync 1, 128;" ::: "memory");
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       if (EPI == EPI_RESIDUAL) {
-        // While the tile's main loop is still running: pull this thread's row of x (1 KB) towards L2, so that the
-        // epilogue's loads, eight dependent round trips per tile otherwise, find it there.
+        // While the tile's main loop is still running: pull this thread's part of its row of x (512 bytes) towards L2,
+        // so that the epilogue's loads, four dependent round trips per tile otherwise, find it there.
         const int64_t prow = int64_t(m0) + row_in_tile;
         if (prow < a.M) {
-          const char* xr = reinterpret_cast<const char*>(a.x + prow * a.N + n0);
-          for (int j = 0; j < BN * 4 / 128; j++)
-            if (n0 + 32 * j < a.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(xr + 128 * j));
+          const char* xr = reinterpret_cast<const char*>(a.x + prow * a.N + n0 + cb);
+          for (int j = 0; j < BN / 2 * 4 / 128; j++)
+            if (n0 + cb + 32 * j < a.N) asm volatile("prefetch.global.L2 [%0];" ::"l"(xr + 128 * j));
         }
       }
-      // the four warps agree on the outcome of the wait, so that none is left alone at the next named barrier
+      // the warps agree on the outcome of the wait, so that none is left alone at the next named barrier
       const bool landed = mbar_wait(smem_u32(&sm.acc_full[buf]), unsigned((local >> 1) & 1));
       if (!epilogue_all(landed)) {
         ok = false;
@@ -368,143 +488,100 @@ __global__ void __launch_bounds__(kThreads, 1)
       const bool row_on = row < a.M;
       const float* g = sm.gate[(EPI == EPI_RESIDUAL && row < a.gate.prefix_len) ? 0 : 1];
       const unsigned taddr = tmem_base + (unsigned(quarter * 32) << 16) + unsigned(buf * kAccCols);
+      // this warp is done reading the accumulator (the pair's `acc_empty` is the first CTA's)
+      auto release = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if (CTAS == 1) mbar_arrive_local(smem_u32(&sm.acc_empty[buf]));
+          else mbar_arrive_cluster(map_to_cta(smem_u32(&sm.acc_empty[buf]), 0));
+        }
+      };
       if constexpr (EPI == EPI_QKV) {
-        // The tile's 256 columns are heads h0 and h0 + 1 of one tensor; this thread holds one token's row of both.
-        // Per head: one pass over the accumulator for the sum of squares, a second one to normalise, rotate and
-        // store (re-reading tensor memory is cheaper than keeping 128 values in registers).  A value is what the
-        // separate calls would have read from memory: bf16(acc), then bf16(. + bias).
+        // The tile's 256 columns are two heads of one tensor; this thread holds one token's row of one of them.
+        // One pass over the accumulator takes each value the way the separate calls would have read it from memory -
+        // bf16(acc), then bf16(. + bias) - keeps it as packed bf16 pairs (64 registers) and sums the squares.  The
+        // accumulator is handed back right after that pass; normalising, rotating and storing run from registers
+        // while the tensor cores fill it again.
         const int inner = a.H * kHeadDim;
-        const int ti = n0 / inner, h0 = (n0 - ti * inner) / kHeadDim;
+        const int ti = n0 / inner, h = (n0 - ti * inner + cb) / kHeadDim;
         const bool has_norm = a.norm_w[ti] != nullptr;
-        const int mode = a.mode[ti], rot = mode == MXK_ROPE_NONE ? 0 : a.rot[ti], half = rot >> 1;
-        const float* nw = sm.gate[0];
-        auto value = [&](float acc, int c) {  // c: column inside the tile
-          float v = __bfloat162float(__float2bfloat16(acc));
-          if (a.bias) v = __bfloat162float(__float2bfloat16(v + sm.bias[c]));
-          return v;
-        };
-        auto store16 = [&](bf16* dst, const float (&o)[16]) {
-          float lo[8], hi[8];
+        const int mode = a.mode[ti], rot = mode == MXK_ROPE_NONE ? 0 : a.rot[ti];
+        unsigned P[kHeadDim / 2];
+        float ss = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; i++) lo[i] = o[i], hi[i] = o[8 + i];
-          reinterpret_cast<uint4*>(dst)[0] = pack8(lo);
-          reinterpret_cast<uint4*>(dst)[1] = pack8(hi);
-        };
-#pragma unroll 1
-        for (int hh = 0; hh < 2; hh++) {
-          const int cb = hh * kHeadDim;  // first column of the head inside the tile
-          float rstd = 1.f;
-          if (has_norm) {
-            float ss = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < kHeadDim; c += 16) {
-              float acc[16];
-              tc_ld16(taddr + unsigned(cb + c), acc);
+        for (int c = 0; c < kHeadDim; c += 16) {
+          float acc[16];
+          tc_ld16(taddr + unsigned(cb + c), acc);
 #pragma unroll
-              for (int i = 0; i < 16; i++) {
-                const float v = value(acc[i], cb + c + i);
-                ss = fmaf(v, v, ss);
-              }
+          for (int i = 0; i < 16; i += 2) {
+            float v0 = __bfloat162float(__float2bfloat16(acc[i])), v1 = __bfloat162float(__float2bfloat16(acc[i + 1]));
+            if (a.bias) {
+              v0 = __bfloat162float(__float2bfloat16(v0 + sm.bias[cb + c + i]));
+              v1 = __bfloat162float(__float2bfloat16(v1 + sm.bias[cb + c + i + 1]));
             }
-            rstd = rsqrtf(ss * (1.f / kHeadDim) + a.eps);
+            ss = fmaf(v0, v0, ss);
+            ss = fmaf(v1, v1, ss);
+            P[(c + i) >> 1] = (__float_as_uint(v0) >> 16) | (__float_as_uint(v1) & 0xffff0000u);  // both are bf16 values
           }
-          bf16* orow = row_on ? a.out[ti] + (row * a.H + h0 + hh) * kHeadDim : nullptr;
+        }
+        release();
+        if (row_on) {
+          const float rstd = has_norm ? rsqrtf(ss * (1.f / kHeadDim) + a.eps) : 1.f;
+          bf16* orow = a.out[ti] + (row * a.H + h) * kHeadDim;
+          const int half = rot >> 1;
           const float* cr = a.cos + row * half;
           const float* sr = a.sin + row * half;
-          auto normed = [&](float (&v)[16], int c) {  // c: first column inside the head
-            float acc[16];
-            tc_ld16(taddr + unsigned(cb + c), acc);
-#pragma unroll
-            for (int i = 0; i < 16; i++) {
-              v[i] = value(acc[i], cb + c + i);
-              if (has_norm) v[i] = v[i] * rstd * nw[c + i];
-            }
-          };
           if (mode == MXK_ROPE_HALF && rot > 0) {
-            // pairs (i, i + half): the 16-column chunk at c pairs with the one at half + c (half % 16 == 0)
-#pragma unroll 1
-            for (int c = 0; c < half; c += 16) {
-              float va[16], vb[16];
-              normed(va, c);
-              normed(vb, half + c);
-              if (row_on) {
-#pragma unroll
-                for (int i = 0; i < 16; i++) {
-                  const float cs = cr[c + i], sn = sr[c + i], x0 = va[i], x1 = vb[i];
-                  va[i] = x0 * cs - x1 * sn;
-                  vb[i] = fmaf(x0, sn, x1 * cs);
-                }
-                store16(orow + c, va);
-                store16(orow + half + c, vb);
-              }
+            switch (rot >> 5) {  // rot is a multiple of 32 in this mode
+              case 1: qkv_head_store<1>(P, has_norm, rstd, sm.gate[0], cr, sr, rot, orow); break;
+              case 2: qkv_head_store<2>(P, has_norm, rstd, sm.gate[0], cr, sr, rot, orow); break;
+              case 3: qkv_head_store<3>(P, has_norm, rstd, sm.gate[0], cr, sr, rot, orow); break;
+              default: qkv_head_store<4>(P, has_norm, rstd, sm.gate[0], cr, sr, rot, orow); break;
             }
-          } else if (mode == MXK_ROPE_INTERLEAVED && rot > 0) {
-#pragma unroll 1
-            for (int c = 0; c < rot; c += 16) {  // pairs (2i, 2i + 1): eight of them per chunk (rot % 16 == 0)
-              float v[16];
-              normed(v, c);
-              if (row_on) {
-#pragma unroll
-                for (int i = 0; i < 8; i++) {
-                  const float cs = cr[(c >> 1) + i], sn = sr[(c >> 1) + i], x0 = v[2 * i], x1 = v[2 * i + 1];
-                  v[2 * i] = x0 * cs - x1 * sn;
-                  v[2 * i + 1] = fmaf(x0, sn, x1 * cs);
-                }
-                store16(orow + c, v);
-              }
-            }
-          }
-#pragma unroll 1
-          for (int c = rot; c < kHeadDim; c += 16) {  // channels outside the rotation
-            float v[16];
-            normed(v, c);
-            if (row_on) store16(orow + c, v);
+          } else {
+            qkv_head_store<0>(P, has_norm, rstd, sm.gate[0], cr, sr, rot, orow);
           }
         }
-      } else
+      } else {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        float acc[32];
-        tc_ld32(taddr + unsigned(c0), acc);  // warp-wide: every lane takes part whether or not its row exists
-        if (!row_on || n0 + c0 >= a.N) continue;
-        if (EPI == EPI_RESIDUAL) {
-          float4* xr = reinterpret_cast<float4*>(a.x + row * a.N + n0 + c0);
-          float4 xv[8];
+        for (int c0 = cb; c0 < cb + BN / 2; c0 += 32) {
+          float acc[32];
+          tc_ld32(taddr + unsigned(c0), acc);  // warp-wide: every lane takes part whether or not its row exists
+          if (!row_on || n0 + c0 >= a.N) continue;
+          if (EPI == EPI_RESIDUAL) {
+            float4* xr = reinterpret_cast<float4*>(a.x + row * a.N + n0 + c0);
+            float4 xv[8];
 #pragma unroll
-          for (int j = 0; j < 8; j++) xv[j] = xr[j];
+            for (int j = 0; j < 8; j++) xv[j] = xr[j];
 #pragma unroll
-          for (int j = 0; j < 8; j++) {
-            float y[4] = {acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]};
-            float o[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
+            for (int j = 0; j < 8; j++) {
+              float y[4] = {acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]};
+              float o[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
 #pragma unroll
-            for (int i = 0; i < 4; i++) {
-              float v = __bfloat162float(__float2bfloat16(y[i]));                               // the GEMM's bf16 output
-              if (a.bias) v = __bfloat162float(__float2bfloat16(v + sm.bias[c0 + 4 * j + i]));  // add_bias_bf16
-              o[i] = fmaf(v, g[c0 + 4 * j + i], o[i]);                                          // gated_residual
+              for (int i = 0; i < 4; i++) {
+                float v = __bfloat162float(__float2bfloat16(y[i]));                               // the GEMM's bf16 output
+                if (a.bias) v = __bfloat162float(__float2bfloat16(v + sm.bias[c0 + 4 * j + i]));  // add_bias_bf16
+                o[i] = fmaf(v, g[c0 + 4 * j + i], o[i]);                                          // gated_residual
+              }
+              xr[j] = make_float4(o[0], o[1], o[2], o[3]);
             }
-            xr[j] = make_float4(o[0], o[1], o[2], o[3]);
-          }
-        } else {
-          uint4* yr = reinterpret_cast<uint4*>(a.y + row * a.N + n0 + c0);
+          } else {
+            uint4* yr = reinterpret_cast<uint4*>(a.y + row * a.N + n0 + c0);
 #pragma unroll
-          for (int j = 0; j < 4; j++) {
-            float o[8];
+            for (int j = 0; j < 4; j++) {
+              float o[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-              float v = __bfloat162float(__float2bfloat16(acc[8 * j + i]));
-              if (a.bias) v += sm.bias[c0 + 8 * j + i];
-              o[i] = v;
+              for (int i = 0; i < 8; i++) {
+                float v = __bfloat162float(__float2bfloat16(acc[8 * j + i]));
+                if (a.bias) v += sm.bias[c0 + 8 * j + i];
+                o[i] = v;
+              }
+              yr[j] = pack8(o);
             }
-            yr[j] = pack8(o);
           }
         }
-      }
-      // this warp is done reading the accumulator (the pair's `acc_empty` is the first CTA's)
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        if (CTAS == 1) mbar_arrive_local(smem_u32(&sm.acc_empty[buf]));
-        else mbar_arrive_cluster(map_to_cta(smem_u32(&sm.acc_empty[buf]), 0));
+        release();
       }
     }
   }
@@ -585,9 +662,16 @@ int run_linear(const char* name, const mxk_bf16* A, const mxk_bf16* W, LinearArg
   if (a.gate.target && !a.gate.prefix && a.gate.prefix_len > 0)
     return fail(MXK_ERR_INVALID_ARG, "%s: prefix_len > 0 with a null prefix vector", name);
   a.err = device_error_word();
-  // Two CTAs per tile (a cluster of two, half of the W tile each) when there is more than one 256-row tile; the
-  // single-CTA form otherwise and on request (`linear_ctas = 1`).
-  const bool pair = tune(TUNE_LINEAR_CTAS, 2) == 2 && a.M > BM;
+  // Two CTAs per tile (a cluster of two, half of the W tile each) or one.  A pair tile of 256 x 256 takes about 0.9 of
+  // the time of the two 128 x 256 tiles it replaces (less operand traffic), but pairs quantise the work more coarsely:
+  // the form that needs fewer (weighted) waves over the SMs runs.  `linear_ctas` = 1 / 2 forces a form.
+  const int want = tune(TUNE_LINEAR_CTAS, 0);
+  const int64_t waves1 = ceil_div(ceil_div(a.M, BM) * ceil_div(a.N, BN), int64_t(sm_count()));
+  const int64_t waves2 = ceil_div(ceil_div(a.M, 2 * BM) * ceil_div(a.N, BN), int64_t(sm_count() / 2));
+  const bool pair = a.M > BM && want != 1 && (want == 2 || 9 * waves2 <= 10 * waves1);
+  // band height of the tile order: a wave of 74 pairs as 8 x 9 tiles of 256 x 256, of 148 CTAs as 16 x 9 tiles of 128 x 256
+  a.group_m = tune(TUNE_LINEAR_GROUP_M, pair ? 8 : 16);
+  if (a.group_m < 1) a.group_m = 1;
   return pair ? launch_linear<EPI, 2>(name, A, W, a, s) : launch_linear<EPI, 1>(name, A, W, a, s);
 }
 

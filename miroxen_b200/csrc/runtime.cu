@@ -20,7 +20,7 @@ const char* const kTuneNames[TUNE_COUNT] = {
     "res_threads",  "ew_threads",       "ew_unroll",    "act_rows_per_cta", "norm_path",
     "norm_stages",  "rope_path",        "rope_stages",  "ew_ctas_per_sm",   "res_path",     "rope_tokens",
     "stream_warps", "stream_stages",    "stream_ctas_per_sm", "stream_chunk_kb", "act_path",
-    "pdl",          "norm_interleave", "pipe_interleave", "quant_rows_per_cta", "quant_path", "rope_unroll", "rope_wide", "rope_wide_regs", "linear_ctas",
+    "pdl",          "norm_interleave", "pipe_interleave", "quant_rows_per_cta", "quant_path", "rope_unroll", "rope_wide", "rope_wide_regs", "linear_ctas", "linear_group_m",
 };
 }  // namespace
 

@@ -35,7 +35,8 @@ enum TuneKey {
   TUNE_ROPE_UNROLL,        // 1: head pipeline with the pass loop unrolled where the shape allows (default), 2: runtime loop
   TUNE_ROPE_WIDE,          // 1: sixteen channels per lane for D = 128, 2: eight channels per lane (default)
   TUNE_ROPE_WIDE_REGS,     // wide head kernel's register budget: 1 = 128 registers for CTAs of up to 128 threads (default), 2 = 96 everywhere
-  TUNE_LINEAR_CTAS,        // linear layers: 2 = a pair of CTAs per 256 x 256 tile (default), 1 = one CTA per 128 x 256 tile
+  TUNE_LINEAR_CTAS,        // linear layers: 2 = a pair of CTAs per 256 x 256 tile, 1 = one CTA per 128 x 256 tile, 0 = whichever needs fewer waves (default)
+  TUNE_LINEAR_GROUP_M,     // linear layers: row tiles per band of the tile order (default 8 for CTA pairs, 16 for single CTAs)
   TUNE_COUNT
 };
 

@@ -66,6 +66,26 @@ def test_linear_bf16_equals_the_fp32_product(mx, M, N, K, with_bias):
         assert float((y.t != ref).float().mean()) < 0.02
 
 
+@pytest.mark.parametrize("group_m", [1, 3, 5])
+def test_tile_order_does_not_change_a_result(mx, group_m):
+    """The persistent loop numbers its tiles in bands of `linear_group_m` row tiles; every band height (a last band
+    lower than the others included: 1000 rows are 4 pair tiles or 8 single tiles) gives the same bits, because a tile's
+    arithmetic does not depend on who computes it when."""
+    M, N, K = 1000, 3072, 512
+    A, W, bias = operands(M, N, K, 77)
+    want = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    mx.linear_bf16(A, W, bias, M, N, K, want)
+    mx.set_tuning("linear_group_m", group_m)
+    try:
+        y = H.Guarded(torch, (M, N), torch.bfloat16)
+        mx.linear_bf16(A, W, bias, M, N, K, y.t)
+        torch.cuda.synchronize()
+    finally:
+        mx.set_tuning("linear_group_m", 0)
+    y.check("linear y")
+    assert torch.equal(y.t, want)
+
+
 @pytest.mark.parametrize("M,N,K", [(1000, 3072, 3072), (272, 3072, 12288), (130, 5120, 512), (5, 320, 200)])
 @pytest.mark.parametrize("mode", ["tanh_prefix_bias", "identity", "none"])
 def test_linear_gated_residual_equals_the_separate_calls(mx, M, N, K, mode):
