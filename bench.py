@@ -931,6 +931,22 @@ def run_reference_cuda(args, W):
     print(json.dumps(line), flush=True)
 
 
+def interleaved_windows(env, K, arms, rounds=5):
+    """µs per call of every arm: `rounds` rounds, each one window of K calls per arm in turn (CUDA events), median per
+    arm.  The arms alternate so that a drift of the clocks under the power cap during these milliseconds-long
+    GEMMs falls on all of them alike.  Returns ({arm: µs}, [min, max] of the first arm's windows)."""
+    for _, fn in arms:
+        for i in range(3):
+            fn(i)
+    env.barrier()
+    win = {key: [] for key, _ in arms}
+    for _ in range(rounds):
+        for key, fn in arms:
+            win[key].append(env.event_ms(fn, K) / K * 1e3)
+    first = win[arms[0][0]]
+    return {key: statistics.median(v) for key, v in win.items()}, [round(min(first), 1), round(max(first), 1)]
+
+
 def linear_rows(env, w, rows, K):
     """The two projections that feed a gated_residual (attention out-projection: K = H*D; second MLP
     projection: K = F), as one tensor-core kernel with bias + gate + residual in its epilogue, against what it
@@ -969,15 +985,8 @@ def linear_rows(env, w, rows, K):
             torch.matmul(A[j], W.T, out=y[j])
             mx.ops.gated_residual_bias(x[j], y[j], bias, rows, N, gate, w.gate_tanh, env.stream)
 
-        t = {}
-        for key, fn in (("fused", fused), ("cublas_gemm", gemm_only), ("cublas_bias_residual", three_calls), ("cublas_fused_bias_residual", two_calls)):
-            for i in range(3):
-                fn(i)
-            env.barrier()
-            w3 = [env.event_ms(fn, K) / K * 1e3 for _ in range(3)]
-            t[key] = statistics.median(w3)
-            if key == "fused":
-                spread = [round(min(w3), 1), round(max(w3), 1)]
+        t, spread = interleaved_windows(env, K, (("fused", fused), ("cublas_gemm", gemm_only), ("cublas_bias_residual", three_calls),
+                                                 ("cublas_fused_bias_residual", two_calls)))
         flops = 2.0 * rows * N * Kd
         out.append({"layer": name, "M": rows, "N": N, "K": Kd, "us": round(t["fused"], 1), "us_min_max": spread,
                     "tflops": round(flops / t["fused"] / 1e6, 1), "frac_of_bf16_peak": round(flops / t["fused"] / 1e6 / peak_tf, 3),
@@ -1015,15 +1024,7 @@ def linear_rows(env, w, rows, K):
         torch.matmul(A[i % n_sets], W.T, out=y[i % n_sets])
 
     if w.D == 128 and w.H % 2 == 0:
-        t = {}
-        for key, fn in (("fused", q_fused), ("cublas_gemm", q_gemm), ("separate", q_sep)):
-            for i in range(3):
-                fn(i)
-            env.barrier()
-            w3 = [env.event_ms(fn, K) / K * 1e3 for _ in range(3)]
-            t[key] = statistics.median(w3)
-            if key == "fused":
-                spread = [round(min(w3), 1), round(max(w3), 1)]
+        t, spread = interleaved_windows(env, K, (("fused", q_fused), ("cublas_gemm", q_gemm), ("separate", q_sep)))
         flops = 2.0 * rows * Nq * Kd
         out.append({"layer": "QKV projection + head norm + rope", "M": rows, "N": Nq, "K": Kd, "us": round(t["fused"], 1), "us_min_max": spread,
                     "tflops": round(flops / t["fused"] / 1e6, 1), "frac_of_bf16_peak": round(flops / t["fused"] / 1e6 / peak_tf, 3),
@@ -1186,8 +1187,10 @@ def main():
     if args.linear_only:
         job.close()
         if rank == 0:
-            print(json.dumps({"impl": args.impl, "workload": w.name, "rows": rows, "steps": K, "linear_epilogue": linear_rows(env, w, rows, K)}),
-                  flush=True)
+            with ClockSampler(env.local) as sampler:
+                rec = linear_rows(env, w, rows, K)
+            print(json.dumps({"impl": args.impl, "workload": w.name, "rows": rows, "steps": K, "tune": args.tune, "linear_epilogue": rec,
+                              "clocks": sampler.summary()}), flush=True)
         return
     if args.quant_only:
         if rank == 0:
