@@ -1032,7 +1032,45 @@ def linear_rows(env, w, rows, K):
                     "us_cublas_then_bias_then_qkv_norm_rope": round(t["separate"], 1),
                     "speedup_vs_reference_sequence": round(t["separate"] / t["fused"], 3)})
     del A, W, y, outs
-    return {"what": "linear() + add_bias_bf16 + gated_residual (or head_norm_rope) as one tcgen05 kernel against cuBLAS + the separate ops",
+    # the first MLP projection with its activation in the epilogue, against cuBLAS + add_bias_bf16 + the activation
+    Kd, F = w.dim, w.F
+    swiglu = w.act_mode == 1
+    Nw = 2 * F if swiglu else F
+    n_sets = max(2, math.ceil(3.2 * L2_BYTES / (rows * Kd * 2 + rows * Nw * 2)))
+    A = [torch.randn((rows, Kd), generator=g, device="cuda").to(torch.bfloat16) for _ in range(n_sets)]
+    W = (torch.randn((Nw, Kd), generator=g, device="cuda") / Kd ** 0.5).to(torch.bfloat16)
+    bias = torch.randn(Nw, generator=g, device="cuda") * 0.1
+    y = [torch.empty((rows, Nw), dtype=torch.bfloat16, device="cuda") for _ in range(n_sets)]
+    mid = [torch.empty((rows, F), dtype=torch.bfloat16, device="cuda") for _ in range(n_sets)]
+
+    def f_fused(i):
+        j = i % n_sets
+        if swiglu:
+            mx.ops.linear_silu_mul(A[j], W, bias, rows, F, Kd, mid[j], env.stream)
+        else:
+            mx.ops.linear_act(A[j], W, bias, rows, F, Kd, w.act_mode, mid[j], env.stream)
+
+    def f_sep(i):
+        j = i % n_sets
+        torch.matmul(A[j], W.T, out=y[j])
+        mx.ops.add_bias_bf16(y[j], bias, rows, Nw, env.stream)
+        if swiglu:
+            mx.ops.silu_mul(y[j], rows, F, mid[j], env.stream)
+        else:
+            mx.ops.gelu_tanh_inplace(y[j], rows * F, env.stream)
+
+    def f_gemm(i):
+        torch.matmul(A[i % n_sets], W.T, out=y[i % n_sets])
+
+    t, spread = interleaved_windows(env, K, (("fused", f_fused), ("cublas_gemm", f_gemm), ("separate", f_sep)))
+    flops = 2.0 * rows * Nw * Kd
+    out.append({"layer": "first MLP projection + " + ("silu_mul" if swiglu else "gelu_tanh"), "M": rows, "N": Nw, "K": Kd,
+                "us": round(t["fused"], 1), "us_min_max": spread, "tflops": round(flops / t["fused"] / 1e6, 1),
+                "frac_of_bf16_peak": round(flops / t["fused"] / 1e6 / peak_tf, 3), "us_cublas_gemm_alone": round(t["cublas_gemm"], 1),
+                "us_cublas_then_bias_then_activation": round(t["separate"], 1),
+                "speedup_vs_reference_sequence": round(t["separate"] / t["fused"], 3)})
+    del A, W, y, mid
+    return {"what": "linear() + add_bias_bf16 + gated_residual (or head_norm_rope, or the MLP activation) as one tcgen05 kernel against cuBLAS + the separate ops",
             "bf16_peak_tflops": peak_tf, "peak_source": src, "layers": out}
 
 

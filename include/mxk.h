@@ -212,10 +212,21 @@ int mxk_peer_buffer_free(void* ptr);
  *   NULL; tensors_host[i] gives tensor i's norm_w (NULL: none), rot, mode and out (bf16 [M, H, 128]); its in,
  *   in_stride and col0 are ignored.  = linear() + head_norm_rope() per tensor, the [M, 3 H D] projection
  *   output never written.  D must be 128 and H even; rot a multiple of 16 (interleaved) or 32 (half).
+ * mxk_linear_act:             y bf16 [M, N] = act(A W^T (+ bias)), act_mode 0 GELU (tanh form) / 2 GELU (erf form)
+ *   = linear() + gelu_tanh_inplace() (src/models/qwen_image/dit.cpp:192-193), one write instead of a write and
+ *   a read-modify-write.
+ * mxk_linear_silu_mul:        out bf16 [M, F] = silu(g) * u with [g | u] = A W^T (+ bias), W bf16 [2 F, K] (gate rows,
+ *   then up rows: the reference's concatenated gate_up weight), bias fp32 [2 F] or NULL.  = linear(gate_up) +
+ *   silu_mul() (src/models/qwen_image/dit.cpp:309-312, src/models/minimax_h3/dit.cpp:241-242); the [M, 2 F]
+ *   projection is never written.  F % 32 == 0.
  * No counterpart as single calls in the reference (each replaces two or three of its calls). */
 int mxk_linear_qkv_norm_rope(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t K, int H, int D,
                              const MxkHeadTensor* tensors_host, int n_tensors, float eps, const float* cos, const float* sin,
                              mxk_stream_t stream);
+int mxk_linear_act(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, int act_mode,
+                   mxk_bf16* y, mxk_stream_t stream);
+int mxk_linear_silu_mul(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t F, int64_t K, mxk_bf16* out,
+                        mxk_stream_t stream);
 int mxk_linear_bf16(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, mxk_bf16* y,
                     mxk_stream_t stream);
 int mxk_linear_gated_residual(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, float* x,

@@ -104,6 +104,8 @@ PROTOTYPES = {
     "mxk_peer_buffer_close": (_I, [_P]),
     "mxk_peer_buffer_free": (_I, [_P]),
     "mxk_linear_bf16": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P]),
+    "mxk_linear_act": (_I, [_P, _P, _P, _I64, _I64, _I64, _I, _P, _P]),
+    "mxk_linear_silu_mul": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, _P]),
     "mxk_linear_qkv_norm_rope": (_I, [_P, _P, _P, _I64, _I64, _I, _I, C.POINTER(HeadTensor), _I, _F, _P, _P, _P]),
     "mxk_linear_gated_residual": (_I, [_P, _P, _P, _I64, _I64, _I64, _P, RowMod, _I, _P]),
     "mxk_rope_table_expand": (_I, [_P, _P, C.POINTER(C.c_int64), C.POINTER(C.c_int32), C.POINTER(C.c_int32), _I,

@@ -10,7 +10,12 @@
 //     y  = bf16(y + bias[col])             add_bias_bf16 (src/kernels/ops.cu:249-262), when a bias is given
 //     x += act(gate[col]) * y              gated_residual (src/kernels/ops.cu:73-84), EPI_RESIDUAL
 // so the bf16 projection output never exists in memory: 2·M·N bytes written and 4·M·N (bias) + 2·M·N
-// (residual) bytes re-read disappear.  EPI_STORE writes y as bf16 instead (a plain linear layer).
+// (residual) bytes re-read disappear.  EPI_STORE writes y as bf16 instead (a plain linear layer), optionally through
+// GELU (the reference's linear -> gelu_tanh_inplace, src/models/qwen_image/dit.cpp:192-193).  EPI_SWIGLU is the first
+// MLP projection with silu_mul in its epilogue (linear(gate_up) -> silu_mul, src/models/qwen_image/dit.cpp:309-312,
+// src/models/minimax_h3/dit.cpp:241-242): a tile's 256 accumulator columns are 128 gate columns and the 128 up
+// columns F further along the weight's rows, the epilogue writes silu(gate) * up, and the [M, 2F] projection
+// (written once, read once) never exists.
 //
 // y = A[M, K] · W[N, K]^T, both operands bf16 and K-major (activations row-major, weights in the
 // [out, in] layout the reference keeps them in), fp32 accumulation.
@@ -33,6 +38,7 @@
 
 #include <atomic>
 
+#include "act_math.cuh"
 #include "bulk_copy.cuh"
 #include "common.cuh"
 #include "tuning.h"
@@ -50,13 +56,16 @@ constexpr int kAccCols = BN;                                  // fp32 columns of
 constexpr int kTmemCols = 2 * kAccCols;                       // two accumulators: all 512 columns
 constexpr int kEpiWarps = 8, kEpiThreads = 32 * kEpiWarps;
 constexpr int kThreads = 64 + kEpiThreads;  // producer warp, MMA warp, epilogue warps
-constexpr int EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV = 2;
+constexpr int EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV = 2, EPI_SWIGLU = 3;
+// output columns one tile covers: EPI_SWIGLU spends half of the accumulator on the up half of the projection
+template <int EPI> constexpr int kTileCols = EPI == EPI_SWIGLU ? BN / 2 : BN;
 constexpr int kHeadDim = 128;  // EPI_QKV: a 256-column tile is exactly two heads, one per half of the epilogue warps
 
 struct LinearArgs {
   int64_t M, N, K;
   const float* bias;  // fp32 [N] or null
-  bf16* y;            // EPI_STORE: bf16 [M, N]
+  bf16* y;            // EPI_STORE, EPI_SWIGLU: bf16 [M, N]
+  int act;            // EPI_STORE: 0 none, 1 GELU (tanh form), 2 GELU (erf form) applied to the stored value
   float* x;           // EPI_RESIDUAL: fp32 [M, N], updated in place
   MxkRowMod gate;     // EPI_RESIDUAL
   int gate_tanh;
@@ -327,7 +336,8 @@ __global__ void __launch_bounds__(kThreads, 1)
   constexpr int kSt = kStages<CTAS>;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const unsigned rank = CTAS == 2 ? cluster_rank() : 0u;
-  const int tiles_n = int((a.N + BN - 1) / BN), tiles_m = int((a.M + BM * CTAS - 1) / (BM * CTAS));
+  constexpr int TN = kTileCols<EPI>;  // output columns per tile
+  const int tiles_n = int((a.N + TN - 1) / TN), tiles_m = int((a.M + BM * CTAS - 1) / (BM * CTAS));
   const int n_tiles = tiles_m * tiles_n;
   const int k_blocks = int((a.K + BK - 1) / BK);
   const int tile0 = int(blockIdx.x) / CTAS, tile_step = int(gridDim.x) / CTAS;
@@ -367,7 +377,10 @@ __global__ void __launch_bounds__(kThreads, 1)
       for (int t = tile0; t < n_tiles && ok; t += tile_step) {
         int mt, nt;
         tile_coords(t, tiles_m, tiles_n, a.group_m, mt, nt);
-        const int m0 = mt * BM * CTAS + int(rank) * BM, n0 = nt * BN + int(rank) * (BN / CTAS);
+        // W rows of this CTA's part of the B tile.  EPI_SWIGLU: gate rows [nt TN, +128) then up rows [N + nt TN, +128);
+        // in a pair the first CTA loads the gate rows and the second the up rows
+        const int m0 = mt * BM * CTAS + int(rank) * BM;
+        const int n0 = EPI == EPI_SWIGLU ? nt * TN + int(rank) * int(a.N) : nt * BN + int(rank) * (BN / CTAS);
         for (int kb = 0; kb < k_blocks; kb++, issued++) {
           if (issued >= kSt && !mbar_wait(smem_u32(&sm.empty[st]), ph ^ 1u)) {
             ok = false;
@@ -377,7 +390,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             const unsigned bar = smem_u32(&sm.full[st]);
             mbar_expect_tx(bar, kStageA + kStageB<1>);
             tma_load_2d(smem_u32(sm.a[st]), &map_a, kb * BK, m0, bar);
-            tma_load_2d(smem_u32(sm.b[st]), &map_w, kb * BK, n0, bar);
+            if (EPI == EPI_SWIGLU) {  // two boxes of 128 rows: stacked they are the 256-row tile (16 KB = 16 swizzle groups each)
+              tma_load_2d(smem_u32(sm.b[st]), &map_w, kb * BK, n0, bar);
+              tma_load_2d(smem_u32(sm.b[st]) + kStageB<1> / 2, &map_w, kb * BK, n0 + int(a.N), bar);
+            } else {
+              tma_load_2d(smem_u32(sm.b[st]), &map_w, kb * BK, n0, bar);
+            }
           } else {
             // the pair's `full` barrier is the first CTA's: it expects both CTAs' bytes, both CTAs' copies count on it
             if (rank == 0) mbar_expect_tx(smem_u32(&sm.full[st]), 2 * (kStageA + kStageB<2>));
@@ -444,13 +462,14 @@ __global__ void __launch_bounds__(kThreads, 1)
       const int buf = local & 1;
       int mt, nt;
       tile_coords(t, tiles_m, tiles_n, a.group_m, mt, nt);
-      const int m0 = mt * BM * CTAS + int(rank) * BM, n0 = nt * BN;
+      const int m0 = mt * BM * CTAS + int(rank) * BM, n0 = nt * TN;
       // stage this tile's bias and act(gate) slices; the barrier (id 1, the epilogue warps) also
       // separates them from the previous tile's readers
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiThreads) : "memory");
       for (int c = et; c < BN; c += kEpiThreads) {
-        const int64_t col = n0 + c;
-        const bool in = col < a.N;
+        // accumulator column c -> projection column: EPI_SWIGLU keeps the up half N columns further along
+        const int64_t col = EPI == EPI_SWIGLU ? n0 + (c & (TN - 1)) + (c >= TN ? a.N : 0) : n0 + c;
+        const bool in = EPI == EPI_SWIGLU ? n0 + (c & (TN - 1)) < a.N : col < a.N;
         sm.bias[c] = (a.bias && in) ? a.bias[col] : 0.f;
         if (EPI == EPI_RESIDUAL) {
           float gp = 1.f, gt = 1.f;
@@ -543,6 +562,31 @@ __global__ void __launch_bounds__(kThreads, 1)
             qkv_head_store<0>(P, has_norm, rstd, sm.gate[0], cr, sr, rot, orow);
           }
         }
+      } else if constexpr (EPI == EPI_SWIGLU) {
+        // This thread's 64 output columns: gate from accumulator columns [oc, oc + 64), up from [128 + oc, ...); each
+        // value as silu_mul would have read it from memory (bf16(acc), then bf16(. + bias)), then the stand-alone
+        // kernel's own arithmetic and rounding (act_math.cuh).
+        const int oc = cb / 2;
+#pragma unroll 1
+        for (int c = oc; c < oc + TN / 2; c += 16) {
+          float g[16], u[16];
+          tc_ld16(taddr + unsigned(c), g);  // warp-wide: every lane takes part whether or not its row exists
+          tc_ld16(taddr + unsigned(TN + c), u);
+          if (!row_on || n0 + c >= a.N) continue;
+          uint4* orow = reinterpret_cast<uint4*>(a.y + row * a.N + n0 + c);
+#pragma unroll
+          for (int h8 = 0; h8 < 2; h8++) {
+            float gv[8], uv[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+              gv[i] = __bfloat162float(__float2bfloat16(g[8 * h8 + i]));
+              uv[i] = __bfloat162float(__float2bfloat16(u[8 * h8 + i]));
+              if (a.bias) gv[i] += sm.bias[c + 8 * h8 + i], uv[i] += sm.bias[TN + c + 8 * h8 + i];  // rounded by pack8
+            }
+            orow[h8] = act8<ACT_SILU_MUL>(pack8(gv), pack8(uv));
+          }
+        }
+        release();
       } else {
 #pragma unroll 1
         for (int c0 = cb; c0 < cb + BN / 2; c0 += 32) {
@@ -577,7 +621,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (a.bias) v += sm.bias[c0 + 8 * j + i];
                 o[i] = v;
               }
-              yr[j] = pack8(o);
+              uint4 packed = pack8(o);
+              if (a.act == 1) packed = act8<ACT_GELU_TANH>(packed, packed);
+              else if (a.act == 2) packed = act8<ACT_GELU_ERF>(packed, packed);
+              yr[j] = packed;
             }
           }
         }
@@ -666,8 +713,9 @@ int run_linear(const char* name, const mxk_bf16* A, const mxk_bf16* W, LinearArg
   // the time of the two 128 x 256 tiles it replaces (less operand traffic), but pairs quantise the work more coarsely:
   // the form that needs fewer (weighted) waves over the SMs runs.  `linear_ctas` = 1 / 2 forces a form.
   const int want = tune(TUNE_LINEAR_CTAS, 0);
-  const int64_t waves1 = ceil_div(ceil_div(a.M, BM) * ceil_div(a.N, BN), int64_t(sm_count()));
-  const int64_t waves2 = ceil_div(ceil_div(a.M, 2 * BM) * ceil_div(a.N, BN), int64_t(sm_count() / 2));
+  const int64_t col_tiles = ceil_div(a.N, kTileCols<EPI>);
+  const int64_t waves1 = ceil_div(ceil_div(a.M, BM) * col_tiles, int64_t(sm_count()));
+  const int64_t waves2 = ceil_div(ceil_div(a.M, 2 * BM) * col_tiles, int64_t(sm_count() / 2));
   const bool pair = a.M > BM && want != 1 && (want == 2 || 9 * waves2 <= 10 * waves1);
   // band height of the tile order: a wave of 74 pairs as 8 x 9 tiles of 256 x 256, of 148 CTAs as 16 x 9 tiles of 128 x 256
   a.group_m = tune(TUNE_LINEAR_GROUP_M, pair ? 8 : 16);
@@ -679,12 +727,13 @@ template <int EPI, int CTAS>
 int launch_linear(const char* name, const mxk_bf16* A, const mxk_bf16* W, const LinearArgs& a, cudaStream_t s) {
   CUtensorMap map_a, map_w;
   if (int rc = make_map(name, &map_a, A, a.M, a.K, BM)) return rc;
-  if (int rc = make_map(name, &map_w, W, a.N, a.K, BN / CTAS)) return rc;
+  // EPI_SWIGLU: W has 2 N rows (gate rows, then up rows) and is always fetched in boxes of 128 rows
+  if (int rc = make_map(name, &map_w, W, EPI == EPI_SWIGLU ? 2 * a.N : a.N, a.K, EPI == EPI_SWIGLU ? BN / 2 : BN / CTAS)) return rc;
   auto k = linear_epilogue_kernel<EPI, CTAS>;
   const size_t smem = sizeof(LinearSmem<CTAS>) + 1024;
   cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (e != cudaSuccess) return fail(MXK_ERR_CUDA, "%s: cudaFuncSetAttribute: %s", name, cudaGetErrorString(e));
-  const int64_t tiles = ceil_div(a.M, BM * CTAS) * ceil_div(a.N, BN);
+  const int64_t tiles = ceil_div(a.M, BM * CTAS) * ceil_div(a.N, kTileCols<EPI>);
   int64_t units = sm_count() / CTAS;  // CTAs, or pairs of CTAs
   if (units > tiles) units = tiles;
   cudaLaunchConfig_t cfg{};
@@ -719,6 +768,25 @@ int mxk_linear_bf16(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int
   LinearArgs a{};
   a.M = M, a.N = N, a.K = K, a.bias = bias, a.y = reinterpret_cast<bf16*>(y);
   return run_linear<EPI_STORE>("linear_bf16", A, W, a, as_stream(stream));
+}
+
+int mxk_linear_act(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t N, int64_t K, int act_mode,
+                   mxk_bf16* y, mxk_stream_t stream) {
+  if (act_mode != 0 && act_mode != 2)
+    return fail(MXK_ERR_INVALID_ARG, "linear_act: act_mode %d (0 gelu tanh, 2 gelu erf; silu_mul has mxk_linear_silu_mul)", act_mode);
+  if (M > 0 && !y) return fail(MXK_ERR_INVALID_ARG, "linear_act: null y");
+  LinearArgs a{};
+  a.M = M, a.N = N, a.K = K, a.bias = bias, a.y = reinterpret_cast<bf16*>(y), a.act = act_mode == 0 ? 1 : 2;
+  return run_linear<EPI_STORE>("linear_act", A, W, a, as_stream(stream));
+}
+
+int mxk_linear_silu_mul(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t F, int64_t K, mxk_bf16* out,
+                        mxk_stream_t stream) {
+  if (M > 0 && !out) return fail(MXK_ERR_INVALID_ARG, "linear_silu_mul: null out");
+  if (F >= (int64_t(1) << 30)) return fail(MXK_ERR_TOO_LARGE, "linear_silu_mul: F=%lld", (long long)F);
+  LinearArgs a{};
+  a.M = M, a.N = F, a.K = K, a.bias = bias, a.y = reinterpret_cast<bf16*>(out);
+  return run_linear<EPI_SWIGLU>("linear_silu_mul", A, W, a, as_stream(stream));
 }
 
 int mxk_linear_qkv_norm_rope(const mxk_bf16* A, const mxk_bf16* W, const float* bias, int64_t M, int64_t K, int H, int D,

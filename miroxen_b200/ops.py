@@ -29,7 +29,7 @@ __all__ = [
     "ACT_GELU_TANH", "ACT_SILU_MUL", "ACT_GELU_ERF", "layernorm_mod_quant_mxfp8", "rmsnorm_mod_quant_mxfp8", "gated_residual_norm_quant_mxfp8",
     "qwen_latent_encode", "qwen_latent_decode", "h3_latent_video", "h3_latent_audio",
     "bias_gelu_tanh_inplace", "bias_silu_mul", "gated_residual_bias",
-    "linear_bf16", "linear_gated_residual", "linear_qkv_norm_rope", "quantize_nvfp4_known_amax", "layernorm_mod_amax", "rmsnorm_mod_amax", "gated_residual_norm_amax", "act_amax",
+    "linear_bf16", "linear_act", "linear_silu_mul", "linear_gated_residual", "linear_qkv_norm_rope", "quantize_nvfp4_known_amax", "layernorm_mod_amax", "rmsnorm_mod_amax", "gated_residual_norm_amax", "act_amax",
     "norm_path_probe", "NORM_PATH_GENERIC", "NORM_PATH_VECTOR", "NORM_PATH_BULK",
 ]
 
@@ -304,6 +304,18 @@ def act_amax(act_mode: int, in_, rows: int, F: int, out, amax_out, bias=None, st
 def linear_bf16(A, W, bias, M, N, K, y, stream=None):
     """y bf16 [M, N] = A [M, K] @ W [N, K]^T (+ bias): the reference's linear() as one tensor-core kernel."""
     check(lib().mxk_linear_bf16(_p(A), _p(W), _p(bias), M, N, K, _p(y), _stream(stream)))
+
+
+def linear_act(A, W, bias, M, N, K, act_mode, y, stream=None):
+    """y bf16 [M, N] = act(A @ W^T (+ bias)), act_mode 0 GELU (tanh form) / 2 GELU (erf form): linear() and
+    gelu_tanh_inplace() in one kernel."""
+    check(lib().mxk_linear_act(_p(A), _p(W), _p(bias), M, N, K, int(act_mode), _p(y), _stream(stream)))
+
+
+def linear_silu_mul(A, W, bias, M, F, K, out, stream=None):
+    """out bf16 [M, F] = silu(g) * u with [g | u] = A @ W [2F, K]^T (+ bias [2F]): linear(gate_up) and silu_mul() in one
+    kernel; the [M, 2F] projection is never written."""
+    check(lib().mxk_linear_silu_mul(_p(A), _p(W), _p(bias), M, F, K, _p(out), _stream(stream)))
 
 
 def linear_gated_residual(A, W, bias, M, N, K, x, gate: RowMod, gate_tanh, stream=None):

@@ -161,6 +161,70 @@ def test_linear_qkv_norm_rope_equals_the_separate_calls(mx, M, Hh, K, rot, mode,
         assert float((outs[i].t != ref[i]).float().mean()) < 0.05, f"tensor {i}: too many elements differ"
 
 
+@pytest.mark.parametrize("M,N,K", [(1000, 3072, 512), (272, 12288, 3072), (130, 320, 200), (5, 64, 64)])
+@pytest.mark.parametrize("act_mode", [0, 2])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_linear_act_equals_linear_then_the_activation(mx, M, N, K, act_mode, with_bias):
+    """linear() + gelu in one kernel.  Against this library's own linear layer followed by the stand-alone activation
+    the result is the same bits (same tiles, same accumulation order, same activation arithmetic); against the library
+    GEMM + add_bias_bf16 + the activation it is within what one unit of the product and one of the biased sum can move
+    the output (|gelu'| <= 1.13) plus one unit of the output."""
+    A, W, bias = operands(M, N, K, M + N + K + act_mode)
+    b = bias if with_bias else None
+    act = mx.gelu_tanh_inplace if act_mode == 0 else mx.gelu_erf_inplace
+    same = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    mx.linear_bf16(A, W, b, M, N, K, same)
+    act(same, M * N)
+    prod = A @ W.T
+    y = prod.clone()
+    if b is not None:
+        mx.add_bias_bf16(y, b, M, N)
+    ref = y.clone()
+    act(ref, M * N)
+    out = H.Guarded(torch, (M, N), torch.bfloat16)
+    mx.linear_act(A, W, b, M, N, K, act_mode, out.t)
+    torch.cuda.synchronize()
+    out.check("linear_act y")
+    assert torch.equal(out.t, same)
+    floor = lambda t: torch.clamp(t.float().abs(), min=H.BF16_FLOOR)
+    tol = 2.0 ** -7 * (1.2 * (floor(prod) + floor(y)) + floor(ref))
+    err = (out.t.float() - ref.float()).abs()
+    assert bool((err <= tol).all()), f"{int((err > tol).sum())} of {err.numel()} beyond tolerance, worst {float((err - tol).max()):.3e}"
+    assert float((out.t != ref).float().mean()) < 0.03
+
+
+@pytest.mark.parametrize("M,F,K", [(1000, 1536, 512), (272, 13824, 1024), (300, 12288, 3072), (130, 160, 200), (5, 32, 64), (2176, 3456, 256)])
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_linear_silu_mul_equals_linear_then_silu_mul(mx, M, F, K, with_bias):
+    """The first MLP projection with silu_mul in its epilogue: W [2F, K] = gate rows then up rows.  Same bits as this
+    library's linear layer on the whole weight followed by the stand-alone silu_mul; within the propagated rounding of
+    the library GEMM + add_bias_bf16 + silu_mul (|silu'| <= 1.1, |silu(g)| <= |g|).  F = 13824, 3456 and 160 are not
+    whole numbers of 128-column tiles: their last tile's gate rows run into the up rows and must be ignored."""
+    A, W, bias = operands(M, 2 * F, K, M + F + K)
+    b = bias if with_bias else None
+    gu_same = torch.empty((M, 2 * F), dtype=torch.bfloat16, device="cuda")
+    mx.linear_bf16(A, W, b, M, 2 * F, K, gu_same)
+    same = torch.empty((M, F), dtype=torch.bfloat16, device="cuda")
+    mx.silu_mul(gu_same, M, F, same)
+    prod = A @ W.T
+    gu = prod.clone()
+    if b is not None:
+        mx.add_bias_bf16(gu, b, M, 2 * F)
+    ref = torch.empty((M, F), dtype=torch.bfloat16, device="cuda")
+    mx.silu_mul(gu, M, F, ref)
+    out = H.Guarded(torch, (M, F), torch.bfloat16)
+    mx.linear_silu_mul(A, W, b, M, F, K, out.t)
+    torch.cuda.synchronize()
+    out.check("linear_silu_mul out")
+    assert torch.equal(out.t, same)
+    floor = lambda t: torch.clamp(t.float().abs(), min=H.BF16_FLOOR)
+    g, u, pg, pu = gu[:, :F], gu[:, F:], prod[:, :F], prod[:, F:]
+    tol = 2.0 ** -7 * (1.1 * floor(u) * (floor(pg) + floor(g)) + floor(g) * (floor(pu) + floor(u)) + floor(ref))
+    err = (out.t.float() - ref.float()).abs()
+    assert bool((err <= tol).all()), f"{int((err > tol).sum())} of {err.numel()} beyond tolerance, worst {float((err - tol).max()):.3e}"
+    assert float((out.t != ref).float().mean()) < 0.05
+
+
 def test_linear_argument_checks(mx):
     L = mx.lib()
     from miroxen_b200._lib import RowMod
@@ -170,6 +234,10 @@ def test_linear_argument_checks(mx):
     assert L.mxk_linear_bf16(258, 256, None, 4, 64, 64, 256, None) == -1      # alignment
     assert L.mxk_linear_bf16(None, None, None, 0, 64, 64, None, None) == 0    # no rows
     assert L.mxk_linear_gated_residual(256, 256, None, 4, 64, 64, None, none, 0, None) == -1
+    assert L.mxk_linear_act(256, 256, None, 4, 64, 64, 1, 256, None) == -1      # silu_mul is not an in-place activation
+    assert L.mxk_linear_act(256, 256, None, 4, 64, 64, 0, None, None) == -1     # null y
+    assert L.mxk_linear_silu_mul(256, 256, None, 4, 48, 64, 256, None) == -1    # F % 32
+    assert L.mxk_linear_silu_mul(256, 256, None, 0, 64, 64, None, None) == 0    # no rows
     from miroxen_b200.ops import HeadTensor
     arr = (HeadTensor * 1)(HeadTensor(None, 0, 0, None, 256, 0, 0))
     assert L.mxk_linear_qkv_norm_rope(256, 256, None, 4, 64, 3, 128, arr, 1, 1e-6, None, None, None) == -1   # odd head count
