@@ -1326,6 +1326,10 @@ def main():
                             "speedup": round(msr / ms, 2)}
         rep.close()
 
+    if not args.no_extras and n_gpus == 1:
+        # the linear layers either side of the chain, with the chain's op in their epilogue (after job.close(): they need the memory)
+        line["next_rows"]["linear_epilogue"] = linear_rows(env, w, rows, min(K, 10))
+
     if not args.no_e2e:
         line["e2e"] = e2e_mxk(env, w, rows, row0, mods, args.chain, cos, sin, K, job_bytes)
 
