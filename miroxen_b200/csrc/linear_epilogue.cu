@@ -59,6 +59,7 @@ constexpr int kThreads = 64 + kEpiThreads;  // producer warp, MMA warp, epilogue
 constexpr int EPI_STORE = 0, EPI_RESIDUAL = 1, EPI_QKV = 2, EPI_SWIGLU = 3;
 // output columns one tile covers: EPI_SWIGLU spends half of the accumulator on the up half of the projection
 template <int EPI> constexpr int kTileCols = EPI == EPI_SWIGLU ? BN / 2 : BN;
+constexpr int kTurnRow = 80;   // bytes between rows of the residual epilogue's transposition tile
 constexpr int kHeadDim = 128;  // EPI_QKV: a 256-column tile is exactly two heads, one per half of the epilogue warps
 
 struct LinearArgs {
@@ -100,6 +101,9 @@ struct __align__(1024) LinearSmem {
   unsigned char b[kStages<CTAS>][kStageB<CTAS>];
   float bias[BN];           // the tile's bias slice (0 when absent)
   float gate[2][BN];        // act(gate) for prefix rows [0] and target rows [1] (1 when absent); EPI_QKV: [0][0..127] = norm weights
+  // EPI_RESIDUAL: per epilogue warp a 32 x 32 tile of bf16 y values, rows 80 bytes apart (64 of data: the padding keeps
+  // both the row-per-lane writes and the four-rows-per-instruction reads off each other's banks)
+  unsigned char turn[kEpiWarps][32 * kTurnRow];
   unsigned long long full[kStages<CTAS>], empty[kStages<CTAS>], acc_full[2], acc_empty[2], done;
   unsigned tmem_base;
 };
@@ -505,7 +509,6 @@ __global__ void __launch_bounds__(kThreads, 1)
       tc_fence_after();
       const int64_t row = int64_t(m0) + row_in_tile;
       const bool row_on = row < a.M;
-      const float* g = sm.gate[(EPI == EPI_RESIDUAL && row < a.gate.prefix_len) ? 0 : 1];
       const unsigned taddr = tmem_base + (unsigned(quarter * 32) << 16) + unsigned(buf * kAccCols);
       // this warp is done reading the accumulator (the pair's `acc_empty` is the first CTA's)
       auto release = [&]() {
@@ -592,25 +595,51 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int c0 = cb; c0 < cb + BN / 2; c0 += 32) {
           float acc[32];
           tc_ld32(taddr + unsigned(c0), acc);  // warp-wide: every lane takes part whether or not its row exists
-          if (!row_on || n0 + c0 >= a.N) continue;
+          if (n0 + c0 >= a.N) continue;  // the same for the whole warp (N is a multiple of 32)
           if (EPI == EPI_RESIDUAL) {
-            float4* xr = reinterpret_cast<float4*>(a.x + row * a.N + n0 + c0);
+            // A thread holds 32 columns of ONE row; updating x from there would touch 32 different 128-byte lines per
+            // warp instruction (measured: this epilogue then bounds the kernel, 152 us against 113 us with a bf16 store
+            // on 8704 x 3072 x 3072).  So the warp turns its 32 x 32 values through shared memory: each lane writes its
+            // row of y as bf16 (y IS a bf16 value: bf16(acc), then bf16(. + bias)), then the warp walks the tile four
+            // rows per instruction, eight lanes on the 128 contiguous bytes of x each row has in this chunk.
+            unsigned char* tile = sm.turn[warp - 2];
+            uint4* mine = reinterpret_cast<uint4*>(tile + lane * kTurnRow);
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+              float o[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) {
+                float v = __bfloat162float(__float2bfloat16(acc[8 * j + i]));  // the GEMM's bf16 output
+                if (a.bias) v += sm.bias[c0 + 8 * j + i];                      // add_bias_bf16: rounded by pack8
+                o[i] = v;
+              }
+              mine[j] = pack8(o);
+            }
+            __syncwarp();
+            const int sub = lane >> 3, c4 = (lane & 7) * 4;
+            const int64_t first = int64_t(m0) + quarter * 32 + sub;
             float4 xv[8];
 #pragma unroll
-            for (int j = 0; j < 8; j++) xv[j] = xr[j];
+            for (int j = 0; j < 8; j++) {
+              const int64_t r = first + 4 * j;
+              if (r < a.M) xv[j] = *reinterpret_cast<const float4*>(a.x + r * a.N + n0 + c0 + c4);
+            }
 #pragma unroll
             for (int j = 0; j < 8; j++) {
-              float y[4] = {acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]};
-              float o[4] = {xv[j].x, xv[j].y, xv[j].z, xv[j].w};
-#pragma unroll
-              for (int i = 0; i < 4; i++) {
-                float v = __bfloat162float(__float2bfloat16(y[i]));                               // the GEMM's bf16 output
-                if (a.bias) v = __bfloat162float(__float2bfloat16(v + sm.bias[c0 + 4 * j + i]));  // add_bias_bf16
-                o[i] = fmaf(v, g[c0 + 4 * j + i], o[i]);                                          // gated_residual
+              const int64_t r = first + 4 * j;
+              if (r < a.M) {
+                const uint2 yv = *reinterpret_cast<const uint2*>(tile + (sub + 4 * j) * kTurnRow + c4 * 2);
+                const float* gg = sm.gate[r < a.gate.prefix_len ? 0 : 1] + c0 + c4;
+                float4 o = xv[j];
+                o.x = fmaf(bf16_lo(yv.x), gg[0], o.x);  // gated_residual
+                o.y = fmaf(bf16_hi(yv.x), gg[1], o.y);
+                o.z = fmaf(bf16_lo(yv.y), gg[2], o.z);
+                o.w = fmaf(bf16_hi(yv.y), gg[3], o.w);
+                *reinterpret_cast<float4*>(a.x + r * a.N + n0 + c0 + c4) = o;
               }
-              xr[j] = make_float4(o[0], o[1], o[2], o[3]);
             }
-          } else {
+            __syncwarp();  // the tile is rewritten by the next chunk
+          } else if (row_on) {
             uint4* yr = reinterpret_cast<uint4*>(a.y + row * a.N + n0 + c0);
 #pragma unroll
             for (int j = 0; j < 4; j++) {
