@@ -137,9 +137,13 @@ template <int KIND>
 int run_gelu(const char* name, mxk_bf16* x, int64_t n, cudaStream_t s) {
   bf16* xb = reinterpret_cast<bf16*>(x);
   const int64_t body = n / 8 * 8;
-  // GELU leans on the special-function unit as much as on HBM, so it wants many consumer warps:
-  // 8 per CTA, 3 stages of 8 KB measured best on B200 (87 % of the copy peak at 214 MB in place).
-  if (tune(TUNE_ACT_PATH, 1) == 1 && aligned(x, 16) && body >= (int64_t(1) << 16)) {
+  // Default: the flat kernel, two vectors per thread, ONE tile per CTA and as many CTAs as that takes.  On B200 that
+  // beats both persistent forms - a resident wave of the same kernel walking the array grid-stride, and the bulk-copy
+  // pipeline below (8 consumer warps, 3 stages of 8 KB): 63.3 us against 79.5 and 74.5 us on 107 M elements in
+  // place.  The hardware scheduler hands out tiles as SMs free up, so there is no ramp and no tail, and 2048
+  // threads per SM with two loads each keep more bytes in flight than the pipeline's stages.  act_path = 1 keeps
+  // the pipeline selectable.
+  if (tune(TUNE_ACT_PATH, 2) == 1 && aligned(x, 16) && body >= (int64_t(1) << 16)) {
     const int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 8) * 1024;
     GeluPipeOp<KIND> op{reinterpret_cast<unsigned char*>(x), body * 2, chunk_bytes};
     if (int rc = run_stream_pipe(name, op, ceil_div(body * 2, chunk_bytes), chunk_bytes, s, 8, 3)) return rc;
@@ -149,7 +153,7 @@ int run_gelu(const char* name, mxk_bf16* x, int64_t n, cudaStream_t s) {
     }
     return MXK_OK;
   }
-  return run_flat(name, n, GeluOp<KIND>{xb}, s);
+  return run_flat(name, n, GeluOp<KIND>{xb}, s, 2, true);
 }
 
 constexpr int kActRowsInFlight = 4;
@@ -189,6 +193,31 @@ __global__ void __launch_bounds__(256)
         }
       }
     }
+  }
+}
+
+// The same op with ONE tile per CTA and as many CTAs as that takes: CTA (r, t) owns U x blockDim vectors of row r;
+// every thread has 2 U independent loads in flight and there is no loop.
+template <int U>
+__global__ void __launch_bounds__(256)
+    silu_mul_tile_kernel(const bf16* __restrict__ gu, int64_t F, int nvec, bf16* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t r = blockIdx.x;
+  const uint4* g = reinterpret_cast<const uint4*>(gu + r * 2 * F);
+  const uint4* up = g + nvec;
+  uint4* o = reinterpret_cast<uint4*>(out + r * F);
+  const int T = blockDim.x, base = int(blockIdx.y) * T * U + threadIdx.x;
+  uint4 a[U], b[U];
+#pragma unroll
+  for (int k = 0; k < U; k++) {
+    const int v = base + k * T;
+    if (v < nvec) a[k] = ld_stream(g + v), b[k] = ld_stream(up + v);
+  }
+#pragma unroll
+  for (int k = 0; k < U; k++) {
+    const int v = base + k * T;
+    if (v < nvec) st_stream(o + v, act8<ACT_SILU_MUL>(a[k], b[k]));
   }
 }
 
@@ -245,7 +274,23 @@ int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk
   cudaStream_t s = as_stream(stream);
   const bf16* in = reinterpret_cast<const bf16*>(gu);
   bf16* o = reinterpret_cast<bf16*>(out);
-  if (tune(TUNE_ACT_PATH, 1) == 1 && F % 8 == 0 && aligned(gu, 16) && aligned(out, 16) && rows * F >= (int64_t(1) << 16)) {
+  if (tune(TUNE_ACT_PATH, 3) == 3 && F % 8 == 0 && aligned(gu, 16) && aligned(out, 16) && rows < (int64_t(1) << 31)) {
+    // Default: one tile per CTA, as many CTAs as that takes (33272 x 13824: 413 us against 426 us for the bulk-copy
+    // pipeline below and 523 us for the register kernel on one resident wave; 33272 x 14336: 428 / 465 us).
+    // tile = threads x U vectors, chosen so that the row is a whole number of tiles if one of the shapes allows it
+    const int nvec = int(F / 8);
+    int threads = 256, unroll = 2, best = 1 << 30;
+    for (int u = 2; u >= 1; u--)
+      for (int t = 256; t >= 128; t -= 32) {
+        const int tile = t * u, waste = int(ceil_div(nvec, tile)) * tile - nvec;
+        if (waste < best) best = waste, threads = t, unroll = u;
+      }
+    const dim3 grid(unsigned(rows), unsigned(ceil_div(nvec, threads * unroll)));
+    if (unroll == 2) launch_pdl(silu_mul_tile_kernel<2>, grid, dim3(threads), 0, s, in, F, nvec, o);
+    else launch_pdl(silu_mul_tile_kernel<1>, grid, dim3(threads), 0, s, in, F, nvec, o);
+    return after_launch("silu_mul");
+  }
+  if (tune(TUNE_ACT_PATH, 3) == 1 && F % 8 == 0 && aligned(gu, 16) && aligned(out, 16) && rows * F >= (int64_t(1) << 16)) {
     const int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 4) * 1024;  // 4 warps, 2 stages of 2 x 4 KB measured best
     int cpr = int(ceil_div(F * 2, chunk_bytes));
     int chunk_elems = int(ceil_div(ceil_div(F, cpr), 8) * 8);

@@ -148,8 +148,9 @@ int run_add_bias(const char* name, T* y, const float* bias, int64_t rows, int64_
     const int rpc = 8;
     const unsigned gy = unsigned(ceil_div(dim / VEC, 256));
     const int64_t nchunks = ceil_div(rows, rpc);
-    int64_t gx = ceil_div(int64_t(sm_count()) * resident_ctas(add_bias_vec_kernel<T>, 256), gy);
-    if (gx > nchunks) gx = nchunks;
+    // one strip of rpc rows per CTA and as many CTAs as that takes: on B200 the streaming ops run faster handed out
+    // tile by tile by the hardware than as one resident wave walking the rows (see run_flat)
+    int64_t gx = nchunks < (int64_t(1) << 31) - 1 ? nchunks : (int64_t(1) << 31) - 1;
     if (gx < 1) gx = 1;
     add_bias_vec_kernel<T><<<dim3(unsigned(gx), gy), 256, 0, s>>>(y, bias, rows, int(dim), rpc);
   } else {

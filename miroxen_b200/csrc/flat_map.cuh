@@ -47,19 +47,25 @@ __global__ void __launch_bounds__(256) flat_scalar_kernel(int64_t n, Op op) {
     op.scalar(i);
 }
 
+// full_grid (the default): one tile of threads x unroll vectors per CTA and as many CTAs as that takes, so the
+// grid-stride loop runs once.  Measured on B200 with GELU over 107 M bf16 elements in place: 63.3 us, against 79.5 us for
+// one resident wave of the same kernel walking the array (full_grid = false, or ew_ctas_per_sm set): the hardware
+// scheduler hands out tiles as SMs free up, so there is no ramp, no tail and no imbalance between CTAs.
 template <class Op>
-inline int run_flat(const char* name, int64_t n, const Op& op, cudaStream_t s) {
+inline int run_flat(const char* name, int64_t n, const Op& op, cudaStream_t s, int default_unroll = 4, bool full_grid = true) {
   if (n <= 0) return MXK_OK;
   const int64_t cap = int64_t(sm_count()) * 16;
   if (op.vector_ok() && n >= Op::VEC) {
     const int threads = tune(TUNE_EW_THREADS, 256);
-    const int unroll = tune(TUNE_EW_UNROLL, 4);
+    const int unroll = tune(TUNE_EW_UNROLL, default_unroll);
     const int64_t nvec = n / Op::VEC;
     // a grid-stride loop over exactly one resident wave of CTAs (fewer when the array is small)
     auto go = [&](auto kern) {
       int64_t grid = ceil_div(nvec, int64_t(threads) * unroll);
-      const int64_t wave = int64_t(sm_count()) * tune(TUNE_EW_CTAS_PER_SM, resident_ctas(kern, threads));
+      const int per_sm = tune(TUNE_EW_CTAS_PER_SM, full_grid ? (1 << 20) : resident_ctas(kern, threads));
+      const int64_t wave = int64_t(sm_count()) * per_sm;
       if (grid > wave) grid = wave;
+      if (grid > (int64_t(1) << 31) - 1) grid = (int64_t(1) << 31) - 1;
       launch_pdl(kern, dim3(unsigned(grid)), dim3(threads), 0, s, n, op);
     };
     switch (unroll) {

@@ -47,14 +47,20 @@ inline void launch_norm_inst(const NormPlan& p, NormArgs a, bool tma, cudaStream
     int stages = tune(TUNE_NORM_STAGES, 0);
     // Two stages per CTA measured best on B200: small stages leave room for more resident CTAs,
     // and the CTAs of one SM together keep enough rows in flight.
-    if (stages <= 0) stages = 2;
-    if (stages < 2) stages = 2;
+    // The residual-only mode (MODE 2) does better still as ONE ROW PER CTA, more CTAs than are resident, each with a
+    // single stage: the hardware hands a new row to an SM the moment one finishes, there is no ramp or tail of a
+    // persistent loop, and nothing is reduced over the row that would want the next row's copy under way
+    // (8704 x 3072: 41.9 us against 46.5 us; 33272 x 5120: 242 us against 272 us).  The normalising modes lose
+    // with that grid (their per-CTA set-up - modulation vectors into registers - is paid per row then).
+    const bool row_per_cta = MODE == 2 && !QUANT && tune(TUNE_NORM_CTAS_PER_SM, 0) == 0;
+    if (stages <= 0) stages = row_per_cta ? 1 : 2;
+    if (stages < 2 && !row_per_cta) stages = 2;
     if (stages > kNormMaxStages) stages = kNormMaxStages;
     // the quantising form keeps the bf16 row in shared memory behind the stages
     const size_t smem = size_t(stages) * stage_bytes + (QUANT ? size_t(a.dim) * 2 : 0);
     // static shared memory (reduction scratch, barriers) counts against the 48 KB default too
     if (smem > 40 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    const unsigned grid = norm_grid(a, tune(TUNE_NORM_CTAS_PER_SM, resident_ctas(k, p.threads, smem)));
+    const unsigned grid = norm_grid(a, row_per_cta ? (1 << 20) : tune(TUNE_NORM_CTAS_PER_SM, resident_ctas(k, p.threads, smem)));
     a.row_step = tune(TUNE_NORM_INTERLEAVE, 1) == 1 ? int64_t(grid) : 1;
     launch_pdl(k, dim3(grid), dim3(p.threads), smem, s, a, stages, stage_bytes);
   } else if constexpr (!QUANT && !YBIAS) {  // the quantising and bias forms exist for the bulk-copy kernel only

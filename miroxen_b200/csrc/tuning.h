@@ -26,12 +26,12 @@ enum TuneKey {
   TUNE_STREAM_STAGES,      // its stages (2..8)
   TUNE_STREAM_CTAS_PER_SM,
   TUNE_STREAM_CHUNK_KB,    // bytes per source per chunk, in KB
-  TUNE_ACT_PATH,           // 1 bulk-copy streaming pipeline for GELU / SiLU-mul, 2 register kernels
+  TUNE_ACT_PATH,           // activations: 1 bulk-copy streaming pipeline, 2 register kernels on one resident wave (GELU: the flat kernel, one tile per CTA), 3 silu_mul with one tile per CTA; unset: GELU 2, silu_mul 3
   TUNE_PDL,                // 2 disables programmatic dependent launch (default: on)
   TUNE_NORM_INTERLEAVE,    // 1: CTA i of the bulk-copy row kernels takes rows i, i + grid, ...; 2: contiguous ranges
   TUNE_PIPE_INTERLEAVE,    // same choice for the head and streaming pipelines (1 interleaved, 2 contiguous)
   TUNE_QUANT_ROWS_PER_CTA, // rows per work item of the block-scale quantiser
-  TUNE_QUANT_PATH,         // 1 bulk-copy streaming pipeline for the quantiser, 2 register kernels
+  TUNE_QUANT_PATH,         // 1 bulk-copy streaming pipeline for the quantiser, 2 register kernels, 3 MXFP8 with one thread per scale block and one row per CTA (NVFP4: as 2); unset: MXFP8 3, NVFP4 1 (2 for small MXFP8-sized inputs)
   TUNE_ROPE_UNROLL,        // 1: head pipeline with the pass loop unrolled where the shape allows (default), 2: runtime loop
   TUNE_ROPE_WIDE,          // 1: sixteen channels per lane for D = 128, 2: eight channels per lane (default)
   TUNE_ROPE_WIDE_REGS,     // wide head kernel's register budget: 1 = 128 registers for CTAs of up to 128 threads (default), 2 = 96 everywhere

@@ -21,14 +21,15 @@ from test_cpu_blockscale import ELEM_ERR, GOLDEN, bits_to_f32, rel_rms  # noqa: 
 CASES = ref_blockscale_cases.cases()
 
 
-@pytest.fixture(scope="module", params=["bulk_copy", "registers"])
+@pytest.fixture(scope="module", params=["bulk_copy", "registers", "block_per_thread"])
 def mx(request):
-    """Every test runs with the bulk-copy streaming pipeline (the default) and with the register kernels."""
+    """Every test runs with the bulk-copy streaming pipeline, with the register kernels and with the MXFP8 kernel that
+    gives a thread a whole scale block (NVFP4 then takes the register kernels)."""
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     import miroxen_b200 as m
     m.lib()
-    m.set_tuning("quant_path", 1 if request.param == "bulk_copy" else 2)
+    m.set_tuning("quant_path", {"bulk_copy": 1, "registers": 2, "block_per_thread": 3}[request.param])
     yield m
     torch.cuda.synchronize()
     assert m.device_error() == 0, "a kernel's bounded wait ran out"

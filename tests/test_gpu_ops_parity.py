@@ -334,14 +334,22 @@ def test_qkv_norm_rope_equals_three_calls(mx, S, Hh, rot, mode):
         assert torch.equal(a.view(torch.int16), b.view(torch.int16))
 
 
-@pytest.mark.parametrize("rows,F", [(9, 12288), (33, 13824), (5, 100), (3, 99), (130, 14336)])
-def test_silu_mul(mx, rows, F):
+ACT_PATHS = [0, 1, 2]  # the default (one tile per CTA), the bulk-copy pipeline, the register kernels on one resident wave
+
+
+@pytest.mark.parametrize("act_path", ACT_PATHS)
+@pytest.mark.parametrize("rows,F", [(9, 12288), (33, 13824), (5, 100), (3, 99), (130, 14336), (300, 1736)])
+def test_silu_mul(mx, rows, F, act_path):
     g = H.rng(rows + F)
     gu = H.normal_bf16(g, (rows, 2 * F), 2.0)
     ref = orc.silu_mul(gu, F)
     out = H.Guarded(torch, (rows, F), torch.bfloat16)
-    mx.silu_mul(H.to_dev(torch, gu), rows, F, out.t)
-    torch.cuda.synchronize()
+    mx.set_tuning("act_path", act_path)
+    try:
+        mx.silu_mul(H.to_dev(torch, gu), rows, F, out.t)
+        torch.cuda.synchronize()
+    finally:
+        mx.set_tuning("act_path", 0)
     out.check("silu_mul")
     H.assert_bf16_close(H.bits(out.t), ref, "silu_mul")
 
@@ -352,15 +360,20 @@ def _all_bf16_values():
     return bits_[np.isfinite(v)]
 
 
+@pytest.mark.parametrize("act_path", ACT_PATHS)
 @pytest.mark.parametrize("kind", ["tanh", "erf"])
-def test_gelu_every_bf16_value(mx, kind):
+def test_gelu_every_bf16_value(mx, kind, act_path):
     """Both GELUs on every finite bf16 input (the whole domain), plus a ragged random length."""
     g = H.rng(11)
     for x in (_all_bf16_values(), H.normal_bf16(g, 1000003, 2.5)):
         ref = (orc.gelu_tanh_inplace if kind == "tanh" else orc.gelu_erf_inplace)(x.copy())
         xd = H.Guarded(torch, (x.size,), torch.bfloat16, fill=H.to_dev(torch, x))
-        (mx.gelu_tanh_inplace if kind == "tanh" else mx.gelu_erf_inplace)(xd.t, x.size)
-        torch.cuda.synchronize()
+        mx.set_tuning("act_path", act_path)
+        try:
+            (mx.gelu_tanh_inplace if kind == "tanh" else mx.gelu_erf_inplace)(xd.t, x.size)
+            torch.cuda.synchronize()
+        finally:
+            mx.set_tuning("act_path", 0)
         xd.check("gelu")
         H.assert_bf16_close(H.bits(xd.t), ref, f"gelu_{kind}")
 
