@@ -14,11 +14,12 @@
 // an MXFP8 block (one shuffle joins the two halves' maxima).  It stores 128 (64) bits of codes, so a
 // warp's stores are one contiguous segment.  The arithmetic is packed where the result is the same
 // bits: |.|-maxima on bf16 pairs (max.xorsign.abs.bf16x2; a maximum picks one of its inputs), scaling
-// on fp32 pairs (mul.rn.f32x2), conversion two elements per instruction.  Default path: the bulk-copy
-// streaming pipeline (stream_pipe.cuh) - a producer warp lands row pieces of up to 8 KB in shared
-// memory, consumer warps quantise from there; NVFP4's tensor maximum is a first pass through the same
-// pipeline.  quant_path = 2 selects plain register kernels (also taken when a row piece cannot be cut
-// on a block boundary).
+// on fp32 pairs (mul.rn.f32x2), conversion two elements per instruction.  That layout serves the bulk-copy
+// streaming pipeline (stream_pipe.cuh; NVFP4's default, quant_path = 1) - a producer warp lands row pieces of up
+// to 32 KB in shared memory, consumer warps quantise from there; NVFP4's tensor maximum is a first pass through
+// the same pipeline - and the register kernels on one resident wave (quant_path = 2, also taken when a row piece
+// cannot be cut on a block boundary).  MXFP8's default is quant_mxfp8_block_kernel: a thread owns a whole
+// 32-element block, a CTA one row, and the grid is as many CTAs as rows.
 //
 // Three steps are computed differently from the reference but give the same bits:
 //  - the ue8m0 exponent comes from the bits of the block maximum instead of frexpf(bmax / 448): with

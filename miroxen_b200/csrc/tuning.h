@@ -7,7 +7,7 @@ namespace mxk {
 
 enum TuneKey {
   TUNE_NORM_THREADS = 0,   // preferred CTA size of the row-norm kernels
-  TUNE_NORM_CTAS_PER_SM,   // CTAs per SM the row-norm grid is sized for
+  TUNE_NORM_CTAS_PER_SM,   // CTAs per SM the row-norm grid is sized for (unset: one resident wave; the residual-only mode: one row per CTA)
   TUNE_ROPE_THREADS,       // CTA size of head_norm_rope
   TUNE_ROPE_CTAS_PER_SM,
   TUNE_RES_ROWS_PER_CTA,   // rows each gated_residual CTA walks
@@ -19,7 +19,7 @@ enum TuneKey {
   TUNE_NORM_STAGES,        // rows in flight per CTA of the bulk-copy kernel (2..8)
   TUNE_ROPE_PATH,          // 1 bulk-copy (TMA) pipelined head kernel, 2 register head kernel
   TUNE_ROPE_STAGES,        // tokens in flight per CTA of the bulk-copy head kernel (2..8)
-  TUNE_EW_CTAS_PER_SM,     // CTAs per SM the flat elementwise grid is sized for
+  TUNE_EW_CTAS_PER_SM,     // CTAs per SM the flat elementwise grid is capped at (unset: no cap, one tile per CTA)
   TUNE_RES_PATH,           // 1 bulk-copy pipelined gated_residual, 2 column-strip register kernel
   TUNE_ROPE_TOKENS,        // tokens per stage of the bulk-copy head kernel (1..16)
   TUNE_STREAM_WARPS,       // consumer warps per CTA of the streaming pipeline
@@ -31,7 +31,7 @@ enum TuneKey {
   TUNE_NORM_INTERLEAVE,    // 1: CTA i of the bulk-copy row kernels takes rows i, i + grid, ...; 2: contiguous ranges
   TUNE_PIPE_INTERLEAVE,    // same choice for the head and streaming pipelines (1 interleaved, 2 contiguous)
   TUNE_QUANT_ROWS_PER_CTA, // rows per work item of the block-scale quantiser
-  TUNE_QUANT_PATH,         // 1 bulk-copy streaming pipeline for the quantiser, 2 register kernels, 3 MXFP8 with one thread per scale block and one row per CTA (NVFP4: as 2); unset: MXFP8 3, NVFP4 1 (2 for small MXFP8-sized inputs)
+  TUNE_QUANT_PATH,         // 1 bulk-copy streaming pipeline, 2 register kernels, 3 MXFP8 with a thread per scale block and a row per CTA (NVFP4 as 2); unset: MXFP8 3, NVFP4 1
   TUNE_ROPE_UNROLL,        // 1: head pipeline with the pass loop unrolled where the shape allows (default), 2: runtime loop
   TUNE_ROPE_WIDE,          // 1: sixteen channels per lane for D = 128, 2: eight channels per lane (default)
   TUNE_ROPE_WIDE_REGS,     // wide head kernel's register budget: 1 = 128 registers for CTAs of up to 128 threads (default), 2 = 96 everywhere
