@@ -52,7 +52,9 @@ inline void launch_norm_inst(const NormPlan& p, NormArgs a, bool tma, cudaStream
     // persistent loop, and nothing is reduced over the row that would want the next row's copy under way
     // (8704 x 3072: 41.9 us against 46.5 us; 33272 x 5120: 242 us against 272 us).  The normalising modes lose
     // with that grid (their per-CTA set-up - modulation vectors into registers - is paid per row then).
-    const bool row_per_cta = MODE == 2 && !QUANT && tune(TUNE_NORM_CTAS_PER_SM, 0) == 0;
+    // (the form that also adds a bias reads a second per-column vector per CTA: one row per CTA paid for that at
+    // d = 5120 - 298 us against 269 us - so it keeps the resident wave)
+    const bool row_per_cta = MODE == 2 && !QUANT && !YBIAS && tune(TUNE_NORM_CTAS_PER_SM, 0) == 0;
     if (stages <= 0) stages = row_per_cta ? 1 : 2;
     if (stages < 2 && !row_per_cta) stages = 2;
     if (stages > kNormMaxStages) stages = kNormMaxStages;
