@@ -230,7 +230,9 @@ struct LaneRole {
 // All `ntok` tokens of one tensor inside a stage.  NORM: per-head RMSNorm; MODE as MXK_ROPE_*.
 // src points at the thread's 8 channels of token 0 (pass 0) in shared memory, dst at the same
 // place of the output; cr / sr at the lane's first table entry of token 0.
-template <int LPH, bool NORM, int MODE, int PASSES>
+// PRELOAD (global-memory source, PASSES > 0): every pass's vector of a token is loaded before the first is used - the
+// compiler cannot move a later pass's load above an earlier pass's store on its own (it cannot rule out that they alias).
+template <int LPH, bool NORM, int MODE, int PASSES, bool PRELOAD = false>
 __device__ __forceinline__ void rope_tokens(const unsigned char* src, int tok_bytes, const float* cr, const float* sr,
                                             int half, int ntok, unsigned char* dst, int out_tok_bytes,
                                             const float* w_row, float inv_d, float eps, int passes, int heads_per_pass,
@@ -258,13 +260,20 @@ __device__ __forceinline__ void rope_tokens(const unsigned char* src, int tok_by
     }
     const unsigned char* sp = src;
     unsigned char* dp = dst;
+    uint4 pre[PRELOAD ? PASSES : 1];
+    if (PRELOAD) {
+#pragma unroll
+      for (int pass = 0; pass < (PRELOAD ? PASSES : 0); pass++)
+        pre[pass] = ld_stream(reinterpret_cast<const uint4*>(src + pass * r.pass_off));
+    }
     // PASSES > 0: the pass count is a compile-time constant and every pass is full (H = PASSES *
     // heads_per_pass), so the loop unrolls into independent chains and needs no predicate.
 #pragma unroll
     for (int pass = 0; pass < (PASSES > 0 ? PASSES : passes); pass++) {
       const bool on = PASSES > 0 || r.hp < (pass + 1 < passes ? heads_per_pass : H - pass * heads_per_pass);
       uint4 raw = make_uint4(0u, 0u, 0u, 0u);
-      if (on) raw = *reinterpret_cast<const uint4*>(sp);
+      if (PRELOAD) raw = pre[pass];
+      else if (on) raw = *reinterpret_cast<const uint4*>(sp);
       float v[8];
       unpack8(raw, v);
       if (NORM) {
@@ -636,6 +645,62 @@ __global__ void __launch_bounds__(!WIDE ? 544 : MINB == 1 ? 128 : 160, MINB == 0
   }
 }
 
+// The consumers' arithmetic of the pipeline straight from global memory, ONE group of tokens per CTA and as many CTAs
+// as that takes (rope_path = 3): thread layout, passes and roles as in head_rope_pipe_kernel, no stages, no producer.
+template <int LPH, int PASSES>
+__global__ void __launch_bounds__(256) head_rope_tile_kernel(const RopeArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int half = a.rot >> 1;
+  const bool rope = a.mode != MXK_ROPE_NONE && a.rot > 0;
+  const int l = tid % LPH;
+  LaneRole r;
+  r.hp = tid / LPH;
+  r.thread_off = (r.hp * a.D + 8 * l) * 2;
+  r.pass_off = a.heads_per_pass * a.D * 2;
+  r.rotates = rope && 8 * l < a.rot;
+  r.tab_idx = 0, r.partner = lane, r.first = true;
+  if (r.rotates) {
+    if (a.mode == MXK_ROPE_INTERLEAVED) {
+      r.tab_idx = 4 * l;
+    } else {
+      const int hl = half >> 3;
+      r.first = l < hl;
+      r.tab_idx = 8 * (r.first ? l : l - hl);
+      r.partner = (lane & ~(LPH - 1)) + (r.first ? l + hl : l - hl);
+    }
+  }
+  const float inv_d = 1.f / float(a.D);
+  const int tok_out_bytes = a.H * a.D * 2;
+  const int64_t s0 = int64_t(blockIdx.x) * a.tpc;
+  const int ntok = int(a.S - s0 < a.tpc ? a.S - s0 : a.tpc);
+  const float* cr = rope ? a.cos + s0 * half + r.tab_idx : nullptr;
+  const float* sr = rope ? a.sin + s0 * half + r.tab_idx : nullptr;
+#pragma unroll 1
+  for (int ti = 0; ti < a.n_tensors; ti++) {
+    const MxkHeadTensor& t = a.t[ti];
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(t.in + s0 * t.in_stride + t.col0) + r.thread_off;
+    unsigned char* dst = reinterpret_cast<unsigned char*>(t.out) + s0 * tok_out_bytes + r.thread_off;
+    const int tok_bytes = int(t.in_stride * 2);
+    const bool t_rope = t.mode != MXK_ROPE_NONE && t.rot > 0;
+    const float* wr = t.norm_w ? t.norm_w + 8 * l : nullptr;
+#define MXK_ROPE_CALL(NORM, MODE)                                                                                        \
+  rope_tokens<LPH, NORM, MODE, PASSES, (PASSES > 0)>(src, tok_bytes, cr, sr, half, ntok, dst, tok_out_bytes, wr, inv_d, a.eps, \
+                                                     a.passes, a.heads_per_pass, a.H, r)
+    if (t.norm_w) {
+      if (!t_rope) MXK_ROPE_CALL(true, MXK_ROPE_NONE);
+      else if (a.mode == MXK_ROPE_INTERLEAVED) MXK_ROPE_CALL(true, MXK_ROPE_INTERLEAVED);
+      else MXK_ROPE_CALL(true, MXK_ROPE_HALF);
+    } else {
+      if (!t_rope) MXK_ROPE_CALL(false, MXK_ROPE_NONE);
+      else if (a.mode == MXK_ROPE_INTERLEAVED) MXK_ROPE_CALL(false, MXK_ROPE_INTERLEAVED);
+      else MXK_ROPE_CALL(false, MXK_ROPE_HALF);
+    }
+#undef MXK_ROPE_CALL
+  }
+}
+
 // Any even D <= 256, any rot, any alignment: one warp per (token, head), the head's values pass
 // through shared memory for the partner exchange.
 __global__ void __launch_bounds__(256) head_rope_generic_kernel(const RopeArgs a) {
@@ -801,6 +866,16 @@ template <bool SCATTER>
 int launch_register(const char* name, RopeArgs a, cudaStream_t stream);
 int launch_generic(const char* name, RopeArgs a, cudaStream_t stream);
 
+template <int PASSES>
+int launch_tile(const char* name, RopeArgs a, cudaStream_t stream) {
+  int tpc = tune(TUNE_ROPE_TOKENS, 1);
+  if (tpc < 1) tpc = 1;
+  a.tpc = tpc;
+  const int threads = 16 * a.heads_per_pass;
+  launch_pdl(head_rope_tile_kernel<16, PASSES>, dim3(unsigned(ceil_div(a.S, tpc))), dim3(threads), 0, stream, a);
+  return after_launch(name);
+}
+
 int run(const char* name, RopeArgs a, cudaStream_t stream) {
   // D = 128 (every model shape): sixteen channels per lane, eight lanes per head
   // (opt-in, rope_wide = 1: measured within 2 % of the eight-channel mapping on every model shape, so the mapping with
@@ -826,6 +901,20 @@ int run(const char* name, RopeArgs a, cudaStream_t stream) {
 #undef MXK_WIDE_CASE
     }
     if (8 * a.heads_per_pass + 32 <= 160) return launch_pipe<8, 0, true>(name, a, stream);
+  }
+  if (a.D == 128 && fast_ok(a) && tune(TUNE_ROPE_PATH, 1) == 3 && a.S < (int64_t(1) << 31) && pipe_plan(a) &&
+      16 * a.heads_per_pass <= 256 && (16 * a.heads_per_pass) % 32 == 0) {
+    const bool exact = a.H == a.passes * a.heads_per_pass;
+    if (exact) {
+      switch (a.passes) {
+        case 3: return launch_tile<3>(name, a, stream);
+        case 4: return launch_tile<4>(name, a, stream);
+        case 5: return launch_tile<5>(name, a, stream);
+        case 7: return launch_tile<7>(name, a, stream);
+        default: break;
+      }
+    }
+    return launch_tile<0>(name, a, stream);
   }
   if (fast_ok(a) && tune(TUNE_ROPE_PATH, 1) == 1 && a.S >= 2 && pipe_plan(a)) {
     switch (a.D / 8) {

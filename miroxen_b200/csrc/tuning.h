@@ -17,7 +17,7 @@ enum TuneKey {
   TUNE_ACT_ROWS_PER_CTA,   // rows each silu_mul CTA walks
   TUNE_NORM_PATH,          // 1 bulk-copy (TMA) pipelined row kernel, 2 register-prefetch row kernel
   TUNE_NORM_STAGES,        // rows in flight per CTA of the bulk-copy kernel (2..8)
-  TUNE_ROPE_PATH,          // 1 bulk-copy (TMA) pipelined head kernel, 2 register head kernel
+  TUNE_ROPE_PATH,          // 1 bulk-copy (TMA) pipelined head kernel (default), 2 register head kernel, 3 D = 128: one group of tokens per CTA straight from global memory
   TUNE_ROPE_STAGES,        // tokens in flight per CTA of the bulk-copy head kernel (2..8)
   TUNE_EW_CTAS_PER_SM,     // CTAs per SM the flat elementwise grid is capped at (unset: no cap, one tile per CTA)
   TUNE_RES_PATH,           // 1 bulk-copy pipelined gated_residual, 2 column-strip register kernel

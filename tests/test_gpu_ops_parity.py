@@ -12,18 +12,19 @@ torch = pytest.importorskip("torch")
 pytestmark = pytest.mark.gpu
 
 
-@pytest.fixture(scope="module", params=["bulk_copy", "registers", "bulk_copy_wide_heads"])
+@pytest.fixture(scope="module", params=["bulk_copy", "registers", "bulk_copy_wide_heads", "tile_heads"])
 def mx(request):
-    """Every test runs three times: with the bulk-copy (TMA) pipelined row / head kernels, which are the
-    default; with the register-prefetch kernels that serve the shapes the bulk copies cannot; and with the
-    head pipeline's sixteen-channels-per-lane mapping (D = 128 shapes; the others fall to the default)."""
+    """Every test runs four times: with the bulk-copy (TMA) pipelined row / head kernels, which are the
+    default; with the register-prefetch kernels that serve the shapes the bulk copies cannot; with the
+    head pipeline's sixteen-channels-per-lane mapping (D = 128 shapes; the others fall to the default); and with
+    the head kernel that reads straight from global memory, one group of tokens per CTA (D = 128 shapes)."""
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     import miroxen_b200 as m
     m.lib()  # raises if libmxk.so is missing - there is no fallback
     path = 2 if request.param == "registers" else 1
     m.set_tuning("norm_path", path)
-    m.set_tuning("rope_path", path)
+    m.set_tuning("rope_path", 3 if request.param == "tile_heads" else path)
     m.set_tuning("rope_wide", 1 if request.param == "bulk_copy_wide_heads" else 0)
     yield m
     torch.cuda.synchronize()
