@@ -274,7 +274,8 @@ int mxk_silu_mul(const mxk_bf16* gu, int64_t rows, int64_t F, mxk_bf16* out, mxk
   cudaStream_t s = as_stream(stream);
   const bf16* in = reinterpret_cast<const bf16*>(gu);
   bf16* o = reinterpret_cast<bf16*>(out);
-  if (tune(TUNE_ACT_PATH, 3) == 3 && F % 8 == 0 && aligned(gu, 16) && aligned(out, 16) && rows < (int64_t(1) << 31)) {
+  if (tune(TUNE_ACT_PATH, 3) == 3 && F % 8 == 0 && aligned(gu, 16) && aligned(out, 16) && rows < (int64_t(1) << 31) &&
+      F / 8 <= 65535 * 128) {  // grid.y holds the tiles of a row
     // Default: one tile per CTA, as many CTAs as that takes (33272 x 13824: 413 us against 426 us for the bulk-copy
     // pipeline below and 523 us for the register kernel on one resident wave; 33272 x 14336: 428 / 465 us).
     // tile = threads x U vectors, chosen so that the row is a whole number of tiles if one of the shapes allows it
