@@ -298,6 +298,60 @@ __global__ void __launch_bounds__(256) quant_mxfp8_block_kernel(const bf16* __re
   }
 }
 
+// NVFP4 in the same form (quant_path = 3): a thread owns two 16-element blocks (four 128-bit loads, one 128-bit store of
+// codes, the two scale bytes as one 16-bit store: block pairs sit next to each other in the interleaved scale layout).
+__global__ void __launch_bounds__(256) quant_nvfp4_block_kernel(const bf16* __restrict__ x, int64_t ldx, int64_t rows, int K,
+                                                                 uint8_t* __restrict__ q, uint8_t* __restrict__ sf,
+                                                                 const float* amax) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const Fp4Scale fs = fp4_scale(amax);
+  const int np = K / 32, nkb_pad = int(pad_to(K / 16, 4));
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const uint4* row = reinterpret_cast<const uint4*>(x + r * ldx);
+    uint4* qrow = reinterpret_cast<uint4*>(q + r * (K / 2));
+    uint8_t* sfr = sf + sf_row_offset(uint64_t(r), nkb_pad);
+    for (int p = threadIdx.x; p < np; p += blockDim.x) {
+      const uint4 lo[2] = {row[4 * p], row[4 * p + 1]};
+      const uint4 hi[2] = {row[4 * p + 2], row[4 * p + 3]};
+      uint4 o0, o1;
+      const uint8_t s0 = quant16<2>(lo, block_absmax<2>(lo), fs, o0);
+      const uint8_t s1 = quant16<2>(hi, block_absmax<2>(hi), fs, o1);
+      qrow[p] = make_uint4(o0.x, o0.y, o1.x, o1.y);
+      *reinterpret_cast<uint16_t*>(sfr + sf_col_offset(2 * p)) = uint16_t(s0) | uint16_t(uint16_t(s1) << 8);
+    }
+  }
+}
+
+// The tensor maximum in the same spirit: four rows per CTA, as many CTAs as that takes, ONE atomic per CTA.
+__global__ void __launch_bounds__(256) amax_rows_kernel(const bf16* __restrict__ x, int64_t ldx, int64_t rows, int nvec, float* out) {
+  constexpr int U = kRowsInFlight;
+  __shared__ float part[8];
+  pdl_launch_dependents();
+  pdl_wait();
+  uint32_t m = 0u;
+  for (int64_t r = int64_t(blockIdx.x) * U; r < rows; r += int64_t(gridDim.x) * U) {
+    for (int j = threadIdx.x; j < nvec; j += blockDim.x) {
+      uint4 raw[U];
+#pragma unroll
+      for (int u = 0; u < U; u++)
+        raw[u] = r + u < rows ? reinterpret_cast<const uint4*>(x + (r + u) * ldx)[j] : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+      for (int u = 0; u < U; u++) m = absmax_bf16x2(m, absmax_bf16x2(raw[u]));
+    }
+  }
+  float v = bf16x2_max_to_float(m);
+#pragma unroll
+  for (int o = 16; o; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < int(blockDim.x >> 5); w++) v = fmaxf(v, part[w]);
+    // non-negative floats order like their bit patterns (src/kernels/blockscale.cu:68)
+    if (v > 0.f) atomicMax(reinterpret_cast<int*>(out), __float_as_int(v));
+  }
+}
+
 // Activation + MXFP8 in the same form (thread per scale block, row per CTA): the 32 activation inputs of a block (and
 // the 32 of the up half for silu_mul) are loaded, an optional bias is added and rounded to bf16 as add_bias_bf16 leaves
 // it, the activation is applied and rounded to bf16 exactly as the stand-alone kernel rounds it, and the block is
@@ -465,6 +519,25 @@ static int quantize_impl(int mode, const mxk_bf16* x, int64_t ldx, int64_t rows,
     }
     if (nb < 128) threads = int(ceil_div(nb, 32) * 32);
     launch_pdl(quant_mxfp8_block_kernel, dim3(unsigned(rows)), dim3(threads), 0, s, xb, ldx, rows, int(K), static_cast<uint8_t*>(q), sf);
+    return after_launch("quantize_blockscaled");
+  }
+  if (fp4 && tune(TUNE_QUANT_PATH, 1) == 3 && rows < (int64_t(1) << 31)) {
+    // NVFP4 with a thread per pair of scale blocks and a row per CTA; the maximum pass with four rows per CTA.  Opt-in:
+    // within a few per cent of the pipeline either way (8704 x 12288: 83.7 against 85.6 us; 33272 x 5120: 137.7 against
+    // 134.1 us) - the two passes over the input bound this mode, not the form of either kernel.
+    if (!amax_known) {
+      launch_pdl(amax_rows_kernel, dim3(unsigned(ceil_div(rows, kRowsInFlight))), dim3(256), 0, s, xb, ldx, rows, nvec, amax);
+      if (int rc = after_launch("quantize_blockscaled (amax)")) return rc;
+    }
+    const int np = int(K / 32);
+    int threads = 128, best = 1 << 30;
+    for (int t = 128; t <= 256; t += 32) {
+      const int waste = int(ceil_div(np, t)) * t - np;
+      if (waste < best) best = waste, threads = t;
+    }
+    if (np < 128) threads = int(ceil_div(np, 32) * 32);
+    launch_pdl(quant_nvfp4_block_kernel, dim3(unsigned(rows)), dim3(threads), 0, s, xb, ldx, rows, int(K), static_cast<uint8_t*>(q), sf,
+               static_cast<const float*>(amax));
     return after_launch("quantize_blockscaled");
   }
   int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, fp4 ? 32 : 16) * 1024;

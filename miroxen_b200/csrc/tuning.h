@@ -31,7 +31,7 @@ enum TuneKey {
   TUNE_NORM_INTERLEAVE,    // 1: CTA i of the bulk-copy row kernels takes rows i, i + grid, ...; 2: contiguous ranges
   TUNE_PIPE_INTERLEAVE,    // same choice for the head and streaming pipelines (1 interleaved, 2 contiguous)
   TUNE_QUANT_ROWS_PER_CTA, // rows per work item of the block-scale quantiser
-  TUNE_QUANT_PATH,         // 1 bulk-copy streaming pipeline, 2 register kernels, 3 MXFP8 with a thread per scale block and a row per CTA (NVFP4 as 2); unset: MXFP8 3, NVFP4 1
+  TUNE_QUANT_PATH,         // 1 bulk-copy streaming pipeline, 2 register kernels on one resident wave, 3 a thread per scale block (NVFP4: per pair) and a row per CTA; unset: MXFP8 3, NVFP4 1
   TUNE_ROPE_UNROLL,        // 1: head pipeline with the pass loop unrolled where the shape allows (default), 2: runtime loop
   TUNE_ROPE_WIDE,          // 1: sixteen channels per lane for D = 128, 2: eight channels per lane (default)
   TUNE_ROPE_WIDE_REGS,     // wide head kernel's register budget: 1 = 128 registers for CTAs of up to 128 threads (default), 2 = 96 everywhere

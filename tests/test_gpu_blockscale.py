@@ -23,8 +23,8 @@ CASES = ref_blockscale_cases.cases()
 
 @pytest.fixture(scope="module", params=["bulk_copy", "registers", "block_per_thread"])
 def mx(request):
-    """Every test runs with the bulk-copy streaming pipeline, with the register kernels and with the MXFP8 kernel that
-    gives a thread a whole scale block (NVFP4 then takes the register kernels)."""
+    """Every test runs with the bulk-copy streaming pipeline, with the register kernels and with the kernels that give
+    a thread a whole MXFP8 scale block (or a pair of NVFP4 blocks) and a CTA one row."""
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     import miroxen_b200 as m
