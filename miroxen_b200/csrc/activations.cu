@@ -112,6 +112,41 @@ struct BiasActPipeOp : RowPieces {
   }
 };
 
+// bias (optional) + activation with ONE tile per CTA and as many CTAs as that takes: CTA (r, t) owns U x blockDim
+// vectors of row r; in [rows, F] (or [rows, 2F] for silu_mul: gate then up), out [rows, F] (may be `in` for the GELUs).
+template <int ACT, int U>
+__global__ void __launch_bounds__(256)
+    bias_act_tile_kernel(const bf16* in, const float* __restrict__ bias, int64_t F, int nvec, bf16* out) {
+  constexpr bool TWO = ACT == ACT_SILU_MUL;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int64_t r = blockIdx.x;
+  const uint4* g = reinterpret_cast<const uint4*>(in + r * F * (TWO ? 2 : 1));
+  const uint4* up = g + nvec;
+  uint4* o = reinterpret_cast<uint4*>(out + r * F);
+  const int T = blockDim.x, base = int(blockIdx.y) * T * U + threadIdx.x;
+  uint4 a[U], b[U];
+#pragma unroll
+  for (int k = 0; k < U; k++) {
+    const int v = base + k * T;
+    if (v < nvec) {
+      a[k] = ld_stream(g + v);
+      b[k] = TWO ? ld_stream(up + v) : a[k];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < U; k++) {
+    const int v = base + k * T;
+    if (v < nvec) {
+      if (bias) {
+        a[k] = add_bias8(a[k], bias + 8 * v);
+        if (TWO) b[k] = add_bias8(b[k], bias + F + 8 * v);
+      }
+      st_stream(o + v, act8<ACT>(a[k], TWO ? b[k] : a[k]));
+    }
+  }
+}
+
 template <int ACT>
 int run_bias_act(const char* name, const mxk_bf16* in, const float* bias, int64_t rows, int64_t F, mxk_bf16* out,
                  cudaStream_t s, float* amax = nullptr) {
@@ -119,6 +154,23 @@ int run_bias_act(const char* name, const mxk_bf16* in, const float* bias, int64_
   if (F <= 0 || F % 8 != 0 || F > (int64_t(1) << 24) || !aligned(in, 16) || !aligned(out, 16) || !aligned(bias, 16))
     return fail(MXK_ERR_INVALID_ARG, "%s: needs F %% 8 == 0, F <= 2^24 and 16-byte aligned buffers; otherwise call "
                 "the separate ops", name);
+  if (!amax && tune(TUNE_ACT_PATH, 3) != 1 && rows < (int64_t(1) << 31)) {
+    // default when no tensor maximum is asked for: one tile per CTA (as silu_mul_tile_kernel); act_path = 1 keeps the
+    // pipeline below, which the maximum-producing form always takes (its running maximum lives in the consumer warps)
+    const int nvec = int(F / 8);
+    int threads = 256, unroll = 2, best = 1 << 30;
+    for (int u = 2; u >= 1; u--)
+      for (int t = 256; t >= 128; t -= 32) {
+        const int tile = t * u, waste = int(ceil_div(nvec, tile)) * tile - nvec;
+        if (waste < best) best = waste, threads = t, unroll = u;
+      }
+    const dim3 grid(unsigned(rows), unsigned(ceil_div(nvec, threads * unroll)));
+    const bf16* ib = reinterpret_cast<const bf16*>(in);
+    bf16* ob = reinterpret_cast<bf16*>(out);
+    if (unroll == 2) launch_pdl(bias_act_tile_kernel<ACT, 2>, grid, dim3(threads), 0, s, ib, bias, F, nvec, ob);
+    else launch_pdl(bias_act_tile_kernel<ACT, 1>, grid, dim3(threads), 0, s, ib, bias, F, nvec, ob);
+    return after_launch(name);
+  }
   int chunk_bytes = tune(TUNE_STREAM_CHUNK_KB, 8) * 1024 / (two ? 2 : 1);
   if (chunk_bytes > 32 * 1024) chunk_bytes = 32 * 1024;
   const int pieces = int(ceil_div(F * 2, chunk_bytes));
