@@ -7,6 +7,7 @@
 #include <cstring>
 
 #include "common.cuh"
+#include "tuning.h"
 
 namespace mxk {
 namespace {
@@ -71,8 +72,10 @@ int mxk_gather_head_groups(const mxk_bf16* const* srcs_host, int groups, int64_t
   a.out = reinterpret_cast<uint4*>(out);
   const int64_t total = rows * int64_t(groups) * a.group_vecs;
   int64_t grid = ceil_div(total, 256 * 4);
-  const int64_t cap = int64_t(sm_count()) * 8;
+  // one tile of 4 x 256 vectors per CTA and as many CTAs as that takes unless ew_ctas_per_sm caps the grid
+  const int64_t cap = int64_t(sm_count()) * tune(TUNE_EW_CTAS_PER_SM, 1 << 20);
   if (grid > cap) grid = cap;
+  if (grid > (int64_t(1) << 31) - 1) grid = (int64_t(1) << 31) - 1;
   launch_pdl(gather_head_groups_kernel, dim3(unsigned(grid)), dim3(256), 0, as_stream(stream), a);
   return after_launch("gather_head_groups");
 }
